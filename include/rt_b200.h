@@ -1,0 +1,230 @@
+/*
+ * rt_b200.h -- C ABI of the sm_100a backward-pass backend.
+ *
+ * Every entry point takes plain pointers and sizes.  All `float*` / `void*` data
+ * arguments are DEVICE pointers unless the name says `host`.  All tensors are fp32,
+ * row-major, contiguous (NCHW for images); a 0-dimensional tensor is one element.
+ * Calls are asynchronous on the context's stream unless stated otherwise; nothing
+ * here synchronises except rt_sync, rt_memcpy_d2h and rt_sum_all_host.
+ *
+ * Each declaration cites the method of the reference's `Backend` trait
+ * (src/backend/mod.rs) -- or the helper it calls -- that a Rust
+ * `impl Backend for B200Backend` would forward to it.
+ *
+ * Return value: RT_OK or one of the RT_ERR_* codes, which mirror the variants of the
+ * reference's `Error` enum (src/error.rs:8-98).  rt_last_error(ctx) gives the text.
+ */
+#ifndef RT_B200_H
+#define RT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct rt_ctx rt_ctx;     /* one device + one stream + a caching allocator (+ an NCCL communicator) */
+typedef struct rt_graph rt_graph; /* an instantiated CUDA graph of a captured call sequence */
+typedef int32_t rt_status;
+
+enum {
+  RT_OK = 0,
+  RT_ERR_SHAPE_MISMATCH = 1,      /* Error::ShapeMismatch */
+  RT_ERR_INCOMPATIBLE_SHAPES = 2, /* Error::IncompatibleShapes */
+  RT_ERR_INVALID_INDEX = 3,       /* Error::InvalidIndex */
+  RT_ERR_INVALID_OPERATION = 4,   /* Error::InvalidOperation */
+  RT_ERR_INTERNAL = 5,            /* Error::InternalLogicError */
+  RT_ERR_DIMENSION_MISMATCH = 6,  /* Error::DimensionMismatch */
+  RT_ERR_CUDA = 7,                /* Error::CudaError */
+  RT_ERR_OOM = 8,                 /* Error::OutOfMemory */
+  RT_ERR_UNIMPLEMENTED = 9,       /* Error::Unimplemented */
+  RT_ERR_EMPTY_TENSOR = 10,       /* Error::EmptyTensor */
+  RT_ERR_TIMEOUT = 14,            /* a bounded device-side wait gave up */
+  RT_ERR_NCCL = 15
+};
+
+#define RT_MAX_DIMS 8
+
+/* ---- lifecycle, memory, stream ------------------------------------------------------------
+ * Replaces the reference's global CUDA context / stream / per-op cuMemAlloc
+ * (src/backend/cuda/context.rs:21-34,250-306; src/backend/cuda/storage.rs:165-179). */
+rt_status rt_ctx_create(int device, rt_ctx** out);
+rt_status rt_ctx_destroy(rt_ctx* ctx);
+const char* rt_last_error(rt_ctx* ctx);
+int rt_device_count(void);
+rt_status rt_malloc(rt_ctx* ctx, size_t bytes, void** out);   /* pooled; Backend::zeros/from_vec storage */
+rt_status rt_free(rt_ctx* ctx, void* ptr);                    /* returns the block to the pool (stream-ordered) */
+rt_status rt_memcpy_h2d(rt_ctx* ctx, void* dst, const void* host_src, size_t bytes); /* Backend::from_vec, update_from_host (mod.rs:48,252) */
+rt_status rt_memcpy_d2h(rt_ctx* ctx, void* host_dst, const void* src, size_t bytes); /* Backend::copy_to_host (mod.rs:248); synchronises */
+rt_status rt_memcpy_h2d_async(rt_ctx* ctx, void* dst, const void* pinned_src, size_t bytes);
+rt_status rt_memcpy_d2h_async(rt_ctx* ctx, void* pinned_dst, const void* src, size_t bytes);
+rt_status rt_memcpy_d2d(rt_ctx* ctx, void* dst, const void* src, size_t bytes);
+rt_status rt_fill(rt_ctx* ctx, float* dst, float value, int64_t n);                  /* Backend::zeros / ones (mod.rs:44,46) */
+rt_status rt_host_alloc(rt_ctx* ctx, size_t bytes, void** out);                      /* pinned host memory */
+rt_status rt_host_free(rt_ctx* ctx, void* ptr);
+rt_status rt_sync(rt_ctx* ctx);
+void* rt_stream(rt_ctx* ctx);                                                        /* the cudaStream_t */
+rt_status rt_mem_stats(rt_ctx* ctx, int64_t* bytes_reserved, int64_t* bytes_in_use, int64_t* n_device_allocs);
+rt_status rt_kernel_launch_count(rt_ctx* ctx, int64_t* launches);                    /* kernels launched by this library so far */
+
+/* CUDA-graph capture of a fixed call sequence (one training step). */
+rt_status rt_graph_begin(rt_ctx* ctx);
+rt_status rt_graph_end(rt_ctx* ctx, rt_graph** out);
+rt_status rt_graph_launch(rt_ctx* ctx, rt_graph* g);
+rt_status rt_graph_destroy(rt_ctx* ctx, rt_graph* g);
+rt_status rt_graph_num_nodes(rt_ctx* ctx, rt_graph* g, int64_t* n);
+
+/* Device-side timing on the context's stream (CUDA events). */
+rt_status rt_timer_start(rt_ctx* ctx);
+rt_status rt_timer_stop(rt_ctx* ctx, float* elapsed_ms); /* synchronises */
+
+/* ---- unary elementwise: y = f(x) and dx = g * f'(x), f' recomputed from the INPUT x ---------- */
+enum {
+  RT_RELU = 0,     /* relu mod.rs:303 / relu_backward mod.rs:344 (mask x > 0) */
+  RT_ELU = 1,      /* elu mod.rs:311 / elu_backward mod.rs:356; p0 = alpha */
+  RT_EXP = 2,      /* exp mod.rs:279 / exp_backward mod.rs:381 */
+  RT_LN = 3,       /* ln mod.rs:281 / ln_backward mod.rs:387 */
+  RT_SIN = 4,      /* sin mod.rs:474 / sin_backward mod.rs:480 */
+  RT_TANH = 5,     /* tanh mod.rs:414 / tanh_backward mod.rs:420 */
+  RT_SIGMOID = 6,  /* sigmoid mod.rs:305 / sigmoid_backward mod.rs:314 */
+  RT_SOFTPLUS = 7, /* softplus mod.rs:426 / softplus_backward mod.rs:429 (ln(1+e^x), as the CPU backend) */
+  RT_SQUARE = 8,   /* square mod.rs:444 / square_backward mod.rs:450 */
+  RT_SQRT = 9,     /* sqrt mod.rs:403 / sqrt_backward mod.rs:405 */
+  RT_ABS = 10,     /* abs mod.rs:395 / abs_backward mod.rs:397 */
+  RT_CLIP = 11,    /* clip mod.rs:629 / clip_backward mod.rs:642; p0 = min, p1 = max (inclusive mask) */
+  RT_MUL_SCALAR = 12, /* mul_scalar mod.rs:655; backward is mul_scalar on the gradient; p0 = scalar */
+  RT_DIV_SCALAR = 13, /* div_scalar mod.rs:242; p0 = scalar (0 -> RT_ERR_INVALID_OPERATION) */
+  RT_COS = 14,     /* cos mod.rs:486 / cos_backward mod.rs:492 */
+  RT_TAN = 15,     /* tan mod.rs:498 / tan_backward mod.rs:504 */
+  RT_UNARY_COUNT = 16
+};
+rt_status rt_unary(rt_ctx* ctx, int op, const float* x, float* y, int64_t n, float p0, float p1);
+rt_status rt_unary_backward(rt_ctx* ctx, int op, const float* x, const float* g, float* dx, int64_t n, float p0, float p1);
+
+/* ---- binary elementwise with numpy broadcasting --------------------------------------------
+ * Shapes are right-aligned; out has the broadcast shape.  rt_binary_backward fuses the
+ * `unbroadcast` reduction (src/ops/cpu_backward.rs:523-678) into the gradient kernels: da has
+ * a's shape and db has b's shape.  Pass NULL for a gradient that is not needed. */
+enum {
+  RT_ADD = 0,     /* add mod.rs:236 / add_backward mod.rs:334 */
+  RT_SUB = 1,     /* sub mod.rs:238 / sub_backward mod.rs:375 */
+  RT_MUL = 2,     /* mul mod.rs:234 / mul_backward mod.rs:329 */
+  RT_DIV = 3,     /* div mod.rs:240 / div_backward mod.rs:369 */
+  RT_POWF = 4,    /* powf mod.rs:435 / powf_backward mod.rs:438 */
+  RT_MAXIMUM = 5, /* maximum mod.rs:456 / maximum_backward mod.rs:459 (ties -> a) */
+  RT_MINIMUM = 6, /* minimum mod.rs:465 / minimum_backward mod.rs:468 (ties -> a) */
+  RT_EQUAL = 7, RT_NOT_EQUAL = 8, RT_GREATER = 9, RT_GREATER_EQUAL = 10, RT_LESS = 11, RT_LESS_EQUAL = 12, /* mod.rs:185-205 */
+  RT_BINARY_COUNT = 13
+};
+rt_status rt_binary(rt_ctx* ctx, int op, const float* a, const int64_t* a_shape, int a_ndim,
+                    const float* b, const int64_t* b_shape, int b_ndim, float* out);
+rt_status rt_binary_backward(rt_ctx* ctx, int op, const float* a, const int64_t* a_shape, int a_ndim,
+                             const float* b, const int64_t* b_shape, int b_ndim, const float* g,
+                             float* da, float* db);
+/* Sum `g` (shape g_shape) down to `target_shape`: leading extra dims and dims where the target
+ * is 1 (unbroadcast, src/ops/cpu_backward.rs:523-678; Broadcast-op backward, src/tensor.rs:785-794). */
+rt_status rt_unbroadcast(rt_ctx* ctx, const float* g, const int64_t* g_shape, int g_ndim,
+                         const int64_t* target_shape, int t_ndim, float* out);
+rt_status rt_broadcast_to(rt_ctx* ctx, const float* x, const int64_t* x_shape, int x_ndim,
+                          const int64_t* out_shape, int out_ndim, float* out);     /* broadcast_to mod.rs:277 */
+rt_status rt_transpose2d(rt_ctx* ctx, const float* x, int64_t rows, int64_t cols, float* out); /* transpose mod.rs:275 */
+/* dst[starts + i] = src[i] for every index i of src (write a block into a larger tensor);
+ * with it: slice_backward mod.rs:535 (= rt_fill 0 + assign), concat mod.rs:550. */
+rt_status rt_slice_assign(rt_ctx* ctx, float* dst, const int64_t* dst_shape, int ndim, const int64_t* starts,
+                          const float* src, const int64_t* src_shape);
+/* out[i] = x[starts + i]: slice mod.rs:522, concat_backward mod.rs:563. */
+rt_status rt_slice(rt_ctx* ctx, const float* x, const int64_t* x_shape, int ndim, const int64_t* starts,
+                   const int64_t* out_shape, float* out);
+
+/* ---- reductions over one axis of a tensor viewed as [outer, len, inner] ----------------------- */
+enum {
+  RT_RED_SUM = 0,       /* sum_along_axis mod.rs:291, sum_all mod.rs:293 */
+  RT_RED_MEAN = 1,      /* mean mod.rs:298 */
+  RT_RED_MAX = 2,       /* max mod.rs:160, max_along_axis mod.rs:295 */
+  RT_RED_MIN = 3,       /* min mod.rs:164 */
+  RT_RED_PROD = 4,      /* prod mod.rs:168 */
+  RT_RED_LOGSUMEXP = 5, /* logsumexp mod.rs:173 */
+  RT_RED_ARGMAX = 6,    /* argmax mod.rs:177 (index as f32, first maximum wins) */
+  RT_RED_ARGMIN = 7,    /* argmin mod.rs:181 */
+  RT_RED_COUNT = 8
+};
+rt_status rt_reduce(rt_ctx* ctx, int kind, const float* x, int64_t outer, int64_t len, int64_t inner, float* out);
+/* dx[o,k,i] from g[o,i]:  SUM: g; MEAN: g/len; MAX/MIN: g * [|x - ext| < 1e-9] / (ties + 1e-9);
+ * PROD: g * prod / (x + 1e-10); LOGSUMEXP: g * exp(x - lse).
+ * sum_backward mod.rs:363, mean_backward mod.rs:339, max/min/prod/logsumexp_backward mod.rs:210-231. */
+rt_status rt_reduce_backward(rt_ctx* ctx, int kind, const float* x, const float* g, int64_t outer, int64_t len,
+                             int64_t inner, float* dx);
+rt_status rt_sum_all_host(rt_ctx* ctx, const float* x, int64_t n, float* host_out); /* sum_all mod.rs:293; synchronises */
+rt_status rt_log_softmax(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* y); /* mod.rs:307 */
+/* dx = g - exp(log_softmax(x)) * sum_axis(g)   (log_softmax_backward mod.rs:349) */
+rt_status rt_log_softmax_backward(rt_ctx* ctx, const float* x, const float* g, int64_t outer, int64_t len,
+                                  int64_t inner, float* dx);
+
+/* ---- pooling (max_pool2d mod.rs:144, max_pool2d_backward mod.rs:151) -------------------------
+ * idx holds the in-window position ky*kw+kx of the first maximum as f32 (strict >, padding = -inf). */
+rt_status rt_max_pool2d(rt_ctx* ctx, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, int kh, int kw,
+                        int sh, int sw, int ph, int pw, float* y, float* idx);
+rt_status rt_max_pool2d_backward(rt_ctx* ctx, const float* g, const float* idx, int64_t n, int64_t c, int64_t h,
+                                 int64_t w, int kh, int kw, int sh, int sw, int ph, int pw, float* dx);
+
+/* ---- dense contractions ---------------------------------------------------------------------- */
+/* C[M,N] = op(A) * op(B) (+ C when accumulate != 0); row-major with leading dimensions.
+ * trans_a: A is stored [K,M]; trans_b: B is stored [N,K].  matmul mod.rs:93 and the
+ * transposed products of its backward closure (src/ops/mod.rs:161-175), without materialising
+ * the transposes. */
+rt_status rt_gemm(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, int64_t n, int64_t k, const float* a,
+                  int64_t lda, const float* b, int64_t ldb, float* c, int64_t ldc, int accumulate);
+/* da[M,K] = g * b^T, db[K,N] = a^T * g   (matmul_backward mod.rs:324); NULL skips one. */
+rt_status rt_matmul_backward(rt_ctx* ctx, const float* a, const float* b, const float* g, int64_t m, int64_t k,
+                             int64_t n, float* da, float* db);
+/* conv2d mod.rs:101: x[N,Cin,H,W], w[Cout,Cin,kh,kw], bias[Cout] or NULL -> y[N,Cout,Ho,Wo] */
+rt_status rt_conv2d(rt_ctx* ctx, const float* x, const float* w, const float* bias, int64_t n, int64_t cin,
+                    int64_t h, int64_t wd, int64_t cout, int kh, int kw, int sh, int sw, int ph, int pw, float* y);
+/* conv2d_backward mod.rs:111: any of dx, dw, db may be NULL.  dx is the mathematically correct
+ * input gradient (the reference CPU code's col2im reuses column 0, src/ops/cpu_ops.rs:266). */
+rt_status rt_conv2d_backward(rt_ctx* ctx, const float* x, const float* w, const float* g, int64_t n, int64_t cin,
+                             int64_t h, int64_t wd, int64_t cout, int kh, int kw, int sh, int sw, int ph, int pw,
+                             float* dx, float* dw, float* db);
+/* conv2d_transpose mod.rs:125: x[N,Cin,H,W], w[Cin,Cout,kh,kw] -> y[N,Cout,(H-1)sh+kh-2ph,(W-1)sw+kw-2pw] */
+rt_status rt_conv2d_transpose(rt_ctx* ctx, const float* x, const float* w, const float* bias, int64_t n,
+                              int64_t cin, int64_t h, int64_t wd, int64_t cout, int kh, int kw, int sh, int sw,
+                              int ph, int pw, float* y);
+/* conv2d_transpose_backward mod.rs:135; g is [N,Cout,OH,OW]. */
+rt_status rt_conv2d_transpose_backward(rt_ctx* ctx, const float* x, const float* w, const float* g, int64_t n,
+                                       int64_t cin, int64_t h, int64_t wd, int64_t cout, int kh, int kw, int sh,
+                                       int sw, int ph, int pw, float* dx, float* dw, float* db);
+
+/* ---- optimizer steps (in place) ---------------------------------------------------------------- */
+rt_status rt_sgd_step(rt_ctx* ctx, float* param, const float* grad, int64_t n, float lr);            /* mod.rs:256 */
+rt_status rt_momentum_sgd_step(rt_ctx* ctx, float* param, const float* grad, float* velocity, int64_t n,
+                               float lr, float momentum);                                              /* mod.rs:18 */
+rt_status rt_adagrad_step(rt_ctx* ctx, float* param, const float* grad, float* accum, int64_t n, float lr,
+                          float epsilon);                                                              /* mod.rs:30 */
+rt_status rt_adam_step(rt_ctx* ctx, float* param, const float* grad, float* m, float* v, int64_t n, float lr,
+                       float beta1, float beta2, float epsilon, int64_t t);                           /* mod.rs:262 */
+/* One launch over a list of tensors (the whole model): kind 0 sgd, 1 adam, 2 momentum, 3 adagrad.
+ * The gradient is first multiplied by grad_scale (1/world after an all-reduce) and, when
+ * clip != 0, clamped to [clip_lo, clip_hi] BEFORE the scale (Backend::clip, mod.rs:629).
+ * state2 is only read for Adam.  Pointer arrays are host arrays of device pointers. */
+rt_status rt_optimizer_step_multi(rt_ctx* ctx, int kind, int n_tensors, float* const* params,
+                                  const float* const* grads, float* const* state1, float* const* state2,
+                                  const int64_t* sizes, float lr, float beta1, float beta2, float epsilon,
+                                  float momentum, int64_t t, float grad_scale, int clip, float clip_lo,
+                                  float clip_hi);
+
+/* ---- data-parallel gradient exchange (no counterpart in the reference: it has no distributed code) */
+/* Copies a list of gradient tensors into one flat buffer (optionally clamping), so that one
+ * all-reduce covers the model. */
+rt_status rt_pack_flat(rt_ctx* ctx, int n_tensors, const float* const* srcs, const int64_t* sizes, float* flat,
+                       int clip, float clip_lo, float clip_hi);
+#define RT_DP_ID_BYTES 128
+rt_status rt_dp_unique_id(uint8_t id[RT_DP_ID_BYTES]);                /* rank 0 creates, every rank receives a copy */
+rt_status rt_dp_init(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID_BYTES]);
+rt_status rt_dp_allreduce_sum(rt_ctx* ctx, float* buf, int64_t n);    /* in place, on the context's stream */
+rt_status rt_dp_finalize(rt_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RT_B200_H */

@@ -38,7 +38,7 @@ def load():
 
 def engine():
     """An ``Engine`` whose tensors live in host memory and whose math is the oracle's."""
-    from rusttensor_b200.engine import Engine
+    from rusttensor_b200.frontend import Engine
 
     return Engine(load(), "orc")
 

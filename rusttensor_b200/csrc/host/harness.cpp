@@ -1,0 +1,315 @@
+// librt_b200_host.so: the host side above the C ABI.
+//
+//  * `rth_*` engine API: the generic autograd engine (autograd.hpp) instantiated for the
+//    CUDA backend, i.e. what a user of the reference gets from Tensor<B> / ops::* /
+//    optim::* once B = B200Backend.
+//  * `rth_dp_*`: the data-parallel training step built on top of it: forward + backward,
+//    one all-reduce of the flat gradient buffer, one fused multi-tensor optimizer launch,
+//    with the forward+backward part replayed from a CUDA graph.
+//
+// No CPU fallback: every entry point fails with CudaError when no context exists.
+#include <cstring>
+
+#include "b200_backend.hpp"
+#include "engine_capi.hpp"
+
+using rt::B200Backend;
+using rt::Error;
+using rt::ErrorKind;
+using Tensor = rt::Tensor<B200Backend>;
+using Storage = B200Backend::Storage;
+
+RT_DEFINE_ENGINE_CAPI(rth, rt::B200Backend)
+
+namespace {
+
+// compiler-rt __powisf2 (f32::powi), for parity of Adam's bias correction on the host
+// side when needed by callers.
+struct DpTrainer {
+  std::shared_ptr<rt::models::Trainer<B200Backend>> tr;
+  int rank = 0, world = 1;
+  std::vector<Storage> state1, state2;  // m / velocity, v
+  Storage flat;                          // packed gradients (offsets padded to 4 elements)
+  std::vector<int64_t> sizes, offsets;
+  int64_t flat_len = 0;
+  int64_t t = 0;
+  // fixed device inputs + pinned host staging for the graph path
+  std::vector<Tensor> inputs;
+  std::vector<float*> pinned_in;
+  float* pinned_loss = nullptr;
+  Tensor captured_loss;
+  rt_graph* graph = nullptr;
+  bool have_loss = false;
+
+  ~DpTrainer() {
+    rt_ctx* c = B200Backend::ctx_slot();
+    if (!c) return;
+    if (graph) rt_graph_destroy(c, graph);
+    for (float* p : pinned_in) rt_host_free(c, p);
+    if (pinned_loss) rt_host_free(c, pinned_loss);
+  }
+
+  void setup() {
+    auto& w = tr->w;
+    int64_t off = 0;
+    for (auto& p : w.params) {
+      int64_t n = (int64_t)p.size();
+      sizes.push_back(n);
+      offsets.push_back(off);
+      off += (n + 3) & ~int64_t(3);
+      if (w.optimizer != 0) state1.push_back(B200Backend::zeros(p.shape()));
+      if (w.optimizer == 1) state2.push_back(B200Backend::zeros(p.shape()));
+    }
+    flat_len = off;
+    if (world > 1) flat = B200Backend::zeros(rt::Shape{(size_t)flat_len});
+    for (auto& s : w.input_shapes) {
+      // C4's first input receives a gradient ("backward to input")
+      bool rg = (w.config == rt::models::C4_CONV_CONVT) && inputs.empty();
+      inputs.push_back(Tensor::zeros(s, rg));
+      void* hp = nullptr;
+      B200Backend::check(rt_host_alloc(B200Backend::ctx(), sizeof(float) * rt::shape_numel(s), &hp));
+      pinned_in.push_back((float*)hp);
+    }
+    void* lp = nullptr;
+    B200Backend::check(rt_host_alloc(B200Backend::ctx(), sizeof(float), &lp));
+    pinned_loss = (float*)lp;
+  }
+
+  // forward + backward (+ pack for the all-reduce); everything asynchronous.
+  Tensor forward_backward() {
+    auto& w = tr->w;
+    for (auto& p : w.params) p.zero_grad();
+    for (auto& x : inputs) x.zero_grad();
+    Tensor loss = rt::models::forward_loss(w, inputs);
+    loss.backward();
+    if (world > 1) {
+      std::vector<const float*> srcs;
+      for (auto& p : w.params) {
+        if (!p.grad()) throw Error(ErrorKind::NoGradientError, "parameter received no gradient");
+        srcs.push_back(p.grad()->ptr());
+      }
+      B200Backend::check(rt_pack_flat(B200Backend::ctx(), (int)srcs.size(), srcs.data(), sizes.data(), flat.ptr(),
+                                      w.clip_grads ? 1 : 0, w.clip_lo, w.clip_hi));
+    }
+    return loss;
+  }
+
+  void exchange_and_update() {
+    auto& w = tr->w;
+    rt_ctx* c = B200Backend::ctx();
+    if (world > 1) B200Backend::check(rt_dp_allreduce_sum(c, flat.ptr(), flat_len));
+    if (w.optimizer == 0) return;
+    t += 1;
+    std::vector<float*> ps, s1, s2;
+    std::vector<const float*> gs;
+    for (size_t i = 0; i < w.params.size(); ++i) {
+      auto& p = w.params[i];
+      B200Backend::make_unique(p.data_mut());
+      B200Backend::make_unique(state1[i]);
+      if (w.optimizer == 1) B200Backend::make_unique(state2[i]);
+      ps.push_back(p.data().ptr());
+      s1.push_back(state1[i].ptr());
+      s2.push_back(w.optimizer == 1 ? state2[i].ptr() : nullptr);
+      if (world > 1) gs.push_back(flat.ptr() + offsets[i]);
+      else {
+        if (!p.grad()) throw Error(ErrorKind::NoGradientError, "parameter received no gradient");
+        gs.push_back(p.grad()->ptr());
+      }
+    }
+    // single GPU: clip fused here; multi GPU: the clip already happened while packing
+    int clip = (world == 1 && w.clip_grads) ? 1 : 0;
+    B200Backend::check(rt_optimizer_step_multi(c, w.optimizer == 1 ? 1 : 2, (int)ps.size(), ps.data(), gs.data(), s1.data(),
+                                               s2.data(), sizes.data(), w.lr, w.beta1, w.beta2, w.eps, w.momentum, t,
+                                               1.0f / (float)world, clip, w.clip_lo, w.clip_hi));
+  }
+
+  void upload_inputs(const float* const* host_inputs, int n, bool from_pinned) {
+    rt_ctx* c = B200Backend::ctx();
+    if (n != (int)inputs.size()) throw Error::invalid_op("wrong number of inputs");
+    for (int i = 0; i < n; ++i) {
+      size_t bytes = sizeof(float) * inputs[i].size();
+      B200Backend::make_unique(inputs[i].data_mut());
+      if (from_pinned) B200Backend::check(rt_memcpy_h2d_async(c, inputs[i].data().ptr(), host_inputs[i], bytes));
+      else {
+        std::memcpy(pinned_in[i], host_inputs[i], bytes);
+        B200Backend::check(rt_memcpy_h2d_async(c, inputs[i].data().ptr(), pinned_in[i], bytes));
+      }
+    }
+  }
+
+  // One eager step (host builds the graph of tensors every time).
+  float step_eager(const float* const* host_inputs, int n) {
+    if (graph) throw Error::invalid_op("step_eager after capture: use step_graph");
+    upload_inputs(host_inputs, n, false);
+    captured_loss = forward_backward();
+    have_loss = true;
+    exchange_and_update();
+    rt_ctx* c = B200Backend::ctx();
+    B200Backend::check(rt_memcpy_d2h_async(c, pinned_loss, captured_loss.data().ptr(), sizeof(float)));
+    B200Backend::check(rt_sync(c));
+    return *pinned_loss;
+  }
+
+  // Records forward+backward(+pack) once; afterwards a step is: H2D of the inputs,
+  // one graph launch, the all-reduce, one optimizer launch, D2H of the loss.
+  void capture() {
+    rt_ctx* c = B200Backend::ctx();
+    if (graph) return;
+    captured_loss = Tensor();
+    have_loss = false;
+    B200Backend::check(rt_graph_begin(c));
+    try {
+      captured_loss = forward_backward();
+    } catch (...) {
+      rt_graph* g = nullptr;
+      rt_graph_end(c, &g);
+      if (g) rt_graph_destroy(c, g);
+      throw;
+    }
+    B200Backend::check(rt_graph_end(c, &graph));
+    have_loss = true;
+  }
+
+  // host_inputs == nullptr: reuse the inputs already resident on the device
+  void step_graph_async(const float* const* host_inputs, int n, bool from_pinned) {
+    if (!graph) capture();
+    rt_ctx* c = B200Backend::ctx();
+    if (host_inputs) upload_inputs(host_inputs, n, from_pinned);
+    B200Backend::check(rt_graph_launch(c, graph));
+    exchange_and_update();
+    if (host_inputs) B200Backend::check(rt_memcpy_d2h_async(c, pinned_loss, captured_loss.data().ptr(), sizeof(float)));
+  }
+};
+
+std::map<int64_t, std::shared_ptr<DpTrainer>>& dp_table() {
+  static std::map<int64_t, std::shared_ptr<DpTrainer>> t;
+  return t;
+}
+int64_t& dp_next() {
+  static int64_t n = 1;
+  return n;
+}
+DpTrainer& dp_get(int64_t h) {
+  auto it = dp_table().find(h);
+  if (it == dp_table().end()) throw Error::invalid_op("unknown dp trainer handle");
+  return *it->second;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Creates the device context used by every rth_* call of this process.
+int rth_init(int device) {
+  return rt::capi::guarded<B200Backend>([&](auto&) {
+    if (B200Backend::ctx_slot()) return;
+    rt_ctx* c = nullptr;
+    rt_status st = rt_ctx_create(device, &c);
+    if (st != RT_OK) throw Error((ErrorKind)st, "rt_ctx_create failed (no usable CUDA device?)");
+    B200Backend::ctx_slot() = c;
+  });
+}
+
+void* rth_ctx() { return B200Backend::ctx_slot(); }
+
+int rth_shutdown() {
+  return rt::capi::guarded<B200Backend>([&](auto& r) {
+    dp_table().clear();
+    r.trainers.clear();
+    r.optims.clear();
+    r.tensors.clear();
+    if (B200Backend::ctx_slot()) {
+      rt_ctx_destroy(B200Backend::ctx_slot());
+      B200Backend::ctx_slot() = nullptr;
+    }
+  });
+}
+
+int rth_sync() {
+  return rt::capi::guarded<B200Backend>([&](auto&) { B200Backend::check(rt_sync(B200Backend::ctx())); });
+}
+
+// Device pointer of a tensor's data (for calling the raw C ABI on engine tensors).
+int rth_tensor_device_ptr(int64_t h, void** out) {
+  return rt::capi::guarded<B200Backend>([&](auto& r) { *out = r.get(h).data().ptr(); });
+}
+
+// ---- data-parallel trainer ------------------------------------------------------------
+int rth_dp_create(int config, const int64_t* dims, int nd, int rank, int world, const uint8_t* nccl_id, int64_t* out) {
+  return rt::capi::guarded<B200Backend>([&](auto&) {
+    auto d = std::make_shared<DpTrainer>();
+    std::vector<size_t> dv(dims, dims + nd);
+    d->tr = std::make_shared<rt::models::Trainer<B200Backend>>(rt::models::make_workload<B200Backend>(config, dv));
+    d->rank = rank;
+    d->world = world;
+    if (world > 1) B200Backend::check(rt_dp_init(B200Backend::ctx(), rank, world, nccl_id));
+    d->setup();
+    dp_table()[dp_next()] = d;
+    *out = dp_next()++;
+  });
+}
+int rth_dp_free(int64_t h) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { dp_table().erase(h); });
+}
+int rth_dp_num_params(int64_t h, int* n) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { *n = (int)dp_get(h).tr->w.params.size(); });
+}
+int rth_dp_param(int64_t h, int i, int64_t* out) {
+  return rt::capi::guarded<B200Backend>([&](auto& r) { *out = r.put(dp_get(h).tr->w.params.at(i)); });
+}
+int rth_dp_input(int64_t h, int i, int64_t* out) {
+  return rt::capi::guarded<B200Backend>([&](auto& r) { *out = r.put(dp_get(h).inputs.at(i)); });
+}
+int rth_dp_state(int64_t h, int which, int i, int64_t* out) {
+  return rt::capi::guarded<B200Backend>([&](auto& r) {
+    auto& d = dp_get(h);
+    *out = r.put(Tensor(which == 0 ? d.state1.at(i) : d.state2.at(i), false));
+  });
+}
+int rth_dp_set_hyper(int64_t h, const double* hp, int n) {
+  return rt::capi::guarded<B200Backend>([&](auto&) {
+    auto& w = dp_get(h).tr->w;
+    if (n > 0) w.lr = (float)hp[0];
+    if (n > 1) w.beta1 = (float)hp[1];
+    if (n > 2) w.beta2 = (float)hp[2];
+    if (n > 3) w.eps = (float)hp[3];
+    if (n > 4) w.momentum = (float)hp[4];
+  });
+}
+// Pinned staging buffer of input i (fill it, then call rth_dp_step_graph with pinned = 1).
+int rth_dp_pinned_input(int64_t h, int i, float** out) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { *out = dp_get(h).pinned_in.at(i); });
+}
+int rth_dp_step_eager(int64_t h, const float* const* host_inputs, int n, float* loss) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { *loss = dp_get(h).step_eager(host_inputs, n); });
+}
+int rth_dp_capture(int64_t h) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { dp_get(h).capture(); });
+}
+// Asynchronous: returns after enqueueing.  host_inputs may be NULL (device-resident inputs).
+int rth_dp_step_graph(int64_t h, const float* const* host_inputs, int n, int pinned) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { dp_get(h).step_graph_async(host_inputs, n, pinned != 0); });
+}
+// Synchronises and returns the loss copied by the last step that uploaded inputs.
+int rth_dp_last_loss(int64_t h, float* loss) {
+  return rt::capi::guarded<B200Backend>([&](auto&) {
+    B200Backend::check(rt_sync(B200Backend::ctx()));
+    *loss = *dp_get(h).pinned_loss;
+  });
+}
+int rth_dp_loss_tensor(int64_t h, int64_t* out) {
+  return rt::capi::guarded<B200Backend>([&](auto& r) {
+    auto& d = dp_get(h);
+    if (!d.have_loss) throw Error::invalid_op("no step has run yet");
+    *out = r.put(d.captured_loss);
+  });
+}
+int rth_dp_graph_nodes(int64_t h, int64_t* n) {
+  return rt::capi::guarded<B200Backend>([&](auto&) {
+    auto& d = dp_get(h);
+    *n = 0;
+    if (d.graph) B200Backend::check(rt_graph_num_nodes(B200Backend::ctx(), d.graph, n));
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,174 @@
+// max_pool2d forward (values + in-window argmax index stored as f32) and backward
+// (gradient routed through the saved indices).
+//
+// Index semantics follow the reference CPU code bit for bit (src/ops/cpu_ops.rs:7-61):
+// windows are scanned ky-outer / kx-inner, a candidate wins only with a strict `>`, the
+// running maximum starts at -inf with index 0, out-of-range taps read as -inf (so they
+// can never win), NaN never wins.
+//
+// Backward (src/ops/cpu_backward.rs:9-46): when windows do not overlap (stride >= kernel)
+// every input element belongs to at most one window, so the scatter has no write
+// conflicts and runs without atomics; the common 2x2 / stride 2 / no-padding case is
+// written as a gather that produces each 2x2 block of dx with two 8-byte stores and needs
+// no zero-fill.  Overlapping windows fall back to atomicAdd into a zero-filled dx.
+#include <cmath>
+
+#include "rt_internal.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__global__ void __launch_bounds__(kThreads) pool_fwd_general(const float* __restrict__ x, float* __restrict__ y,
+                                                              float* __restrict__ idx, int64_t total, int h, int w, int ho,
+                                                              int wo, int kh, int kw, int sh, int sw, int ph, int pw) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += stride) {
+    int xo = (int)(o % wo);
+    int64_t r = o / wo;
+    int yo = (int)(r % ho);
+    int64_t bc = r / ho;
+    const float* p = x + bc * h * w;
+    float mv = -INFINITY;
+    int mi = 0, iw = 0;
+    for (int ky = 0; ky < kh; ++ky) {
+      int iy = yo * sh + ky - ph;
+      for (int kx = 0; kx < kw; ++kx, ++iw) {
+        int ix = xo * sw + kx - pw;
+        float v = (iy >= 0 && iy < h && ix >= 0 && ix < w) ? __ldg(p + (int64_t)iy * w + ix) : -INFINITY;
+        if (v > mv) {
+          mv = v;
+          mi = iw;
+        }
+      }
+    }
+    y[o] = mv;
+    idx[o] = (float)mi;
+  }
+}
+
+// 2x2 window, stride 2, no padding, even H and W: one thread per output, two 8-byte loads.
+__global__ void __launch_bounds__(kThreads) pool_fwd_2x2(const float* __restrict__ x, float* __restrict__ y,
+                                                          float* __restrict__ idx, int64_t total, int w, int ho, int wo) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += stride) {
+    int xo = (int)(o % wo);
+    int64_t row = o / wo;  // = bc * ho + yo ; the input row pair starts at 2 * row (H = 2 * ho)
+    const float2* p = reinterpret_cast<const float2*>(x + (row * 2) * w) + xo;
+    float2 a = __ldg(p), b = __ldg(p + (w >> 1));
+    float mv = -INFINITY;
+    int mi = 0;
+    if (a.x > mv) { mv = a.x; mi = 0; }
+    if (a.y > mv) { mv = a.y; mi = 1; }
+    if (b.x > mv) { mv = b.x; mi = 2; }
+    if (b.y > mv) { mv = b.y; mi = 3; }
+    y[o] = mv;
+    idx[o] = (float)mi;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) pool_bwd_2x2(const float* __restrict__ g, const float* __restrict__ idx,
+                                                          float* __restrict__ dx, int64_t total, int w, int ho, int wo) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += stride) {
+    int xo = (int)(o % wo);
+    int64_t row = o / wo;
+    float gv = __ldg(g + o);
+    int mi = (int)lrintf(__ldg(idx + o));
+    float2 a = make_float2(mi == 0 ? gv : 0.f, mi == 1 ? gv : 0.f);
+    float2 b = make_float2(mi == 2 ? gv : 0.f, mi == 3 ? gv : 0.f);
+    float2* p = reinterpret_cast<float2*>(dx + (row * 2) * w) + xo;
+    p[0] = a;
+    p[w >> 1] = b;
+  }
+}
+
+template <bool ATOMIC>
+__global__ void __launch_bounds__(kThreads) pool_bwd_general(const float* __restrict__ g, const float* __restrict__ idx,
+                                                              float* __restrict__ dx, int64_t total, int h, int w, int ho,
+                                                              int wo, int kw, int sh, int sw, int ph, int pw) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += stride) {
+    int xo = (int)(o % wo);
+    int64_t r = o / wo;
+    int yo = (int)(r % ho);
+    int64_t bc = r / ho;
+    long flat = lrintf(__ldg(idx + o));  // `.round() as usize` in the reference
+    if (flat < 0) flat = 0;
+    int ky = (int)(flat / kw), kx = (int)(flat % kw);
+    int iy = yo * sh + ky - ph, ix = xo * sw + kx - pw;
+    if (iy >= 0 && iy < h && ix >= 0 && ix < w) {
+      float* q = dx + (bc * h + iy) * w + ix;
+      if (ATOMIC) atomicAdd(q, __ldg(g + o));
+      else *q += __ldg(g + o);
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+static rt_status pool_dims(rt_ctx* ctx, int64_t h, int64_t w, int kh, int kw, int sh, int sw, int ph, int pw, int64_t* ho,
+                           int64_t* wo) {
+  if (kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 || ph < 0 || pw < 0)
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "max_pool2d: kernel and stride must be positive, padding non-negative");
+  if (h + 2 * ph < kh || w + 2 * pw < kw) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "max_pool2d: window larger than padded input");
+  if (h >= (1 << 30) || w >= (1 << 30)) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "max_pool2d: image too large");
+  *ho = (h + 2 * ph - kh) / sh + 1;
+  *wo = (w + 2 * pw - kw) / sw + 1;
+  return RT_OK;
+}
+
+rt_status rt_max_pool2d(rt_ctx* ctx, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, int kh, int kw, int sh,
+                        int sw, int ph, int pw, float* y, float* idx) {
+  RT_CHECK_CTX(ctx);
+  int64_t ho, wo;
+  rt_status st = pool_dims(ctx, h, w, kh, kw, sh, sw, ph, pw, &ho, &wo);
+  if (st != RT_OK) return st;
+  int64_t total = n * c * ho * wo;
+  if (total == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, x);
+  RT_CHECK_PTR(ctx, y);
+  RT_CHECK_PTR(ctx, idx);
+  int grid = rt_grid_for(ctx, total, kThreads * 2);
+  bool fast = kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && (h % 2 == 0) && (w % 2 == 0) &&
+              (reinterpret_cast<uintptr_t>(x) % 8 == 0);
+  if (fast) pool_fwd_2x2<<<grid, kThreads, 0, ctx->stream>>>(x, y, idx, total, (int)w, (int)ho, (int)wo);
+  else pool_fwd_general<<<grid, kThreads, 0, ctx->stream>>>(x, y, idx, total, (int)h, (int)w, (int)ho, (int)wo, kh, kw, sh, sw, ph, pw);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+rt_status rt_max_pool2d_backward(rt_ctx* ctx, const float* g, const float* idx, int64_t n, int64_t c, int64_t h, int64_t w,
+                                 int kh, int kw, int sh, int sw, int ph, int pw, float* dx) {
+  RT_CHECK_CTX(ctx);
+  int64_t ho, wo;
+  rt_status st = pool_dims(ctx, h, w, kh, kw, sh, sw, ph, pw, &ho, &wo);
+  if (st != RT_OK) return st;
+  int64_t total = n * c * ho * wo, in_total = n * c * h * w;
+  if (in_total == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, dx);
+  bool fast = kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && (h % 2 == 0) && (w % 2 == 0) &&
+              (reinterpret_cast<uintptr_t>(dx) % 8 == 0);
+  if (fast) {
+    if (total == 0) return RT_OK;
+    RT_CHECK_PTR(ctx, g);
+    RT_CHECK_PTR(ctx, idx);
+    pool_bwd_2x2<<<rt_grid_for(ctx, total, kThreads * 2), kThreads, 0, ctx->stream>>>(g, idx, dx, total, (int)w, (int)ho, (int)wo);
+    RT_LAUNCHED(ctx);
+    return RT_OK;
+  }
+  st = rt_fill(ctx, dx, 0.f, in_total);
+  if (st != RT_OK || total == 0) return st;
+  RT_CHECK_PTR(ctx, g);
+  RT_CHECK_PTR(ctx, idx);
+  int grid = rt_grid_for(ctx, total, kThreads * 2);
+  bool overlap = sh < kh || sw < kw;
+  if (overlap) pool_bwd_general<true><<<grid, kThreads, 0, ctx->stream>>>(g, idx, dx, total, (int)h, (int)w, (int)ho, (int)wo, kw, sh, sw, ph, pw);
+  else pool_bwd_general<false><<<grid, kThreads, 0, ctx->stream>>>(g, idx, dx, total, (int)h, (int)w, (int)ho, (int)wo, kw, sh, sw, ph, pw);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,565 @@
+// Axis reductions (sum / mean / max / min / prod / logsumexp / argmax / argmin),
+// log_softmax, and their gradients, over a tensor viewed as [outer, len, inner].
+//
+// inner == 1  (reduce contiguous rows): a warp per short row (shuffle reduction), a
+//              256-thread block per long row (shared-memory reduction, 128-bit loads),
+//              or, when there are few long rows, a split into chunks whose partial
+//              results are reduced by a second pass.
+// inner  > 1  (reduce a strided axis): threads run along `inner` (coalesced), rows of
+//              the reduced axis are spread over threadIdx.y and, when the output is
+//              small, over blockIdx.y with a second pass over the partials.
+// Every multi-block reduction is two-pass and atomics-free, so results are
+// run-to-run deterministic.
+#include <cfloat>
+#include <cmath>
+
+#include "rt_internal.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <int KIND>
+struct Red;
+template <>
+struct Red<RT_RED_SUM> {
+  static __device__ __forceinline__ float init() { return 0.f; }
+  static __device__ __forceinline__ float op(float a, float b) { return a + b; }
+};
+template <>
+struct Red<RT_RED_MAX> {
+  static __device__ __forceinline__ float init() { return -INFINITY; }
+  static __device__ __forceinline__ float op(float a, float b) { return fmaxf(a, b); }
+};
+template <>
+struct Red<RT_RED_MIN> {
+  static __device__ __forceinline__ float init() { return INFINITY; }
+  static __device__ __forceinline__ float op(float a, float b) { return fminf(a, b); }
+};
+template <>
+struct Red<RT_RED_PROD> {
+  static __device__ __forceinline__ float init() { return 1.f; }
+  static __device__ __forceinline__ float op(float a, float b) { return a * b; }
+};
+
+template <int KIND>
+__device__ __forceinline__ float warp_reduce(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = Red<KIND>::op(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <int KIND>
+__device__ __forceinline__ float block_reduce(float v, float* smem) {  // smem: kThreads/32 floats; result valid in all threads
+  v = warp_reduce<KIND>(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) smem[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = Red<KIND>::init();
+#pragma unroll
+  for (int i = 0; i < kThreads / 32; ++i) r = Red<KIND>::op(r, smem[i]);
+  return r;
+}
+
+// ---- inner == 1: warp per row ------------------------------------------------------
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) row_reduce_warp(const float* __restrict__ x, float* __restrict__ out,
+                                                             int64_t rows, int64_t len, float scale) {
+  int lane = threadIdx.x & 31;
+  int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    const float* p = x + r * len;
+    float acc = Red<KIND>::init();
+    for (int64_t k = lane; k < len; k += 32) acc = Red<KIND>::op(acc, __ldg(p + k));
+    acc = warp_reduce<KIND>(acc);
+    if (lane == 0) out[r] = acc * scale;
+  }
+}
+
+// ---- inner == 1: block per (row, chunk) --------------------------------------------
+// Row r is cut into `chunks` pieces of `chunk_len`; block (r, c) reduces one piece and
+// writes out[r * chunks + c].
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) row_reduce_block(const float* __restrict__ x, float* __restrict__ out,
+                                                              int64_t rows, int64_t len, int64_t chunks,
+                                                              int64_t chunk_len, float scale) {
+  __shared__ float smem[kThreads / 32];
+  for (int64_t job = blockIdx.x; job < rows * chunks; job += gridDim.x) {
+    int64_t r = job / chunks, c = job % chunks;
+    int64_t k0 = c * chunk_len, k1 = k0 + chunk_len;
+    if (k1 > len) k1 = len;
+    const float* p = x + r * len;
+    float acc = Red<KIND>::init();
+    // peel to a 16-byte boundary, then 128-bit loads
+    int64_t k = k0;
+    int64_t mis = ((reinterpret_cast<uintptr_t>(p + k) & 15) >> 2);
+    int64_t head = mis ? 4 - mis : 0;
+    if (head > k1 - k0) head = k1 - k0;
+    if ((int64_t)threadIdx.x < head) acc = Red<KIND>::op(acc, __ldg(p + k + threadIdx.x));
+    k += head;
+    int64_t n4 = (k1 - k) >> 2;
+    const float4* p4 = reinterpret_cast<const float4*>(p + k);
+    for (int64_t i = threadIdx.x; i < n4; i += kThreads) {
+      float4 v = __ldg(p4 + i);
+      acc = Red<KIND>::op(acc, Red<KIND>::op(Red<KIND>::op(v.x, v.y), Red<KIND>::op(v.z, v.w)));
+    }
+    int64_t t0 = k + (n4 << 2);
+    if (t0 + threadIdx.x < k1) acc = Red<KIND>::op(acc, __ldg(p + t0 + threadIdx.x));
+    float res = block_reduce<KIND>(acc, smem);
+    if (threadIdx.x == 0) out[job] = res * scale;
+  }
+}
+
+// ---- inner > 1: column reduction -----------------------------------------------------
+// grid: (inner tiles, k-splits, outer); block: (32, 8).  VEC: 4 columns per thread.
+template <int KIND, bool VEC>
+__global__ void __launch_bounds__(256) col_reduce(const float* __restrict__ x, float* __restrict__ out, int64_t len,
+                                                   int64_t inner, int64_t splits, int64_t rows_per_split, float scale) {
+  constexpr int W = VEC ? 4 : 1;
+  __shared__ float red[8][32 * W + 1];
+  int64_t o = blockIdx.z;
+  int64_t i0 = ((int64_t)blockIdx.x * 32 + threadIdx.x) * W;
+  int64_t k0 = (int64_t)blockIdx.y * rows_per_split, k1 = k0 + rows_per_split;
+  if (k1 > len) k1 = len;
+  float acc[W];
+#pragma unroll
+  for (int j = 0; j < W; ++j) acc[j] = Red<KIND>::init();
+  if (i0 < inner) {
+    const float* base = x + o * len * inner + i0;
+    for (int64_t k = k0 + threadIdx.y; k < k1; k += 8) {
+      if (VEC) {
+        float4 v = __ldg(reinterpret_cast<const float4*>(base + k * inner));
+        acc[0] = Red<KIND>::op(acc[0], v.x);
+        acc[1 % W] = Red<KIND>::op(acc[1 % W], v.y);
+        acc[2 % W] = Red<KIND>::op(acc[2 % W], v.z);
+        acc[3 % W] = Red<KIND>::op(acc[3 % W], v.w);
+      } else {
+        acc[0] = Red<KIND>::op(acc[0], __ldg(base + k * inner));
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < W; ++j) red[threadIdx.y][threadIdx.x * W + j] = acc[j];
+  __syncthreads();
+  if (threadIdx.y == 0 && i0 < inner) {
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      float s = red[0][threadIdx.x * W + j];
+#pragma unroll
+      for (int y = 1; y < 8; ++y) s = Red<KIND>::op(s, red[y][threadIdx.x * W + j]);
+      // out layout [outer, splits, inner]
+      out[(o * splits + blockIdx.y) * inner + i0 + j] = s * scale;
+    }
+  }
+}
+
+template <int KIND>
+rt_status reduce_float(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out, float scale) {
+  if (outer * inner == 0) return RT_OK;
+  if (len == 0) {  // empty reduction -> identity
+    return rt_fill(ctx, out, KIND == RT_RED_SUM ? 0.f : (KIND == RT_RED_PROD ? 1.f : (KIND == RT_RED_MAX ? -INFINITY : INFINITY)),
+                   outer * inner);
+  }
+  const int64_t target_blocks = (int64_t)ctx->sm_count * 4;
+  if (inner == 1) {
+    int64_t rows = outer;
+    if (len <= 1024) {
+      int grid = rt_grid_for(ctx, rows, kThreads / 32);
+      row_reduce_warp<KIND><<<grid, kThreads, 0, ctx->stream>>>(x, out, rows, len, scale);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
+    int64_t chunks = 1;
+    if (rows < target_blocks) {
+      chunks = (target_blocks + rows - 1) / rows;
+      int64_t max_chunks = (len + 4095) / 4096;  // at least 4096 elements per chunk
+      if (chunks > max_chunks) chunks = max_chunks;
+      if (chunks < 1) chunks = 1;
+    }
+    int64_t chunk_len = (len + chunks - 1) / chunks;
+    chunk_len = (chunk_len + 3) & ~int64_t(3);
+    chunks = (len + chunk_len - 1) / chunk_len;
+    int grid = (int)((rows * chunks < target_blocks * 2) ? rows * chunks : target_blocks * 2);
+    if (chunks == 1) {
+      row_reduce_block<KIND><<<grid, kThreads, 0, ctx->stream>>>(x, out, rows, len, 1, chunk_len, scale);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
+    RtScratch part(ctx);
+    rt_status st = part.alloc(sizeof(float) * rows * chunks);
+    if (st != RT_OK) return st;
+    row_reduce_block<KIND><<<grid, kThreads, 0, ctx->stream>>>(x, part.as<float>(), rows, len, chunks, chunk_len, 1.f);
+    RT_LAUNCHED(ctx);
+    return reduce_float<KIND>(ctx, part.as<float>(), rows, chunks, 1, out, scale);
+  }
+  // inner > 1
+  bool vec = (inner % 4 == 0) && rt_aligned16(x);
+  int64_t tiles = (inner + (vec ? 128 : 32) - 1) / (vec ? 128 : 32);
+  int64_t splits = 1;
+  if (tiles * outer < target_blocks) {
+    splits = (target_blocks + tiles * outer - 1) / (tiles * outer);
+    int64_t max_splits = (len + 63) / 64;  // at least 64 rows per split
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    if (splits > 65535) splits = 65535;
+  }
+  int64_t rps = (len + splits - 1) / splits;
+  splits = (len + rps - 1) / rps;
+  if (outer > 65535) {
+    // fold very large outer extents through repeated launches
+    for (int64_t o0 = 0; o0 < outer; o0 += 65535) {
+      int64_t oc = outer - o0 < 65535 ? outer - o0 : 65535;
+      rt_status st = reduce_float<KIND>(ctx, x + o0 * len * inner, oc, len, inner, out + o0 * inner, scale);
+      if (st != RT_OK) return st;
+    }
+    return RT_OK;
+  }
+  dim3 grid((unsigned)tiles, (unsigned)splits, (unsigned)outer), block(32, 8);
+  RtScratch part(ctx);
+  float* dst = out;
+  if (splits > 1) {
+    rt_status st = part.alloc(sizeof(float) * outer * splits * inner);
+    if (st != RT_OK) return st;
+    dst = part.as<float>();
+  }
+  float sc = splits > 1 ? 1.f : scale;
+  if (vec) col_reduce<KIND, true><<<grid, block, 0, ctx->stream>>>(x, dst, len, inner, splits, rps, sc);
+  else col_reduce<KIND, false><<<grid, block, 0, ctx->stream>>>(x, dst, len, inner, splits, rps, sc);
+  RT_LAUNCHED(ctx);
+  if (splits > 1) return reduce_float<KIND>(ctx, dst, outer, splits, inner, out, scale);
+  return RT_OK;
+}
+
+// ---- row-resident softmax-family kernels (inner == 1) ---------------------------------
+enum RowMode { ROW_LSE_FWD = 0, ROW_LSE_BWD = 1, ROW_LSM_FWD = 2, ROW_LSM_BWD = 3 };
+
+template <int G>
+__device__ __forceinline__ float group_reduce_max(float v, float* smem) {
+  if (G == 32) return warp_reduce<RT_RED_MAX>(v);
+  return block_reduce<RT_RED_MAX>(v, smem);
+}
+template <int G>
+__device__ __forceinline__ float group_reduce_sum(float v, float* smem) {
+  if (G == 32) return warp_reduce<RT_RED_SUM>(v);
+  return block_reduce<RT_RED_SUM>(v, smem);
+}
+
+// G threads cooperate on one row (G = 32: a warp, several rows per block; G = 256: the block).
+// The math follows the reference CPU code: max first, then sum of exp(x - max)
+// (src/ops/cpu_ops.rs:462-482, 564-597).  After the first pass the row is re-read from L1/L2.
+template <int MODE, int G>
+__global__ void __launch_bounds__(kThreads) row_softmax_kernel(const float* __restrict__ x, const float* __restrict__ g,
+                                                                float* __restrict__ out, int64_t rows, int64_t len) {
+  __shared__ float smem[kThreads / 32];
+  int lane = threadIdx.x % G;
+  int64_t group = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+  int64_t ngroups = ((int64_t)gridDim.x * blockDim.x) / G;
+  // every thread of a block must take the same number of trips (block_reduce syncs)
+  int64_t trips = (rows + ngroups - 1) / ngroups;
+  for (int64_t t = 0; t < trips; ++t) {
+    int64_t r = group + t * ngroups;
+    bool live = r < rows;
+    const float* p = x + (live ? r : 0) * len;
+    float m = -INFINITY;
+    if (live)
+      for (int64_t k = lane; k < len; k += G) m = fmaxf(m, __ldg(p + k));
+    m = group_reduce_max<G>(m, smem);
+    float s = 0.f;
+    if (live)
+      for (int64_t k = lane; k < len; k += G) s += expf(p[k] - m);
+    s = group_reduce_sum<G>(s, smem);
+    if (MODE == ROW_LSE_FWD) {
+      if (live && lane == 0) out[r] = m + logf(s);
+    } else if (MODE == ROW_LSE_BWD) {
+      if (live) {
+        float lse = m + logf(s), gr = g[r];
+        float* o = out + r * len;
+        for (int64_t k = lane; k < len; k += G) o[k] = gr * expf(p[k] - lse);
+      }
+    } else if (MODE == ROW_LSM_FWD) {
+      if (live) {
+        float ls = logf(s);
+        float* o = out + r * len;
+        for (int64_t k = lane; k < len; k += G) o[k] = (p[k] - m) - ls;
+      }
+    } else {  // ROW_LSM_BWD: dx = g - exp(y) * sum(g)
+      const float* gp = g + (live ? r : 0) * len;
+      float sg = 0.f;
+      if (live)
+        for (int64_t k = lane; k < len; k += G) sg += __ldg(gp + k);
+      sg = group_reduce_sum<G>(sg, smem);
+      if (live) {
+        float ls = logf(s);
+        float* o = out + r * len;
+        for (int64_t k = lane; k < len; k += G) o[k] = gp[k] - expf((p[k] - m) - ls) * sg;
+      }
+    }
+  }
+}
+
+// Generic strided versions (any inner): one thread per output slice (o, i).
+template <int MODE>
+__global__ void __launch_bounds__(kThreads) slice_softmax_kernel(const float* __restrict__ x, const float* __restrict__ g,
+                                                                  float* __restrict__ out, int64_t outer, int64_t len,
+                                                                  int64_t inner) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; s < outer * inner; s += stride) {
+    int64_t o = s / inner, i = s % inner;
+    const float* p = x + o * len * inner + i;
+    float m = -INFINITY;
+    for (int64_t k = 0; k < len; ++k) m = fmaxf(m, p[k * inner]);
+    float sum = 0.f;
+    for (int64_t k = 0; k < len; ++k) sum += expf(p[k * inner] - m);
+    if (MODE == ROW_LSE_FWD) {
+      out[s] = m + logf(sum);
+    } else if (MODE == ROW_LSE_BWD) {
+      float lse = m + logf(sum), gr = g[s];
+      float* q = out + o * len * inner + i;
+      for (int64_t k = 0; k < len; ++k) q[k * inner] = gr * expf(p[k * inner] - lse);
+    } else if (MODE == ROW_LSM_FWD) {
+      float ls = logf(sum);
+      float* q = out + o * len * inner + i;
+      for (int64_t k = 0; k < len; ++k) q[k * inner] = (p[k * inner] - m) - ls;
+    } else {
+      const float* gp = g + o * len * inner + i;
+      float sg = 0.f;
+      for (int64_t k = 0; k < len; ++k) sg += gp[k * inner];
+      float ls = logf(sum);
+      float* q = out + o * len * inner + i;
+      for (int64_t k = 0; k < len; ++k) q[k * inner] = gp[k * inner] - expf((p[k * inner] - m) - ls) * sg;
+    }
+  }
+}
+
+template <int MODE>
+rt_status launch_softmax_family(rt_ctx* ctx, const float* x, const float* g, float* out, int64_t outer, int64_t len,
+                                int64_t inner) {
+  if (outer * inner == 0) return RT_OK;
+  if (inner == 1) {
+    if (len <= 1024) {
+      int grid = rt_grid_for(ctx, outer, kThreads / 32);
+      row_softmax_kernel<MODE, 32><<<grid, kThreads, 0, ctx->stream>>>(x, g, out, outer, len);
+    } else {
+      int grid = rt_grid_for(ctx, outer, 1);
+      row_softmax_kernel<MODE, kThreads><<<grid, kThreads, 0, ctx->stream>>>(x, g, out, outer, len);
+    }
+  } else {
+    int grid = rt_grid_for(ctx, outer * inner, kThreads);
+    slice_softmax_kernel<MODE><<<grid, kThreads, 0, ctx->stream>>>(x, g, out, outer, len, inner);
+  }
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+// argmax / argmin: one thread per slice, sequential scan (first extremum wins, NaN never wins).
+template <bool IS_MAX>
+__global__ void __launch_bounds__(kThreads) arg_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t outer,
+                                                        int64_t len, int64_t inner) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; s < outer * inner; s += stride) {
+    int64_t o = s / inner, i = s % inner;
+    const float* p = x + o * len * inner + i;
+    float best = IS_MAX ? -INFINITY : INFINITY;
+    int64_t bi = 0;
+    for (int64_t k = 0; k < len; ++k) {
+      float v = p[k * inner];
+      if (IS_MAX ? (v > best) : (v < best)) {
+        best = v;
+        bi = k;
+      }
+    }
+    out[s] = (float)bi;
+  }
+}
+
+// dx[o,k,i] = g[o,i] * scale
+__global__ void __launch_bounds__(kThreads) expand_axis_kernel(const float* __restrict__ g, float* __restrict__ dx,
+                                                                int64_t n, int64_t len, int64_t inner, float scale, bool divide) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t li = len * inner;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += stride) {
+    int64_t o = idx / li, i = idx % inner;
+    float v = __ldg(g + o * inner + i);
+    dx[idx] = divide ? v / scale : v;
+  }
+}
+
+// dx[:] = g[0] (/ scale): gradient of a global sum / mean
+__global__ void __launch_bounds__(kThreads) fill_from_scalar_kernel(const float* __restrict__ g, float* __restrict__ dx,
+                                                                     int64_t n, float scale, bool divide) {
+  float v = divide ? g[0] / scale : g[0];
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (rt_aligned16(dx)) {
+    int64_t n4 = n >> 2;
+    float4 v4 = make_float4(v, v, v, v);
+    for (int64_t i = tid; i < n4; i += stride) reinterpret_cast<float4*>(dx)[i] = v4;
+    for (int64_t i = (n4 << 2) + tid; i < n; i += stride) dx[i] = v;
+  } else {
+    for (int64_t i = tid; i < n; i += stride) dx[i] = v;
+  }
+}
+
+// ties[o,i] = number of k with |x - ext| < 1e-9   (equal(), src/backend/cpu.rs:715)
+__global__ void __launch_bounds__(kThreads) count_ties_kernel(const float* __restrict__ x, const float* __restrict__ ext,
+                                                               float* __restrict__ ties, int64_t outer, int64_t len,
+                                                               int64_t inner) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; s < outer * inner; s += stride) {
+    int64_t o = s / inner, i = s % inner;
+    const float* p = x + o * len * inner + i;
+    float e = ext[s], c = 0.f;
+    for (int64_t k = 0; k < len; ++k) c += fabsf(p[k * inner] - e) < 1e-9f ? 1.f : 0.f;
+    ties[s] = c;
+  }
+}
+
+// mode 0 (max/min): dx = (g * mask) / (ties + 1e-9);  mode 1 (prod): dx = (g * prod) / (x + 1e-10)
+__global__ void __launch_bounds__(kThreads) reduce_bwd_final_kernel(const float* __restrict__ x, const float* __restrict__ g,
+                                                                     const float* __restrict__ r0, const float* __restrict__ r1,
+                                                                     float* __restrict__ dx, int64_t n, int64_t len,
+                                                                     int64_t inner, int mode) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t li = len * inner;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += stride) {
+    int64_t s = (idx / li) * inner + idx % inner;
+    float xv = x[idx], gv = g[s];
+    if (mode == 0) {
+      float mask = fabsf(xv - r0[s]) < 1e-9f ? 1.f : 0.f;
+      dx[idx] = (gv * mask) / (r1[s] + 1e-9f);
+    } else {
+      dx[idx] = (gv * r0[s]) / (xv + 1e-10f);
+    }
+  }
+}
+
+}  // namespace
+
+rt_status rt_sum_axis_internal(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out,
+                               float scale) {
+  return reduce_float<RT_RED_SUM>(ctx, x, outer, len, inner, out, scale);
+}
+
+extern "C" {
+
+rt_status rt_reduce(rt_ctx* ctx, int kind, const float* x, int64_t outer, int64_t len, int64_t inner, float* out) {
+  RT_CHECK_CTX(ctx);
+  if (kind < 0 || kind >= RT_RED_COUNT) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_reduce: unknown kind %d", kind);
+  if (outer < 0 || len < 0 || inner < 0) RT_FAIL(ctx, RT_ERR_INVALID_INDEX, "rt_reduce: negative extent");
+  if (outer * inner == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, out);
+  if (len > 0) RT_CHECK_PTR(ctx, x);
+  switch (kind) {
+    case RT_RED_SUM: return reduce_float<RT_RED_SUM>(ctx, x, outer, len, inner, out, 1.f);
+    case RT_RED_MEAN: {
+      if (len == 0) RT_FAIL(ctx, RT_ERR_EMPTY_TENSOR, "mean over an empty axis");
+      // the CPU backend divides the sum by n (ndarray mean_axis): scale by a reciprocal would round differently
+      rt_status st = reduce_float<RT_RED_SUM>(ctx, x, outer, len, inner, out, 1.f);
+      if (st != RT_OK) return st;
+      return rt_unary(ctx, RT_DIV_SCALAR, out, out, outer * inner, (float)len, 0.f);
+    }
+    case RT_RED_MAX: return reduce_float<RT_RED_MAX>(ctx, x, outer, len, inner, out, 1.f);
+    case RT_RED_MIN: return reduce_float<RT_RED_MIN>(ctx, x, outer, len, inner, out, 1.f);
+    case RT_RED_PROD: return reduce_float<RT_RED_PROD>(ctx, x, outer, len, inner, out, 1.f);
+    case RT_RED_LOGSUMEXP: return launch_softmax_family<ROW_LSE_FWD>(ctx, x, nullptr, out, outer, len, inner);
+    case RT_RED_ARGMAX:
+      arg_kernel<true><<<rt_grid_for(ctx, outer * inner, kThreads), kThreads, 0, ctx->stream>>>(x, out, outer, len, inner);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    case RT_RED_ARGMIN:
+      arg_kernel<false><<<rt_grid_for(ctx, outer * inner, kThreads), kThreads, 0, ctx->stream>>>(x, out, outer, len, inner);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+  }
+  return RT_ERR_INTERNAL;
+}
+
+rt_status rt_reduce_backward(rt_ctx* ctx, int kind, const float* x, const float* g, int64_t outer, int64_t len,
+                             int64_t inner, float* dx) {
+  RT_CHECK_CTX(ctx);
+  if (outer < 0 || len < 0 || inner < 0) RT_FAIL(ctx, RT_ERR_INVALID_INDEX, "rt_reduce_backward: negative extent");
+  int64_t n = outer * len * inner;
+  if (n == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, g);
+  RT_CHECK_PTR(ctx, dx);
+  int grid = rt_grid_for(ctx, n, kThreads * 2);
+  switch (kind) {
+    case RT_RED_SUM:
+      if (outer * inner == 1) fill_from_scalar_kernel<<<rt_grid_for(ctx, (n + 3) / 4, kThreads * 2), kThreads, 0, ctx->stream>>>(g, dx, n, 1.f, false);
+      else expand_axis_kernel<<<grid, kThreads, 0, ctx->stream>>>(g, dx, n, len, inner, 1.f, false);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    case RT_RED_MEAN:  // div_scalar(broadcast(g), len)  (src/ops/cpu_backward.rs:716,764)
+      if (outer * inner == 1) fill_from_scalar_kernel<<<rt_grid_for(ctx, (n + 3) / 4, kThreads * 2), kThreads, 0, ctx->stream>>>(g, dx, n, (float)len, true);
+      else expand_axis_kernel<<<grid, kThreads, 0, ctx->stream>>>(g, dx, n, len, inner, (float)len, true);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    case RT_RED_MAX:
+    case RT_RED_MIN: {
+      RT_CHECK_PTR(ctx, x);
+      RtScratch ext(ctx), ties(ctx);
+      rt_status st = ext.alloc(sizeof(float) * outer * inner);
+      if (st == RT_OK) st = ties.alloc(sizeof(float) * outer * inner);
+      if (st != RT_OK) return st;
+      st = rt_reduce(ctx, kind, x, outer, len, inner, ext.as<float>());
+      if (st != RT_OK) return st;
+      count_ties_kernel<<<rt_grid_for(ctx, outer * inner, kThreads), kThreads, 0, ctx->stream>>>(x, ext.as<float>(), ties.as<float>(), outer, len, inner);
+      RT_LAUNCHED(ctx);
+      reduce_bwd_final_kernel<<<grid, kThreads, 0, ctx->stream>>>(x, g, ext.as<float>(), ties.as<float>(), dx, n, len, inner, 0);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
+    case RT_RED_PROD: {
+      RT_CHECK_PTR(ctx, x);
+      RtScratch pr(ctx);
+      rt_status st = pr.alloc(sizeof(float) * outer * inner);
+      if (st != RT_OK) return st;
+      st = rt_reduce(ctx, RT_RED_PROD, x, outer, len, inner, pr.as<float>());
+      if (st != RT_OK) return st;
+      reduce_bwd_final_kernel<<<grid, kThreads, 0, ctx->stream>>>(x, g, pr.as<float>(), nullptr, dx, n, len, inner, 1);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
+    case RT_RED_LOGSUMEXP:
+      RT_CHECK_PTR(ctx, x);
+      return launch_softmax_family<ROW_LSE_BWD>(ctx, x, g, dx, outer, len, inner);
+    default:
+      RT_FAIL(ctx, RT_ERR_UNIMPLEMENTED, "rt_reduce_backward: kind %d has no gradient", kind);
+  }
+}
+
+rt_status rt_sum_all_host(rt_ctx* ctx, const float* x, int64_t n, float* host_out) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, host_out);
+  if (n == 0) {
+    *host_out = 0.f;
+    return RT_OK;
+  }
+  RtScratch s(ctx);
+  rt_status st = s.alloc(sizeof(float));
+  if (st != RT_OK) return st;
+  st = reduce_float<RT_RED_SUM>(ctx, x, 1, n, 1, s.as<float>(), 1.f);
+  if (st != RT_OK) return st;
+  return rt_memcpy_d2h(ctx, host_out, s.ptr, sizeof(float));
+}
+
+rt_status rt_log_softmax(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* y) {
+  RT_CHECK_CTX(ctx);
+  if (outer * len * inner == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, x);
+  RT_CHECK_PTR(ctx, y);
+  return launch_softmax_family<ROW_LSM_FWD>(ctx, x, nullptr, y, outer, len, inner);
+}
+
+rt_status rt_log_softmax_backward(rt_ctx* ctx, const float* x, const float* g, int64_t outer, int64_t len, int64_t inner,
+                                  float* dx) {
+  RT_CHECK_CTX(ctx);
+  if (outer * len * inner == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, x);
+  RT_CHECK_PTR(ctx, g);
+  RT_CHECK_PTR(ctx, dx);
+  return launch_softmax_family<ROW_LSM_BWD>(ctx, x, g, dx, outer, len, inner);
+}
+
+}  // extern "C"

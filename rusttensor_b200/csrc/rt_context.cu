@@ -1,0 +1,367 @@
+// Context, caching allocator, copies, CUDA-graph capture, timers and the NCCL
+// gradient all-reduce of librt_b200.so.
+#include <dlfcn.h>
+
+#include <cstring>
+
+#include "rt_internal.cuh"
+
+extern "C" {
+
+int rt_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+rt_status rt_ctx_create(int device, rt_ctx** out) {
+  if (!out) return RT_ERR_INVALID_OPERATION;
+  *out = nullptr;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0) {
+    cudaGetLastError();
+    return RT_ERR_CUDA;  // no CUDA device: this library has no CPU fallback
+  }
+  if (device < 0 || device >= n) return RT_ERR_INVALID_INDEX;
+  rt_ctx* ctx = new rt_ctx();
+  ctx->device = device;
+  if (cudaSetDevice(device) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+    delete ctx;
+    return RT_ERR_CUDA;
+  }
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
+  cudaEventCreate(&ctx->ev_start);
+  cudaEventCreate(&ctx->ev_stop);
+  *out = ctx;
+  return RT_OK;
+}
+
+rt_status rt_ctx_destroy(rt_ctx* ctx) {
+  RT_CHECK_CTX(ctx);
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  rt_dp_finalize(ctx);
+  for (auto& kv : ctx->free_blocks) cudaFree(kv.second);
+  for (auto& kv : ctx->capture_free) cudaFree(kv.second);
+  for (auto& kv : ctx->live_blocks) cudaFree(kv.first);
+  if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
+  if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return RT_OK;
+}
+
+const char* rt_last_error(rt_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+static size_t round_size(size_t bytes) {
+  if (bytes == 0) bytes = 1;
+  if (bytes <= (1u << 20)) return (bytes + 511) & ~size_t(511);
+  const size_t two_mb = size_t(2) << 20;
+  return (bytes + two_mb - 1) / two_mb * two_mb;
+}
+
+rt_status rt_malloc(rt_ctx* ctx, size_t bytes, void** out) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, out);
+  size_t sz = round_size(bytes);
+  if (ctx->capturing) {
+    auto cit = ctx->capture_free.lower_bound(sz);
+    if (cit != ctx->capture_free.end() && cit->first <= sz + sz / 4) {
+      *out = cit->second;
+      ctx->live_blocks[cit->second] = cit->first;
+      ctx->bytes_in_use += (int64_t)cit->first;
+      ctx->capture_free.erase(cit);
+      return RT_OK;
+    }
+  }
+  auto it = ctx->free_blocks.lower_bound(sz);
+  if (it != ctx->free_blocks.end() && it->first <= sz + sz / 4) {
+    *out = it->second;
+    ctx->live_blocks[it->second] = it->first;
+    ctx->bytes_in_use += (int64_t)it->first;
+    ctx->free_blocks.erase(it);
+    return RT_OK;
+  }
+  void* p = nullptr;
+  cudaSetDevice(ctx->device);
+  cudaError_t e = cudaMalloc(&p, sz);
+  if (e == cudaErrorMemoryAllocation) {
+    // Give cached blocks back to the driver and retry once.
+    cudaGetLastError();
+    if (!ctx->capturing) {
+      cudaStreamSynchronize(ctx->stream);
+      for (auto& kv : ctx->free_blocks) {
+        cudaFree(kv.second);
+        ctx->bytes_reserved -= (int64_t)kv.first;
+      }
+      ctx->free_blocks.clear();
+      e = cudaMalloc(&p, sz);
+    }
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    RT_FAIL(ctx, e == cudaErrorMemoryAllocation ? RT_ERR_OOM : RT_ERR_CUDA, "cudaMalloc(%zu) failed: %s", sz,
+            cudaGetErrorString(e));
+  }
+  ctx->n_device_allocs++;
+  ctx->bytes_reserved += (int64_t)sz;
+  ctx->bytes_in_use += (int64_t)sz;
+  ctx->live_blocks[p] = sz;
+  *out = p;
+  return RT_OK;
+}
+
+rt_status rt_free(rt_ctx* ctx, void* ptr) {
+  RT_CHECK_CTX(ctx);
+  if (!ptr) return RT_OK;
+  auto it = ctx->live_blocks.find(ptr);
+  if (it == ctx->live_blocks.end()) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_free: pointer %p is not a live block", ptr);
+  ctx->bytes_in_use -= (int64_t)it->second;
+  if (ctx->capturing) ctx->capture_free.emplace(it->second, ptr);
+  else ctx->free_blocks.emplace(it->second, ptr);
+  ctx->live_blocks.erase(it);
+  return RT_OK;
+}
+
+rt_status rt_mem_stats(rt_ctx* ctx, int64_t* reserved, int64_t* in_use, int64_t* n_allocs) {
+  RT_CHECK_CTX(ctx);
+  if (reserved) *reserved = ctx->bytes_reserved;
+  if (in_use) *in_use = ctx->bytes_in_use;
+  if (n_allocs) *n_allocs = ctx->n_device_allocs;
+  return RT_OK;
+}
+
+rt_status rt_kernel_launch_count(rt_ctx* ctx, int64_t* launches) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, launches);
+  *launches = ctx->launches;
+  return RT_OK;
+}
+
+rt_status rt_memcpy_h2d(rt_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  RT_CHECK_CTX(ctx);
+  if (bytes == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, dst);
+  RT_CHECK_PTR(ctx, src);
+  RT_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  // The source may be pageable and freed by the caller right after the call.
+  RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return RT_OK;
+}
+
+rt_status rt_memcpy_d2h(rt_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  RT_CHECK_CTX(ctx);
+  if (bytes == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, dst);
+  RT_CHECK_PTR(ctx, src);
+  RT_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return RT_OK;
+}
+
+rt_status rt_memcpy_h2d_async(rt_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  RT_CHECK_CTX(ctx);
+  if (bytes == 0) return RT_OK;
+  RT_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return RT_OK;
+}
+
+rt_status rt_memcpy_d2h_async(rt_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  RT_CHECK_CTX(ctx);
+  if (bytes == 0) return RT_OK;
+  RT_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return RT_OK;
+}
+
+rt_status rt_memcpy_d2d(rt_ctx* ctx, void* dst, const void* src, size_t bytes) {
+  RT_CHECK_CTX(ctx);
+  if (bytes == 0) return RT_OK;
+  RT_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return RT_OK;
+}
+
+rt_status rt_host_alloc(rt_ctx* ctx, size_t bytes, void** out) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, out);
+  RT_CUDA(ctx, cudaHostAlloc(out, bytes ? bytes : 1, cudaHostAllocDefault));
+  return RT_OK;
+}
+
+rt_status rt_host_free(rt_ctx* ctx, void* ptr) {
+  RT_CHECK_CTX(ctx);
+  if (ptr) RT_CUDA(ctx, cudaFreeHost(ptr));
+  return RT_OK;
+}
+
+rt_status rt_sync(rt_ctx* ctx) {
+  RT_CHECK_CTX(ctx);
+  RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return RT_OK;
+}
+
+void* rt_stream(rt_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+// ---- CUDA graphs -----------------------------------------------------------------
+rt_status rt_graph_begin(rt_ctx* ctx) {
+  RT_CHECK_CTX(ctx);
+  if (ctx->capturing) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_graph_begin: already capturing");
+  // Relaxed mode: the pool may still call cudaMalloc for a size it has not seen.
+  RT_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+  ctx->capturing = true;
+  return RT_OK;
+}
+
+rt_status rt_graph_end(rt_ctx* ctx, rt_graph** out) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, out);
+  if (!ctx->capturing) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_graph_end: not capturing");
+  ctx->capturing = false;
+  rt_graph* g = new rt_graph();
+  for (auto& kv : ctx->capture_free) g->retired.emplace_back(kv.first, kv.second);
+  ctx->capture_free.clear();
+  cudaError_t e = cudaStreamEndCapture(ctx->stream, &g->graph);
+  if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    if (g->graph) cudaGraphDestroy(g->graph);
+    for (auto& kv : g->retired) ctx->free_blocks.emplace(kv.first, kv.second);
+    delete g;
+    RT_FAIL(ctx, RT_ERR_CUDA, "graph capture/instantiate failed: %s", cudaGetErrorString(e));
+  }
+  *out = g;
+  return RT_OK;
+}
+
+rt_status rt_graph_launch(rt_ctx* ctx, rt_graph* g) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, g);
+  RT_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+  return RT_OK;
+}
+
+rt_status rt_graph_num_nodes(rt_ctx* ctx, rt_graph* g, int64_t* n) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, g);
+  size_t cnt = 0;
+  RT_CUDA(ctx, cudaGraphGetNodes(g->graph, nullptr, &cnt));
+  *n = (int64_t)cnt;
+  return RT_OK;
+}
+
+rt_status rt_graph_destroy(rt_ctx* ctx, rt_graph* g) {
+  RT_CHECK_CTX(ctx);
+  if (!g) return RT_OK;
+  cudaStreamSynchronize(ctx->stream);
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  if (g->graph) cudaGraphDestroy(g->graph);
+  for (auto& kv : g->retired) ctx->free_blocks.emplace(kv.first, kv.second);
+  delete g;
+  return RT_OK;
+}
+
+// ---- timers ----------------------------------------------------------------------
+rt_status rt_timer_start(rt_ctx* ctx) {
+  RT_CHECK_CTX(ctx);
+  RT_CUDA(ctx, cudaEventRecord(ctx->ev_start, ctx->stream));
+  return RT_OK;
+}
+
+rt_status rt_timer_stop(rt_ctx* ctx, float* ms) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, ms);
+  RT_CUDA(ctx, cudaEventRecord(ctx->ev_stop, ctx->stream));
+  RT_CUDA(ctx, cudaEventSynchronize(ctx->ev_stop));
+  RT_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev_start, ctx->ev_stop));
+  return RT_OK;
+}
+
+// ---- NCCL, resolved at run time so that the library loads on machines without it ---
+namespace {
+struct NcclId {
+  char internal[128];
+};
+struct NcclApi {
+  void* handle = nullptr;
+  int (*GetUniqueId)(NcclId*) = nullptr;
+  int (*CommInitRank)(void**, int, NcclId, int) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*CommDestroy)(void*) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  bool ok = false;
+};
+NcclApi& nccl() {
+  static NcclApi api;
+  if (!api.handle) {
+    api.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!api.handle) api.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (api.handle) {
+      api.GetUniqueId = (int (*)(NcclId*))dlsym(api.handle, "ncclGetUniqueId");
+      api.CommInitRank = (int (*)(void**, int, NcclId, int))dlsym(api.handle, "ncclCommInitRank");
+      api.AllReduce = (int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t))dlsym(api.handle, "ncclAllReduce");
+      api.CommDestroy = (int (*)(void*))dlsym(api.handle, "ncclCommDestroy");
+      api.GetErrorString = (const char* (*)(int))dlsym(api.handle, "ncclGetErrorString");
+      api.ok = api.GetUniqueId && api.CommInitRank && api.AllReduce && api.CommDestroy;
+    }
+  }
+  return api;
+}
+}  // namespace
+
+rt_status rt_dp_unique_id(uint8_t id[RT_DP_ID_BYTES]) {
+  if (!id) return RT_ERR_INVALID_OPERATION;
+  NcclApi& n = nccl();
+  if (!n.ok) return RT_ERR_NCCL;
+  NcclId nid;
+  if (n.GetUniqueId(&nid) != 0) return RT_ERR_NCCL;
+  static_assert(sizeof(NcclId) == RT_DP_ID_BYTES, "id size");
+  memcpy(id, &nid, sizeof(nid));
+  return RT_OK;
+}
+
+rt_status rt_dp_init(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID_BYTES]) {
+  RT_CHECK_CTX(ctx);
+  if (world < 1 || rank < 0 || rank >= world) RT_FAIL(ctx, RT_ERR_INVALID_INDEX, "rt_dp_init: rank %d of %d", rank, world);
+  ctx->dp_rank = rank;
+  ctx->dp_world = world;
+  if (world == 1) return RT_OK;
+  RT_CHECK_PTR(ctx, id);
+  NcclApi& n = nccl();
+  if (!n.ok) RT_FAIL(ctx, RT_ERR_NCCL, "libnccl.so.2 could not be loaded");
+  NcclId nid;
+  memcpy(&nid, id, sizeof(nid));
+  RT_CUDA(ctx, cudaSetDevice(ctx->device));
+  int rc = n.CommInitRank(&ctx->nccl_comm, world, nid, rank);
+  if (rc != 0) RT_FAIL(ctx, RT_ERR_NCCL, "ncclCommInitRank failed: %s", n.GetErrorString ? n.GetErrorString(rc) : "?");
+  return RT_OK;
+}
+
+rt_status rt_dp_allreduce_sum(rt_ctx* ctx, float* buf, int64_t count) {
+  RT_CHECK_CTX(ctx);
+  if (ctx->dp_world == 1 || count == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, buf);
+  if (!ctx->nccl_comm) RT_FAIL(ctx, RT_ERR_NCCL, "rt_dp_allreduce_sum: rt_dp_init was not called");
+  NcclApi& n = nccl();
+  const int nccl_float32 = 7, nccl_sum = 0;
+  int rc = n.AllReduce(buf, buf, (size_t)count, nccl_float32, nccl_sum, ctx->nccl_comm, ctx->stream);
+  if (rc != 0) RT_FAIL(ctx, RT_ERR_NCCL, "ncclAllReduce failed: %s", n.GetErrorString ? n.GetErrorString(rc) : "?");
+  return RT_OK;
+}
+
+rt_status rt_dp_finalize(rt_ctx* ctx) {
+  RT_CHECK_CTX(ctx);
+  if (ctx->nccl_comm) {
+    nccl().CommDestroy(ctx->nccl_comm);
+    ctx->nccl_comm = nullptr;
+  }
+  ctx->dp_world = 1;
+  ctx->dp_rank = 0;
+  return RT_OK;
+}
+
+}  // extern "C"

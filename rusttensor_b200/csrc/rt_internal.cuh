@@ -1,0 +1,100 @@
+// Internal declarations shared by the kernel translation units of librt_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/rt_b200.h"
+
+struct rt_graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  // Blocks that were released while the graph was being captured.  The graph's kernels
+  // still write them on every replay, so they stay out of the pool until the graph is
+  // destroyed.
+  std::vector<std::pair<size_t, void*>> retired;
+};
+
+struct rt_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  int sm_count = 148;
+  std::string last_error;
+  // Caching allocator: freed blocks are kept per rounded size and handed out again.
+  // All work is ordered on one stream, so reuse needs no extra synchronisation.
+  std::multimap<size_t, void*> free_blocks;
+  std::map<void*, size_t> live_blocks;
+  int64_t bytes_reserved = 0, bytes_in_use = 0, n_device_allocs = 0;
+  int64_t launches = 0;
+  bool capturing = false;
+  std::multimap<size_t, void*> capture_free;  // released during capture: reusable only inside it
+  cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+  // NCCL (loaded at run time, see rt_dp.cu)
+  void* nccl_comm = nullptr;
+  int dp_rank = 0, dp_world = 1;
+};
+
+#define RT_FAIL(ctx, code, ...)                         \
+  do {                                                  \
+    char _buf[512];                                     \
+    snprintf(_buf, sizeof(_buf), __VA_ARGS__);          \
+    if (ctx) (ctx)->last_error = _buf;                  \
+    return (code);                                      \
+  } while (0)
+
+#define RT_CUDA(ctx, expr)                                                                     \
+  do {                                                                                         \
+    cudaError_t _e = (expr);                                                                   \
+    if (_e != cudaSuccess)                                                                     \
+      RT_FAIL(ctx, _e == cudaErrorMemoryAllocation ? RT_ERR_OOM : RT_ERR_CUDA, "%s failed: %s", #expr, \
+              cudaGetErrorString(_e));                                                         \
+  } while (0)
+
+#define RT_CHECK_CTX(ctx) \
+  do {                    \
+    if (!(ctx)) return RT_ERR_INVALID_OPERATION; \
+  } while (0)
+
+#define RT_CHECK_PTR(ctx, p)                                                   \
+  do {                                                                         \
+    if (!(p)) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "%s: null pointer %s", __func__, #p); \
+  } while (0)
+
+// Records a kernel launch and converts a launch error into a status.
+#define RT_LAUNCHED(ctx)                                                                   \
+  do {                                                                                     \
+    (ctx)->launches++;                                                                     \
+    cudaError_t _e = cudaPeekAtLastError();                                                \
+    if (_e != cudaSuccess) {                                                               \
+      cudaGetLastError();                                                                  \
+      RT_FAIL(ctx, RT_ERR_CUDA, "%s: kernel launch failed: %s", __func__, cudaGetErrorString(_e)); \
+    }                                                                                      \
+  } while (0)
+
+// Scratch memory from the context pool, released when the guard goes out of scope
+// (stream-ordered, so the block may be reused by the next call).
+struct RtScratch {
+  rt_ctx* ctx;
+  void* ptr = nullptr;
+  explicit RtScratch(rt_ctx* c) : ctx(c) {}
+  rt_status alloc(size_t bytes) { return rt_malloc(ctx, bytes, &ptr); }
+  ~RtScratch() {
+    if (ptr) rt_free(ctx, ptr);
+  }
+  template <class T>
+  T* as() { return static_cast<T*>(ptr); }
+};
+
+static inline int rt_grid_for(rt_ctx* ctx, int64_t work_items, int per_block, int max_waves = 8) {
+  int64_t blocks = (work_items + per_block - 1) / per_block;
+  int64_t cap = (int64_t)ctx->sm_count * max_waves;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+static __host__ __device__ inline bool rt_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

@@ -1,0 +1,120 @@
+"""Data-parallel training step on the CUDA backend (one process per GPU).
+
+forward + backward are replayed from a CUDA graph, the flat gradient buffer is summed
+with one NCCL all-reduce, and one fused multi-tensor kernel applies the optimizer
+(with the 1/world scale and the optional gradient clip folded in).
+"""
+import ctypes as C
+
+import numpy as np
+
+from .frontend import Tensor, EngineError, _i64, _f64
+
+_f32p = C.POINTER(C.c_float)
+
+
+class DataParallelTrainer:
+    def __init__(self, config, dims, rank=0, world=1, nccl_id=None, device=None):
+        from . import engine
+
+        self.engine = engine(device)
+        self.host = self.engine.lib
+        self.rank, self.world = rank, world
+        idbuf = (C.c_uint8 * 128)(*(nccl_id if nccl_id is not None else [0] * 128))
+        out = C.c_int64(0)
+        self._call("dp_create", C.c_int(config), _i64(dims), C.c_int(len(dims)), C.c_int(rank), C.c_int(world), idbuf,
+                   C.byref(out))
+        self.handle = out.value
+        n = C.c_int(0)
+        self._call("dp_num_params", C.c_int64(self.handle), C.byref(n))
+        self.params = [self._tensor("dp_param", i) for i in range(n.value)]
+        self.inputs = []
+        i = 0
+        while True:
+            try:
+                self.inputs.append(self._tensor("dp_input", i))
+            except EngineError:
+                break
+            i += 1
+        self._pinned = []
+        for i, t in enumerate(self.inputs):
+            p = _f32p()
+            self._call("dp_pinned_input", C.c_int64(self.handle), C.c_int(i), C.byref(p))
+            self._pinned.append(np.ctypeslib.as_array(p, shape=t.shape))
+
+    def _call(self, name, *args):
+        self.engine._call(name, *args)
+
+    def _tensor(self, fn, i, *extra):
+        h = C.c_int64(0)
+        self._call(fn, C.c_int64(self.handle), *extra, C.c_int(i), C.byref(h))
+        return Tensor(self.engine, h.value)
+
+    def __del__(self):
+        try:
+            self._call("dp_free", C.c_int64(self.handle))
+        except Exception:
+            pass
+
+    @staticmethod
+    def unique_id():
+        """A fresh NCCL id (rank 0 creates it and sends the 128 bytes to every rank)."""
+        from . import load_library
+
+        buf = (C.c_uint8 * 128)()
+        rc = load_library().rt_dp_unique_id(buf)
+        if rc != 0:
+            raise RuntimeError(f"rt_dp_unique_id failed with status {rc}")
+        return bytes(buf)
+
+    def set_hyper(self, *hp):
+        self._call("dp_set_hyper", C.c_int64(self.handle), _f64(hp), C.c_int(len(hp)))
+
+    def state(self, which, i):
+        return self._tensor("dp_state", i, C.c_int(which))
+
+    def pinned_input(self, i):
+        """numpy view of the pinned host staging buffer of input ``i``."""
+        return self._pinned[i]
+
+    def _ptrs(self, arrays):
+        keep = [np.ascontiguousarray(a, dtype=np.float32) for a in arrays]
+        arr = (_f32p * len(keep))(*[a.ctypes.data_as(_f32p) for a in keep])
+        return keep, arr
+
+    def step_eager(self, arrays):
+        keep, arr = self._ptrs(arrays)
+        loss = C.c_float(0)
+        self._call("dp_step_eager", C.c_int64(self.handle), arr, C.c_int(len(keep)), C.byref(loss))
+        return loss.value
+
+    def capture(self):
+        self._call("dp_capture", C.c_int64(self.handle))
+
+    def step(self, arrays=None, pinned=False):
+        """Enqueues one step.  ``arrays``: host inputs (copied through pinned staging), or None to
+        reuse the inputs resident on the device; ``pinned=True`` takes the data already written
+        into ``pinned_input(i)``."""
+        if pinned:
+            arr = (_f32p * len(self._pinned))(*[a.ctypes.data_as(_f32p) for a in self._pinned])
+            self._call("dp_step_graph", C.c_int64(self.handle), arr, C.c_int(len(self._pinned)), C.c_int(1))
+        elif arrays is None:
+            self._call("dp_step_graph", C.c_int64(self.handle), None, C.c_int(0), C.c_int(0))
+        else:
+            keep, arr = self._ptrs(arrays)
+            self._call("dp_step_graph", C.c_int64(self.handle), arr, C.c_int(len(keep)), C.c_int(0))
+
+    def last_loss(self):
+        loss = C.c_float(0)
+        self._call("dp_last_loss", C.c_int64(self.handle), C.byref(loss))
+        return loss.value
+
+    def loss_tensor(self):
+        h = C.c_int64(0)
+        self._call("dp_loss_tensor", C.c_int64(self.handle), C.byref(h))
+        return Tensor(self.engine, h.value)
+
+    def graph_nodes(self):
+        n = C.c_int64(0)
+        self._call("dp_graph_nodes", C.c_int64(self.handle), C.byref(n))
+        return n.value

@@ -1,0 +1,150 @@
+"""Calls through the raw C ABI (include/rt_b200.h) with device pointers, against numpy / the oracle."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from helpers import assert_close, rng
+from rusttensor_b200.capi import BINARY, REDUCE, UNARY, RtError
+
+pytestmark = pytest.mark.gpu
+
+
+def test_unary_backward_vectorised_and_tail(capi):
+    r = rng(61)
+    for n in (1, 3, 4, 5, 1023, 1 << 20, (1 << 20) + 3):
+        x = r.standard_normal(n).astype(np.float32)
+        g = r.standard_normal(n).astype(np.float32)
+        dx, dg, dd = capi.to_device(x), capi.to_device(g), capi.empty((n,))
+        capi.call("unary_backward", C.c_int(UNARY["tanh"]), dx.ptr, dg.ptr, dd.ptr, C.c_int64(n), C.c_float(0), C.c_float(0))
+        assert_close(dd.numpy(), g * (1 - np.tanh(x.astype(np.float64)) ** 2), 1e-4, f"tanh_backward n={n}")
+        capi.call("unary_backward", C.c_int(UNARY["relu"]), dx.ptr, dg.ptr, dd.ptr, C.c_int64(n), C.c_float(0), C.c_float(0))
+        assert np.array_equal(dd.numpy(), g * (x > 0))
+
+
+def test_unaligned_pointers_take_the_scalar_path(capi):
+    r = rng(62)
+    n = 1000
+    x = r.standard_normal(n + 1).astype(np.float32)
+    dx, dy = capi.to_device(x), capi.empty((n + 1,))
+    off = lambda d: C.c_void_p(d.ptr.value + 4)
+    capi.call("unary", C.c_int(UNARY["exp"]), off(dx), off(dy), C.c_int64(n), C.c_float(0), C.c_float(0))
+    assert_close(dy.numpy()[1:], np.exp(x[1:].astype(np.float64)), 1e-5, "exp on an unaligned pointer")
+
+
+def test_binary_backward_rowvec_fused_column_sum(capi):
+    r = rng(63)
+    for rows, cols in ((4096, 512), (1000, 132), (37, 4), (3, 260)):
+        a = r.standard_normal((rows, cols)).astype(np.float32)
+        b = r.standard_normal(cols).astype(np.float32)
+        g = r.standard_normal((rows, cols)).astype(np.float32)
+        da_, db_, dg_ = capi.to_device(a), capi.to_device(b), capi.to_device(g)
+        oa, ob = capi.empty((rows, cols)), capi.empty((cols,))
+        capi.call("binary_backward", C.c_int(BINARY["mul"]), da_.ptr, capi.i64([rows, cols]), C.c_int(2), db_.ptr,
+                  capi.i64([cols]), C.c_int(1), dg_.ptr, oa.ptr, ob.ptr)
+        assert_close(oa.numpy(), g.astype(np.float64) * b, 1e-5, "dA")
+        assert_close(ob.numpy(), (g.astype(np.float64) * a).sum(0), 1e-4, f"db {rows}x{cols}")
+        # run-to-run determinism of the two-pass reduction
+        ob2 = capi.empty((cols,))
+        capi.call("binary_backward", C.c_int(BINARY["mul"]), da_.ptr, capi.i64([rows, cols]), C.c_int(2), db_.ptr,
+                  capi.i64([cols]), C.c_int(1), dg_.ptr, None, ob2.ptr)
+        assert np.array_equal(ob.numpy(), ob2.numpy())
+
+
+def test_unbroadcast_patterns(capi):
+    r = rng(64)
+    cases = [((6, 5), (5,)), ((6, 5), (6, 1)), ((6, 5), ()), ((2, 3, 4), (3, 1)), ((2, 3, 4), (1, 3, 1)), ((4, 3, 5, 6), (3, 1, 1)),
+             ((300, 70), (70,)), ((2, 1, 4), (4,)), ((5,), (5,))]
+    for gs, ts in cases:
+        g = r.standard_normal(gs).astype(np.float32)
+        out = capi.empty(ts)
+        capi.call("unbroadcast", capi.to_device(g).ptr, capi.i64(gs), C.c_int(len(gs)), capi.i64(ts), C.c_int(len(ts)), out.ptr)
+        ref = g.astype(np.float64)
+        lead = len(gs) - len(ts)
+        if lead:
+            ref = ref.sum(axis=tuple(range(lead)))
+        for i, t in enumerate(ts):
+            if t == 1 and ref.shape[i] != 1:
+                ref = ref.sum(axis=i, keepdims=True)
+        assert_close(out.numpy(), ref.reshape(ts), 1e-4, f"unbroadcast {gs}->{ts}")
+    with pytest.raises(RtError) as ei:
+        capi.call("unbroadcast", capi.to_device(np.zeros((4, 3))).ptr, capi.i64([4, 3]), C.c_int(2), capi.i64([2]), C.c_int(1), capi.empty((2,)).ptr)
+    assert ei.value.code == 2
+
+
+def test_reduce_shapes(capi):
+    r = rng(65)
+    for outer, ln, inner in ((1, 1 << 22, 1), (3, 70000, 1), (1000, 17, 1), (1, 4096, 4096), (5, 300, 7), (2, 9000, 4), (70000, 3, 2)):
+        x = r.standard_normal((outer, ln, inner)).astype(np.float32)
+        dx = capi.to_device(x)
+        for kind, f in (("sum", np.sum), ("max", np.max), ("min", np.min)):
+            out = capi.empty((outer, inner))
+            capi.call("reduce", C.c_int(REDUCE[kind]), dx.ptr, C.c_int64(outer), C.c_int64(ln), C.c_int64(inner), out.ptr)
+            assert_close(out.numpy(), f(x.astype(np.float64), axis=1), 1e-4, f"{kind} [{outer},{ln},{inner}]")
+    host = C.c_float(0)
+    x = r.standard_normal(100001).astype(np.float32)
+    capi.call("sum_all_host", capi.to_device(x).ptr, C.c_int64(x.size), C.byref(host))
+    assert abs(host.value - x.astype(np.float64).sum()) < 1e-2
+
+
+def test_gemm_transposes_ld_and_accumulate(capi):
+    r = rng(66)
+    m, n, k = 70, 50, 90
+    for ta in (0, 1):
+        for tb in (0, 1):
+            a = r.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
+            b = r.standard_normal((n, k) if tb else (k, n)).astype(np.float32)
+            c0 = r.standard_normal((m, n)).astype(np.float32)
+            dc = capi.to_device(c0)
+            capi.call("gemm", C.c_int(ta), C.c_int(tb), C.c_int64(m), C.c_int64(n), C.c_int64(k), capi.to_device(a).ptr,
+                      C.c_int64(a.shape[1]), capi.to_device(b).ptr, C.c_int64(b.shape[1]), dc.ptr, C.c_int64(n), C.c_int(1))
+            A = a.T if ta else a
+            B = b.T if tb else b
+            assert_close(dc.numpy(), c0 + A.astype(np.float64) @ B.astype(np.float64), 1e-4, f"gemm ta={ta} tb={tb} accumulate")
+    # split-K path: tiny output, long reduction
+    a = r.standard_normal((20000, 24)).astype(np.float32)
+    g = r.standard_normal((20000, 40)).astype(np.float32)
+    out = capi.empty((24, 40))
+    capi.call("gemm", C.c_int(1), C.c_int(0), C.c_int64(24), C.c_int64(40), C.c_int64(20000), capi.to_device(a).ptr, C.c_int64(24),
+              capi.to_device(g).ptr, C.c_int64(40), out.ptr, C.c_int64(40), C.c_int(0))
+    assert_close(out.numpy(), a.astype(np.float64).T @ g.astype(np.float64), 1e-4, "split-K gemm")
+
+
+def test_optimizer_multi_matches_per_tensor(capi):
+    r = rng(67)
+    sizes = [1, 7, 4096, 5000, 33]
+    ps = [r.standard_normal(s).astype(np.float32) for s in sizes]
+    gs = [r.standard_normal(s).astype(np.float32) * 10 for s in sizes]
+    single, multi = [], []
+    for p, g in zip(ps, gs):
+        dp, dg, dm, dv = capi.to_device(p), capi.to_device(np.clip(g, -5, 5) * 0.5), capi.to_device(np.zeros_like(p)), capi.to_device(np.zeros_like(p))
+        capi.call("adam_step", dp.ptr, dg.ptr, dm.ptr, dv.ptr, C.c_int64(p.size), C.c_float(1e-3), C.c_float(0.9), C.c_float(0.999),
+                  C.c_float(1e-8), C.c_int64(3))
+        single.append((dp.numpy(), dm.numpy(), dv.numpy()))
+    dps = [capi.to_device(p) for p in ps]
+    dgs = [capi.to_device(g) for g in gs]
+    dms = [capi.to_device(np.zeros_like(p)) for p in ps]
+    dvs = [capi.to_device(np.zeros_like(p)) for p in ps]
+    arr = lambda ds: (C.c_void_p * len(ds))(*[d.ptr for d in ds])
+    capi.call("optimizer_step_multi", C.c_int(1), C.c_int(len(ps)), arr(dps), arr(dgs), arr(dms), arr(dvs), capi.i64(sizes),
+              C.c_float(1e-3), C.c_float(0.9), C.c_float(0.999), C.c_float(1e-8), C.c_float(0), C.c_int64(3), C.c_float(0.5),
+              C.c_int(1), C.c_float(-5), C.c_float(5))
+    for i in range(len(ps)):
+        assert_close(dps[i].numpy(), single[i][0], 1e-6, "multi-tensor Adam params")
+        assert_close(dms[i].numpy(), single[i][1], 1e-6, "m")
+        assert_close(dvs[i].numpy(), single[i][2], 1e-6, "v")
+
+
+def test_argument_validation(capi):
+    with pytest.raises(RtError) as ei:
+        capi.call("unary", C.c_int(99), None, None, C.c_int64(4), C.c_float(0), C.c_float(0))
+    assert ei.value.code == 4
+    with pytest.raises(RtError) as ei:
+        capi.call("unary", C.c_int(UNARY["div_scalar"]), capi.empty((4,)).ptr, capi.empty((4,)).ptr, C.c_int64(4), C.c_float(0), C.c_float(0))
+    assert ei.value.code == 4
+    with pytest.raises(RtError):
+        capi.call("adam_step", capi.empty((4,)).ptr, capi.empty((4,)).ptr, capi.empty((4,)).ptr, capi.empty((4,)).ptr, C.c_int64(4),
+                  C.c_float(1e-3), C.c_float(0.9), C.c_float(0.999), C.c_float(1e-8), C.c_int64(0))
+    # empty tensors are no-ops
+    capi.call("unary", C.c_int(0), None, None, C.c_int64(0), C.c_float(0), C.c_float(0))
+    capi.call("reduce", C.c_int(0), None, C.c_int64(0), C.c_int64(5), C.c_int64(3), None)

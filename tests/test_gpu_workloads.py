@@ -1,0 +1,134 @@
+"""The five benchmark workloads: CUDA backend vs CPU oracle on the same seeded inputs.
+Gradients, updated parameters and optimizer state within 1e-4 (max-abs-rel with the documented
+floor for near-zero sums)."""
+import numpy as np
+import pytest
+
+import oracle
+import rusttensor_b200
+from helpers import assert_close, setup_trainer, workload_data
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+
+SMALL = {
+    1: [8, 20, 16, 5],
+    2: [64, 48],
+    3: [4, 8, 4, 6, 16, 5],
+    4: [2, 3, 8, 5],
+    5: [11, 8, 4, 3],
+}
+FULL = {1: [64, 784, 128, 10], 3: [256, 28, 32, 64, 128, 10]}
+
+
+def run_reference_step(engine, config, dims, params, inputs, steps=1, conv_dx_correct=False):
+    tr = setup_trainer(engine, config, dims, params)
+    ins = [engine.tensor(a, requires_grad=(config == 4 and i == 0)) for i, a in enumerate(inputs)]
+    losses = []
+    if conv_dx_correct:
+        oracle.set_conv_dx_faithful(False)
+    try:
+        for _ in range(steps):
+            loss = tr.step(ins) if config != 2 else tr.forward_backward(ins)
+            losses.append(float(loss.numpy()))
+    finally:
+        oracle.set_conv_dx_faithful(True)
+    grads = [p.grad.numpy() for p in tr.params]
+    vals = [p.numpy() for p in tr.params]
+    extra = [ins[0].grad.numpy()] if config == 4 else []
+    states = []
+    if config in (1, 3, 5):
+        states = [tr.optim_state(0, i).numpy() for i in range(len(tr.params))] + [tr.optim_state(1, i).numpy() for i in range(len(tr.params))]
+    elif config == 4:
+        states = [tr.optim_state(0, i).numpy() for i in range(len(tr.params))]
+    return dict(loss=losses, grads=grads, params=vals, extra=extra, states=states)
+
+
+def compare_runs(cpu, gpu, what, tol=TOL):
+    assert_close(np.array(gpu["loss"]), np.array(cpu["loss"]), tol, f"{what} loss")
+    for k in ("grads", "params", "extra", "states"):
+        assert len(cpu[k]) == len(gpu[k])
+        for i, (a, b) in enumerate(zip(cpu[k], gpu[k])):
+            assert_close(b, a, tol, f"{what} {k}[{i}]")
+
+
+@pytest.mark.parametrize("config", [1, 2, 3, 4, 5])
+def test_small_workload_matches_oracle(oracle_engine, gpu_engine, config):
+    dims = SMALL[config]
+    params, inputs = workload_data(config, dims, seed=0)
+    # conv input gradients: the CUDA kernels are mathematically correct, so configs whose
+    # parameter gradients sit downstream of a conv dX (3: conv1 behind conv2's dX; 4: dX itself)
+    # are compared with the oracle's corrected mode.
+    correct = config in (3, 4)
+    cpu = run_reference_step(oracle_engine, config, dims, params, inputs, steps=2, conv_dx_correct=correct)
+    gpu = run_reference_step(gpu_engine, config, dims, params, inputs, steps=2)
+    compare_runs(cpu, gpu, f"C{config} small")
+
+
+def test_c3_reference_defect_is_confined(oracle_engine, gpu_engine):
+    """With the reference's conv dX defect reproduced (faithful mode) everything NOT downstream of
+    a conv input gradient still matches the CUDA path: conv2 / fc gradients of C3."""
+    dims = SMALL[3]
+    params, inputs = workload_data(3, dims, seed=1)
+    cpu = run_reference_step(oracle_engine, 3, dims, params, inputs, steps=1, conv_dx_correct=False)
+    gpu = run_reference_step(gpu_engine, 3, dims, params, inputs, steps=1)
+    for i in range(2, 8):  # conv2_w, conv2_b, fc1_w, fc1_b, fc2_w, fc2_b
+        assert_close(gpu["grads"][i], cpu["grads"][i], TOL, f"C3 faithful grads[{i}]")
+    gap = np.max(np.abs(gpu["grads"][0] - cpu["grads"][0]))
+    print(f"conv1_w gradient gap caused by the reference defect: {gap:.3e}")
+
+
+@pytest.mark.parametrize("config", [1, 3])
+def test_full_size_workload_matches_oracle(oracle_engine, gpu_engine, config):
+    dims = FULL[config]
+    params, inputs = workload_data(config, dims, seed=2)
+    cpu = run_reference_step(oracle_engine, config, dims, params, inputs, steps=1, conv_dx_correct=(config == 3))
+    gpu = run_reference_step(gpu_engine, config, dims, params, inputs, steps=1)
+    compare_runs(cpu, gpu, f"C{config} full")
+
+
+@pytest.mark.parametrize("config", [1, 3, 4, 5])
+def test_fused_trainer_eager_and_graph_match_per_tensor_path(gpu_engine, config):
+    """DataParallelTrainer (fused multi-tensor optimizer, CUDA-graph replay) == the per-tensor API."""
+    dims = SMALL[config]
+    params, inputs = workload_data(config, dims, seed=3)
+    ref = run_reference_step(gpu_engine, config, dims, params, inputs, steps=3)
+    for mode in ("eager", "graph"):
+        tr = rusttensor_b200.DataParallelTrainer(config, dims)
+        for t, p in zip(tr.params, params):
+            t.update_from_host(p)
+        losses = []
+        for _ in range(3):
+            if mode == "eager":
+                losses.append(tr.step_eager(inputs))
+            else:
+                tr.step(inputs)
+                losses.append(tr.last_loss())
+        if mode == "graph":
+            assert tr.graph_nodes() > 0
+        assert_close(np.array(losses), np.array(ref["loss"]), 1e-5, f"C{config} {mode} losses")
+        for i, p in enumerate(tr.params):
+            assert_close(p.numpy(), ref["params"][i], 1e-5, f"C{config} {mode} params[{i}]")
+        n = len(tr.params)
+        for i in range(n):
+            assert_close(tr.state(0, i).numpy(), ref["states"][i], 1e-5, f"C{config} {mode} state0[{i}]")
+
+
+def test_graph_replay_is_deterministic_and_uses_fresh_inputs(gpu_engine):
+    dims = SMALL[3]
+    params, in_a = workload_data(3, dims, seed=4)
+    _, in_b = workload_data(3, dims, seed=5)
+    runs = []
+    for _ in range(2):
+        tr = rusttensor_b200.DataParallelTrainer(3, dims)
+        for t, p in zip(tr.params, params):
+            t.update_from_host(p)
+        out = []
+        for ins in (in_a, in_b, in_a):
+            tr.step(ins)
+            out.append(tr.last_loss())
+        runs.append((out, [p.numpy() for p in tr.params]))
+    assert runs[0][0] == runs[1][0]
+    assert runs[0][0][0] != runs[0][0][1]
+    for a, b in zip(runs[0][1], runs[1][1]):
+        assert np.array_equal(a, b)
