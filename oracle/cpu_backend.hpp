@@ -111,28 +111,36 @@ inline std::vector<size_t> bcast_strides(const Shape& shape, const Shape& out) {
   return st;
 }
 
-// src/util.rs:2-26 -- numpy-style right-aligned broadcast of two shapes.
-inline Shape broadcast_shapes(const Shape& a, const Shape& b, const char* op) {
+// Broadcast shape of two right-aligned shapes.
+//  ndarray_operator = false: the rule of src/util.rs:2-26 and src/ops/cpu_ops.rs:319-335 (the larger
+//    extent wins when one side is 1), followed by ndarray's `broadcast`, which only stretches
+//    extents equal to 1 -- so pairing an extent 0 with an extent 1 is an IncompatibleShapes error.
+//  ndarray_operator = true: ndarray's operator co-broadcast used by sub/div
+//    (src/backend/cpu.rs:1259-1269): an extent 1 stretches to the other side, 0 included.
+inline Shape broadcast_shapes(const Shape& a, const Shape& b, const char* op, bool ndarray_operator = false) {
   size_t nd = std::max(a.size(), b.size());
   Shape out(nd);
   for (size_t i = 0; i < nd; ++i) {
     size_t ad = i < nd - a.size() ? 1 : a[i - (nd - a.size())];
     size_t bd = i < nd - b.size() ? 1 : b[i - (nd - b.size())];
     if (ad == bd) out[i] = ad;
-    else if (ad == 1 || bd == 1) out[i] = std::max(ad, bd);
-    else throw Error::incompatible(op, a, b);
+    else if (ad == 1 || bd == 1) {
+      out[i] = ndarray_operator ? (ad == 1 ? bd : ad) : std::max(ad, bd);
+      if (out[i] != ad && ad != 1) throw Error::incompatible(op, a, b);
+      if (out[i] != bd && bd != 1) throw Error::incompatible(op, a, b);
+    } else throw Error::incompatible(op, a, b);
   }
   return out;
 }
 
 template <class F>
-Array broadcast_binary(const Array& a, const Array& b, const char* op, F f) {
+Array broadcast_binary(const Array& a, const Array& b, const char* op, F f, bool ndarray_operator = false) {
   if (a.shape == b.shape) {
     Array out(std::vector<float>(a.size()), a.shape);
     for (size_t i = 0; i < a.size(); ++i) out.data[i] = f(a.data[i], b.data[i]);
     return out;
   }
-  Shape os = broadcast_shapes(a.shape, b.shape, op);
+  Shape os = broadcast_shapes(a.shape, b.shape, op, ndarray_operator);
   Array out(std::vector<float>(shape_numel(os)), os);
   auto sa = bcast_strides(a.shape, os), sb = bcast_strides(b.shape, os);
   size_t nd = os.size();
@@ -239,10 +247,10 @@ struct CpuBackend {
   // src/backend/cpu.rs:1259-1269: ndarray operator broadcasting (the reference panics on
   // incompatible shapes; here that is an IncompatibleShapes error).
   static Array sub(const Array& a, const Array& b) {
-    return broadcast_binary(a, b, "sub", [](float x, float y) { return x - y; });
+    return broadcast_binary(a, b, "sub", [](float x, float y) { return x - y; }, true);
   }
   static Array div(const Array& a, const Array& b) {
-    return broadcast_binary(a, b, "div", [](float x, float y) { return x / y; });
+    return broadcast_binary(a, b, "div", [](float x, float y) { return x / y; }, true);
   }
   static Array powf(const Array& a, const Array& b) {  // src/ops/cpu_ops.rs:765-830
     return broadcast_binary(a, b, "powf", [](float x, float y) { return std::pow(x, y); });

@@ -95,7 +95,7 @@ class CApi:
         return DeviceArray(self, p, shape)
 
     def to_device(self, array):
-        a = np.ascontiguousarray(array, dtype=np.float32)
+        a = np.require(array, dtype=np.float32, requirements='C')
         d = self.empty(a.shape)
         self.check(self.lib.rt_memcpy_h2d(self.ctx, d.ptr, a.ctypes.data_as(C.c_void_p), C.c_size_t(a.nbytes)))
         return d

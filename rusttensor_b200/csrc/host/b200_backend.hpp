@@ -119,20 +119,27 @@ struct B200Backend {
     check(rt_unary_backward(ctx(), op, x.ptr(), g.ptr(), dx.ptr(), (int64_t)x.numel(), p0, p1));
     return dx;
   }
-  static Shape bshape(const Shape& a, const Shape& b, const char* op) {
+  // Broadcast shape.  For add/mul/powf/maximum/minimum/comparisons the reference takes the larger
+  // extent when one side is 1 and then asks ndarray to stretch each operand, which fails when an
+  // extent 0 meets an extent 1 (src/ops/cpu_ops.rs:319-352; src/util.rs:2-26); sub/div use ndarray's
+  // operator broadcasting, where 1 stretches to 0 (src/backend/cpu.rs:1259-1269).
+  static Shape bshape(const Shape& a, const Shape& b, const char* op, bool ndarray_operator = false) {
     size_t nd = std::max(a.size(), b.size());
     Shape out(nd);
     for (size_t i = 0; i < nd; ++i) {
       size_t ad = i < nd - a.size() ? 1 : a[i - (nd - a.size())];
       size_t bd = i < nd - b.size() ? 1 : b[i - (nd - b.size())];
       if (ad == bd) out[i] = ad;
-      else if (ad == 1 || bd == 1) out[i] = std::max(ad, bd);
-      else throw Error::incompatible(op, a, b);
+      else if (ad == 1 || bd == 1) {
+        out[i] = ndarray_operator ? (ad == 1 ? bd : ad) : std::max(ad, bd);
+        if ((out[i] != ad && ad != 1) || (out[i] != bd && bd != 1)) throw Error::incompatible(op, a, b);
+      } else throw Error::incompatible(op, a, b);
     }
     return out;
   }
+  static bool is_operator_op(int op) { return op == RT_SUB || op == RT_DIV; }
   static Storage binary(int op, const Storage& a, const Storage& b, const char* name) {
-    Storage out = alloc(bshape(a.shape, b.shape, name));
+    Storage out = alloc(bshape(a.shape, b.shape, name, is_operator_op(op)));
     auto as = dims(a.shape), bs = dims(b.shape);
     check(rt_binary(ctx(), op, a.ptr(), as.data(), (int)as.size(), b.ptr(), bs.data(), (int)bs.size(), out.ptr()));
     return out;
@@ -141,7 +148,7 @@ struct B200Backend {
     if (o.inputs.size() != 2) throw Error::invalid_op(std::string(name) + " requires 2 inputs");
     const Storage& a = o.inputs[0].data();
     const Storage& b = o.inputs[1].data();
-    Shape os = bshape(a.shape, b.shape, name);
+    Shape os = bshape(a.shape, b.shape, name, is_operator_op(op));
     if (g.numel() != shape_numel(os)) throw Error::incompatible(name, os, g.shape);
     bool need_a = o.inputs[0].requires_grad(), need_b = o.inputs[1].requires_grad();
     Storage da = need_a ? alloc(a.shape) : Storage{nullptr, a.shape};

@@ -707,7 +707,12 @@ rt_status rt_binary_backward(rt_ctx* ctx, int op, const float* a, const int64_t*
   int out_nd = 0;
   if (!make_geom(a_shape, a_ndim, b_shape, b_ndim, &geo, out_shape, &out_nd))
     RT_FAIL(ctx, RT_ERR_INCOMPATIBLE_SHAPES, "rt_binary_backward: shapes cannot be broadcast together");
-  if (geo.numel == 0 || (!da && !db)) return RT_OK;
+  if (!da && !db) return RT_OK;
+  if (geo.numel == 0) {  // an empty broadcast result still owes zero gradients to non-empty operands
+    rt_status st = da ? rt_fill(ctx, da, 0.f, numel_of(a_shape, a_ndim)) : RT_OK;
+    if (st == RT_OK && db) st = rt_fill(ctx, db, 0.f, numel_of(b_shape, b_ndim));
+    return st;
+  }
   RT_CHECK_PTR(ctx, a);
   RT_CHECK_PTR(ctx, b);
   RT_CHECK_PTR(ctx, g);
@@ -742,7 +747,7 @@ rt_status rt_unbroadcast(rt_ctx* ctx, const float* g, const int64_t* g_shape, in
     else RT_FAIL(ctx, RT_ERR_INCOMPATIBLE_SHAPES, "rt_unbroadcast: dimension %d: %lld cannot reduce to %lld", i, (long long)cur[i], (long long)td);
     if (red[i] && cur[i] != 1) any = true;
   }
-  if (n == 0) return RT_OK;
+  if (n == 0) return out ? rt_fill(ctx, out, 0.f, numel_of(t_shape, t_ndim)) : RT_OK;
   RT_CHECK_PTR(ctx, g);
   RT_CHECK_PTR(ctx, out);
   if (!any) return rt_memcpy_d2d(ctx, out, g, sizeof(float) * n);

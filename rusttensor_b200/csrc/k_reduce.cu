@@ -77,6 +77,33 @@ __global__ void __launch_bounds__(kThreads) row_reduce_warp(const float* __restr
   }
 }
 
+// ---- inner == 1, very short rows (class axes, loss tails): one thread per row ---------
+// Sums in the association order of the CPU backend's eight-way unrolled fold
+// (ndarray sum of a contiguous lane), so that tiny reductions round like the CPU ones.
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) row_reduce_thread(const float* __restrict__ x, float* __restrict__ out,
+                                                               int64_t rows, int len, float scale) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += stride) {
+    const float* p = x + r * len;
+    float part[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) part[j] = Red<KIND>::init();
+    int k = 0;
+    for (; k + 8 <= len; k += 8) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) part[j] = Red<KIND>::op(part[j], __ldg(p + k + j));
+    }
+    float acc = Red<KIND>::init();
+    acc = Red<KIND>::op(acc, Red<KIND>::op(part[0], part[4]));
+    acc = Red<KIND>::op(acc, Red<KIND>::op(part[1], part[5]));
+    acc = Red<KIND>::op(acc, Red<KIND>::op(part[2], part[6]));
+    acc = Red<KIND>::op(acc, Red<KIND>::op(part[3], part[7]));
+    for (; k < len; ++k) acc = Red<KIND>::op(acc, __ldg(p + k));
+    out[r] = acc * scale;
+  }
+}
+
 // ---- inner == 1: block per (row, chunk) --------------------------------------------
 // Row r is cut into `chunks` pieces of `chunk_len`; block (r, c) reduces one piece and
 // writes out[r * chunks + c].
@@ -164,6 +191,11 @@ rt_status reduce_float(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, 
   const int64_t target_blocks = (int64_t)ctx->sm_count * 4;
   if (inner == 1) {
     int64_t rows = outer;
+    if (len <= 16) {
+      row_reduce_thread<KIND><<<rt_grid_for(ctx, rows, kThreads), kThreads, 0, ctx->stream>>>(x, out, rows, (int)len, scale);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
     if (len <= 1024) {
       int grid = rt_grid_for(ctx, rows, kThreads / 32);
       row_reduce_warp<KIND><<<grid, kThreads, 0, ctx->stream>>>(x, out, rows, len, scale);

@@ -74,7 +74,7 @@ class Tensor:
         return out
 
     def update_from_host(self, data):
-        a = np.ascontiguousarray(data, dtype=np.float32)
+        a = np.require(data, dtype=np.float32, requirements='C')
         self.engine._call("tensor_update_from_host", C.c_int64(self.handle), a.ctypes.data_as(_f32p), C.c_int64(a.size))
 
     @property
@@ -241,7 +241,7 @@ class Engine:
 
     def tensor(self, data, shape=None, requires_grad=False):
         """``Tensor::from_vec(data, shape, requires_grad)`` (src/tensor.rs:948-950)."""
-        a = np.ascontiguousarray(data, dtype=np.float32)
+        a = np.require(data, dtype=np.float32, requirements='C')
         if shape is None:
             shape = a.shape
         shape = tuple(int(s) for s in shape)

@@ -78,7 +78,7 @@ class DataParallelTrainer:
         return self._pinned[i]
 
     def _ptrs(self, arrays):
-        keep = [np.ascontiguousarray(a, dtype=np.float32) for a in arrays]
+        keep = [np.require(a, dtype=np.float32, requirements='C') for a in arrays]
         arr = (_f32p * len(keep))(*[a.ctypes.data_as(_f32p) for a in keep])
         return keep, arr
 

@@ -31,9 +31,14 @@ def max_abs_rel(a, b):
     return float(np.max(rel))
 
 
-def assert_close(got, ref, tol=1e-4, what=""):
+def assert_close(got, ref, tol=1e-4, what="", abs_floor=0.0):
     """max-abs-rel <= tol, or, for the near-zero outputs of long zero-mean sums whose relative
-    error is unbounded for any summation order, |a-b| <= tol*max(|a|,|b|) + 1e-6*max|ref|."""
+    error is unbounded for any summation order, |a-b| <= tol*max(|a|,|b|) + 1e-6*max|ref| + abs_floor.
+
+    abs_floor is used only for parameters after an Adam step: Adam divides by sqrt(v)+eps, so for an
+    element whose gradient is a near-zero sum (|g| comparable to eps) the rounding noise the gradient
+    check itself allows becomes a change of up to noise/|g| of a full step lr; callers pass a few
+    1e-4 * lr."""
     got = np.asarray(got, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     assert got.shape == ref.shape, f"{what}: shape {got.shape} vs {ref.shape}"
@@ -43,7 +48,7 @@ def assert_close(got, ref, tol=1e-4, what=""):
     if m <= tol:
         return
     scale = float(np.max(np.abs(ref[np.isfinite(ref)]))) if np.isfinite(ref).any() else 0.0
-    bound = tol * np.maximum(np.abs(got), np.abs(ref)) + 1e-6 * scale
+    bound = tol * np.maximum(np.abs(got), np.abs(ref)) + 1e-6 * scale + abs_floor
     bad = ~(np.abs(got - ref) <= bound) & ~((got == ref) | (np.isnan(got) & np.isnan(ref)))
     assert not bad.any(), (f"{what}: max-abs-rel {m:.3e} > {tol}; {int(bad.sum())} of {got.size} elements outside the "
                            f"mixed bound, worst |d|={np.max(np.abs(got - ref)[bad]):.3e} (ref scale {scale:.3e})")

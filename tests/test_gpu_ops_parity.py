@@ -23,10 +23,9 @@ def both(oracle_engine, gpu_engine, build, arrays, requires_grad=None, seed_grad
         if y.requires_grad:
             if seed_grad is not None:
                 y.set_grad(e.tensor(seed_grad(y.shape)))
-            elif len(y.shape) != 0 or True:
-                if int(np.prod(y.shape, dtype=np.int64)) != 1:
-                    g = rng(77).standard_normal(y.shape).astype(np.float32)
-                    y.set_grad(e.tensor(g))
+            elif len(y.shape) != 0:  # only a 0-D root is seeded implicitly (src/tensor.rs:1157-1170)
+                g = rng(77).standard_normal(y.shape).astype(np.float32)
+                y.set_grad(e.tensor(g, y.shape))
             y.backward()
             res["grads"] = [None if t.grad is None else (t.grad.numpy(), t.grad.shape) for t in ts]
         outs.append(res)
@@ -75,12 +74,26 @@ def test_parametrised_unary(oracle_engine, gpu_engine, shape):
     compare(both(oracle_engine, gpu_engine, lambda e, t: e.ops.clip(t[0], -0.5, 1.0), [x]), "clip")
     compare(both(oracle_engine, gpu_engine, lambda e, t: e.ops.mul_scalar(t[0], -1.5), [x]), "mul_scalar")
     compare(both(oracle_engine, gpu_engine, lambda e, t: e.ops.div_scalar(t[0], 3.0), [x], requires_grad=[False]), "div_scalar")
-    compare(both(oracle_engine, gpu_engine, lambda e, t: e.ops.powf_scalar(e.ops.abs(t[0]), 2.5), [x + 3.0]), "powf_scalar")
+    if x.size:  # a [1]-shaped exponent cannot broadcast against an empty base (see the next test)
+        compare(both(oracle_engine, gpu_engine, lambda e, t: e.ops.powf_scalar(e.ops.abs(t[0]), 2.5), [x + 3.0]), "powf_scalar")
+
+
+def test_extent_zero_against_extent_one(oracle_engine, gpu_engine):
+    """add/mul/powf: an extent 0 cannot pair with an extent 1 (the reference takes max(0,1)=1 and then
+    fails to stretch the empty operand); sub/div go through ndarray's operators, where it can."""
+    for e in (oracle_engine, gpu_engine):
+        a, b = e.tensor(np.zeros((0,), np.float32)), e.tensor(np.ones((1,), np.float32))
+        for op in ("add", "mul", "powf", "maximum"):
+            with pytest.raises(EngineError) as ei:
+                getattr(e.ops, op)(a, b)
+            assert ei.value.kind == "IncompatibleShapes"
+        assert e.ops.sub(a, b).shape == (0,)
+        assert e.ops.div(a, b).shape == (0,)
 
 
 BROADCAST_PAIRS = [((5, 3), (5, 3)), ((4, 128), (128,)), ((33, 257), (257,)), ((128,), (4, 128)), ((6, 5), ()), ((), (6, 5)),
                    ((3, 1), (1, 4)), ((2, 3, 4), (3, 1)), ((2, 1, 4), (5, 1)), ((7,), (1,)), ((4, 4, 8), (4, 1, 8)),
-                   ((512, 256), (256,)), ((0, 3), (3,)), ((2, 3, 4, 5), (4, 5))]
+                   ((512, 256), (256,)), ((0, 3), (1, 3)), ((2, 3, 4, 5), (4, 5))]
 
 
 @pytest.mark.parametrize("sa,sb", BROADCAST_PAIRS, ids=str)
@@ -93,6 +106,10 @@ def test_binary_broadcast_forward_backward(oracle_engine, gpu_engine, op, sa, sb
         b = (np.sign(b) * (np.abs(b) + 0.5)).astype(np.float32)
     if op == "powf":
         a = (np.abs(a) + 0.5).astype(np.float32)
+    if 0 in sa + sb and op != "sub":
+        # outside sub/div an extent 0 cannot meet an extent 1 (test_extent_zero_against_extent_one);
+        # div's backward multiplies through `mul`, so it fails the same way in the reference.
+        pytest.skip("extent 0 against extent 1 is only defined for sub")
     compare(both(oracle_engine, gpu_engine, lambda e, t: getattr(e.ops, op)(t[0], t[1]), [a, b]), f"{op}{sa}{sb}")
 
 

@@ -44,12 +44,17 @@ def run_reference_step(engine, config, dims, params, inputs, steps=1, conv_dx_co
     return dict(loss=losses, grads=grads, params=vals, extra=extra, states=states)
 
 
-def compare_runs(cpu, gpu, what, tol=TOL):
+LR = {1: 1e-3, 3: 1e-3, 4: 1e-2, 5: 1e-3, 2: 0.0}
+
+
+def compare_runs(cpu, gpu, what, tol=TOL, lr=0.0):
     assert_close(np.array(gpu["loss"]), np.array(cpu["loss"]), tol, f"{what} loss")
     for k in ("grads", "params", "extra", "states"):
         assert len(cpu[k]) == len(gpu[k])
         for i, (a, b) in enumerate(zip(cpu[k], gpu[k])):
-            assert_close(b, a, tol, f"{what} {k}[{i}]")
+            # updated parameters: an extra 5e-4 of one step for elements whose gradient is a
+            # near-zero sum (see helpers.assert_close)
+            assert_close(b, a, tol, f"{what} {k}[{i}]", abs_floor=5e-4 * lr if k == "params" else 0.0)
 
 
 @pytest.mark.parametrize("config", [1, 2, 3, 4, 5])
@@ -62,7 +67,7 @@ def test_small_workload_matches_oracle(oracle_engine, gpu_engine, config):
     correct = config in (3, 4)
     cpu = run_reference_step(oracle_engine, config, dims, params, inputs, steps=2, conv_dx_correct=correct)
     gpu = run_reference_step(gpu_engine, config, dims, params, inputs, steps=2)
-    compare_runs(cpu, gpu, f"C{config} small")
+    compare_runs(cpu, gpu, f"C{config} small", lr=LR[config])
 
 
 def test_c3_reference_defect_is_confined(oracle_engine, gpu_engine):
@@ -84,7 +89,7 @@ def test_full_size_workload_matches_oracle(oracle_engine, gpu_engine, config):
     params, inputs = workload_data(config, dims, seed=2)
     cpu = run_reference_step(oracle_engine, config, dims, params, inputs, steps=1, conv_dx_correct=(config == 3))
     gpu = run_reference_step(gpu_engine, config, dims, params, inputs, steps=1)
-    compare_runs(cpu, gpu, f"C{config} full")
+    compare_runs(cpu, gpu, f"C{config} full", lr=LR[config])
 
 
 @pytest.mark.parametrize("config", [1, 3, 4, 5])
