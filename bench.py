@@ -1,0 +1,303 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: forward + backward + optimizer step, samples/s.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c1|c4|c5] [--impl ours|reference]
+
+N > 1 is launched by `python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...`
+(one rank per GPU; RANK / LOCAL_RANK / WORLD_SIZE from the environment).  Rank 0 prints ONE JSON
+line.  Weak scaling: every rank processes the same per-GPU batch on its own shard of synthetic data
+and the ranks exchange gradients with one NCCL all-reduce per step.
+
+The default workload is the CNN training step (conv-relu-pool x2, two linear layers, log-softmax
+NLL, Adam) at 256 samples per GPU; inputs are seeded synthetic tensors with MNIST's shapes and value
+range, weights are Kaiming-uniform from a seed.
+
+--impl reference times the CPU restatement of the reference's CPU backend (oracle/, single thread,
+as the reference's ndarray/matrixmultiply build is) on the same workload.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+WORKLOADS = {
+    # name: (config id, dims, samples per step per GPU, description)
+    "c3": (3, [256, 28, 32, 64, 128, 10], 256, "C3 CNN train step, 256x1x28x28 per GPU, Adam"),
+    "c1": (1, [64, 784, 128, 10], 64, "C1 MLP train step, batch 64, Adam"),
+    "c4": (4, [128, 64, 56, 128], 128, "C4 conv/conv-transpose train step, 128x64x56x56, MomentumSGD"),
+    "c5": (5, [65, 512, 128, 64], 64, "C5 char-LSTM train step, T=128, batch 64 per GPU, Adam"),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                    source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        for s in self.samples:
+            f = [x.strip() for x in s.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_step_time(config, dims, seed, steps):
+    """Times `steps` training steps of the CPU oracle (single thread). Returns seconds per step."""
+    import oracle
+    from helpers import setup_trainer, workload_data
+
+    e = oracle.engine()
+    params, inputs = workload_data(config, dims, seed)
+    tr = setup_trainer(e, config, dims, params)
+    ins = [e.tensor(a, requires_grad=(config == 4 and i == 0)) for i, a in enumerate(inputs)]
+    tr.step(ins)  # warm-up (page faults, allocator)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        loss = tr.step(ins)
+    float(loss.numpy())
+    return (time.perf_counter() - t0) / steps
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the reference's own CPU algorithm (oracle port) on the host cores."""
+    if rank != 0:
+        return
+    config, dims, per_gpu, desc = WORKLOADS[args.workload]
+    n_timed = max(1, min(args.steps, 20 if args.workload in ("c3", "c1") else 1))  # bounded: about 10-15 s of CPU work
+    t = [cpu_step_time(config, dims, 0, n_timed)]
+    sec = float(np.mean(t))
+    value = per_gpu / sec
+    line = {
+        "impl": "reference", "metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": desc, "per_gpu_batch": per_gpu, "note": "CPU path of the reference, single host thread; one rank only"},
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": 1, "kind": "port",
+                         "sample": f"{n_timed} timed full-batch steps ({per_gpu} samples each) of the C++ restatement of the reference "
+                                   f"CPU backend; the Rust reference cannot be built here (no cargo/rustc); host has {os.cpu_count()} cores, "
+                                   "the reference's ndarray/matrixmultiply build is single-threaded"},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def measure_dominant_kernel(rt, capi, config, dims, pk):
+    """Times the dominant kernel of the step in isolation with CUDA events on the library's stream,
+    flushing L2 between launches, and reports it against its roofline."""
+    lib, ctx = capi.lib, capi.ctx
+    if config == 3:
+        n, hw, c1, c2 = dims[0], dims[1] // 2, dims[2], dims[3]
+        # conv2 gradients: x [n,c1,hw,hw], w [c2,c1,3,3], g [n,c2,hw,hw] -> dX and dW implicit GEMMs
+        r = np.random.default_rng(0)
+        x = capi.to_device(r.standard_normal((n, c1, hw, hw)).astype(np.float32))
+        w = capi.to_device(r.standard_normal((c2, c1, 3, 3)).astype(np.float32))
+        g = capi.to_device(r.standard_normal((n, c2, hw, hw)).astype(np.float32))
+        dx, dw, db = capi.empty((n, c1, hw, hw)), capi.empty((c2, c1, 3, 3)), capi.empty((c2,))
+        flops = 2.0 * 2.0 * n * hw * hw * c2 * c1 * 9  # dX + dW, 2*M*N*K each
+        call = lambda: capi.call("conv2d_backward", x.ptr, w.ptr, g.ptr, C.c_int64(n), C.c_int64(c1), C.c_int64(hw), C.c_int64(hw),
+                                 C.c_int64(c2), C.c_int(3), C.c_int(3), C.c_int(1), C.c_int(1), C.c_int(1), C.c_int(1), dx.ptr, dw.ptr, None)
+        name = "conv2 input+weight gradient (implicit GEMM)"
+    else:
+        return None
+    flush = capi.empty((64 * 1024 * 1024,))  # 256 MB > 126 MB L2
+    ms = C.c_float(0)
+    for _ in range(3):
+        call()
+    times = []
+    for _ in range(20):
+        capi.call("fill", flush.ptr, C.c_float(1.0), C.c_int64(flush.size))
+        capi.call("timer_start")
+        call()
+        capi.call("timer_stop", C.byref(ms))
+        times.append(ms.value)
+    t = float(np.mean(times)) * 1e-3
+    peak = pk["bf16"] / 6.0  # 3xTF32: TF32 runs at half the bf16 rate, three MMAs per product
+    achieved = flops / t / 1e12
+    return {"bound": "tensor", "kernel": name, "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+            "traffic": None, "avg_launch_ms": t * 1e3,
+            "peak_source": f"{pk['source']} bf16 burst {pk['bf16']} TFLOP/s / 6 (TF32 = bf16/2, three TF32 MMAs per fp32 product)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import rusttensor_b200 as rt
+    from helpers import workload_data
+
+    config, dims, per_gpu, desc = WORKLOADS[args.workload]
+    dist = None
+    nccl_id = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            idt = torch.tensor(list(rt.DataParallelTrainer.unique_id()), dtype=torch.uint8, device="cuda")
+        dist.broadcast(idt, 0)
+        nccl_id = idt.cpu().tolist()
+
+    tr = rt.DataParallelTrainer(config, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
+    capi = rt.CApi(ctx=rt.context_handle())
+    params, inputs = workload_data(config, dims, seed=0, rank=rank)  # same weights on every rank, different data
+    for t, p in zip(tr.params, params):
+        t.update_from_host(p)
+    for i, a in enumerate(inputs):
+        tr.pinned_input(i)[...] = a
+    h2d = int(sum(a.nbytes for a in inputs))
+
+    def barrier():
+        capi.sync()
+        if dist is not None:
+            dist.barrier()
+        capi.sync()
+
+    # warm-up: the first step runs eagerly inside capture(); then replays
+    l0 = capi.launches()
+    tr.step(inputs)
+    tr.last_loss()
+    launches_per_replay = capi.launches() - l0 - 1  # kernels recorded in the graph (the optimizer launch is eager)
+    for _ in range(args.warmup):
+        tr.step(None)
+    barrier()
+
+    def timed(fn, k):
+        ms = C.c_float(0)
+        barrier()
+        capi.call("timer_start")
+        for _ in range(k):
+            fn()
+        capi.call("timer_stop", C.byref(ms))
+        barrier()
+        v = ms.value
+        if dist is not None:
+            import torch
+
+            tt = torch.tensor([v], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            v = float(tt.item())
+        return v
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    lb = capi.launches()
+    ms_resident = timed(lambda: tr.step(None), args.steps)
+    gpu_launches = (capi.launches() - lb) + launches_per_replay * args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    def e2e_step():
+        tr.step(pinned=True)   # H2D of this step's inputs from pinned memory, graph, all-reduce, optimizer, D2H of the loss
+        tr.last_loss()         # the user reads the loss every step
+
+    ms_e2e = timed(e2e_step, args.steps)
+    loss = tr.last_loss()
+
+    if rank == 0:
+        pk = peaks()
+        res, in_use, nalloc = C.c_int64(0), C.c_int64(0), C.c_int64(0)
+        capi.call("mem_stats", C.byref(res), C.byref(in_use), C.byref(nalloc))
+        roof = measure_dominant_kernel(rt, capi, config, dims, pk)
+        cpu = None
+        if not args.no_cpu_baseline:
+            steps_cpu = 15 if args.workload in ("c3", "c1") else 1
+            sec = cpu_step_time(config, dims, 0, steps_cpu)
+            cpu = {"value": per_gpu / sec, "unit": "samples/s", "cores": 1, "kind": "port",
+                   "sample": f"{steps_cpu} full-batch steps ({per_gpu} samples each) of the C++ restatement of the reference CPU "
+                             f"backend, single thread (as the reference builds ndarray/matrixmultiply); host has {os.cpu_count()} cores"}
+        total = per_gpu * world
+        line = {
+            "metric": "train_samples_per_s", "value": total * args.steps / (ms_resident * 1e-3), "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_resident / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": desc, "per_gpu_batch": per_gpu, "global_batch": total, "parallelism": f"dp{world}",
+                       "l2": f"no explicit flush: device memory in use by one step is {in_use.value / 1e6:.0f} MB (L2 is 126 MB); steps run back to back",
+                       "step": "CUDA-graph replay of forward+backward, one NCCL all-reduce of the flat gradients (N>1), one fused optimizer launch"},
+            "e2e": {"value": total * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": int(gpu_launches), "final_loss": loss, "clocks": clocks,
+        }
+        if roof:
+            line["roofline"] = roof
+        if cpu:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
