@@ -67,6 +67,11 @@ rt_status rt_sync(rt_ctx* ctx);
 void* rt_stream(rt_ctx* ctx);                                                        /* the cudaStream_t */
 rt_status rt_mem_stats(rt_ctx* ctx, int64_t* bytes_reserved, int64_t* bytes_in_use, int64_t* n_device_allocs);
 rt_status rt_kernel_launch_count(rt_ctx* ctx, int64_t* launches);                    /* kernels launched by this library so far */
+/* Synchronises and reads the device error word: kernels that wait on barriers give up after a bounded
+ * number of polls, record a code there and return; non-zero -> RT_ERR_TIMEOUT (and the word is cleared). */
+rt_status rt_device_status(rt_ctx* ctx, int* code);
+/* 1 (default): large contractions run on the tcgen05 3xTF32 tensor-core kernels; 0: exact FP32 kernels only. */
+rt_status rt_set_tensor_cores(rt_ctx* ctx, int enable);
 
 /* CUDA-graph capture of a fixed call sequence (one training step). */
 rt_status rt_graph_begin(rt_ctx* ctx);

@@ -15,6 +15,8 @@
 
 rt_status rt_sum_axis_internal(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out,
                                float scale);
+rt_status rt_gemm_tc_internal(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, int64_t n, int64_t k, const float* a,
+                              int64_t lda, const float* b, int64_t ldb, float* c, int64_t ldc, int accumulate);
 
 namespace {
 
@@ -448,6 +450,10 @@ rt_status rt_gemm(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, int64_t n, i
   if (lda < (trans_a ? m : k) || ldb < (trans_b ? k : n) || ldc < n)
     RT_FAIL(ctx, RT_ERR_SHAPE_MISMATCH, "rt_gemm: leading dimension smaller than the row length");
   bool acc = accumulate != 0;
+  if (ctx->use_tensor_cores && k >= 32 && m >= 32 && n >= 16 && m * n * k >= (1ll << 20)) {
+    rt_status st = rt_gemm_tc_internal(ctx, trans_a, trans_b, m, n, k, a, lda, b, ldb, c, ldc, accumulate);
+    if (st != RT_ERR_UNIMPLEMENTED) return st;
+  }
   if (!trans_a && !trans_b) return gemm_plain(ctx, MatA<false>{a, lda}, MatB<false>{b, ldb}, c, ldc, m, n, k, acc, true);
   if (!trans_a && trans_b) return gemm_plain(ctx, MatA<false>{a, lda}, MatB<true>{b, ldb}, c, ldc, m, n, k, acc, true);
   if (trans_a && !trans_b) return gemm_plain(ctx, MatA<true>{a, lda}, MatB<false>{b, ldb}, c, ldc, m, n, k, acc, true);

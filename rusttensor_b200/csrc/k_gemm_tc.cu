@@ -1,0 +1,418 @@
+// Dense contractions on the 5th-generation tensor cores (tcgen05) with 3xTF32 emulation
+// of fp32: every fp32 operand is split as a = hi + lo (hi = a with the low 13 mantissa
+// bits cleared, lo = a - hi, exact), and a*b is accumulated as hi*hi + hi*lo + lo*hi in an
+// fp32 accumulator held in tensor memory (TMEM).  The dropped lo*lo term and the rounding
+// of lo to TF32 are O(2^-21) relative, i.e. fp32-level accuracy.
+//
+// One CTA computes one 128 x BN output tile (optionally one K-split of it):
+//   * 8 producer warps gather the operand tiles straight from global memory through a
+//     loader functor (plain matrices in either orientation, or the implicit-GEMM views of
+//     a convolution: no im2col buffer exists), split them into hi / lo and store both into
+//     shared memory in the K-major, non-swizzled UMMA core-matrix layout (8 rows x 16 bytes
+//     per core matrix; the stride between 8-row groups is padded by 16 bytes so that the
+//     128-bit stores of both the K-contiguous and the transposing path are conflict free);
+//   * one thread of a ninth warp issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8), three per
+//     K-step, and signals stage reuse / accumulator completion with tcgen05.commit;
+//   * the producer warps then read the accumulator with tcgen05.ld and write the result.
+// Stages are handed over with mbarriers.  Every wait is bounded: on expiry the kernel
+// records an error code in the context's status word, skips the rest of its work, still
+// frees its TMEM columns and returns.
+#include "rt_internal.cuh"
+
+rt_status rt_sum_axis_internal(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out,
+                               float scale);
+
+namespace tc {
+
+constexpr int BM = 128;          // UMMA M
+constexpr int BK = 32;           // fp32 elements per stage along K (4 UMMA K-steps of 8)
+constexpr int kProducerWarps = 8;
+constexpr int kThreads = (kProducerWarps + 1) * 32;
+constexpr uint32_t LBO = 128;    // bytes between core matrices along K
+constexpr uint32_t SBO = (BK / 4) * 128 + 16;  // bytes between 8-row groups (padded: SBO/16 is odd)
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__host__ __device__ constexpr uint32_t tile_bytes(int rows) { return (uint32_t)(rows / 8) * SBO; }
+
+// ---- PTX wrappers ----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (and records `code`) when the barrier never completes.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try(bar, parity)) return true;
+    if (i > 64) __nanosleep(64);
+  }
+  atomicCAS(status, 0, code);
+  return false;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor: K-major, no swizzle, LBO / SBO as above, descriptor version 1.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((LBO >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((SBO >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+// Instruction descriptor: D = F32, A = B = TF32, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void split4(const float (&v)[4], float4& hi, float4& lo) {
+  float h[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __uint_as_float(__float_as_uint(v[i]) & 0xFFFFE000u);
+  hi = make_float4(h[0], h[1], h[2], h[3]);
+  lo = make_float4(v[0] - h[0], v[1] - h[1], v[2] - h[2], v[3] - h[3]);
+}
+
+// ---- operand loaders -----------------------------------------------------------------------
+// Rows are the M (A operand) or N (B operand) index.  kContigK loaders return 4 consecutive k
+// of one row; the others return 4 consecutive rows of one k.  Out-of-range elements are 0.
+struct MatK {  // element(row, k) = p[row * ld + k]
+  static constexpr bool kContigK = true;
+  const float* p;
+  int64_t ld;
+  int rows;
+  bool vec;  // base and ld allow 16-byte loads
+  __device__ __forceinline__ void load_k4(int row, int k0, int kend, float (&v)[4]) const {
+    if (row >= rows) {
+      v[0] = v[1] = v[2] = v[3] = 0.f;
+      return;
+    }
+    const float* q = p + (int64_t)row * ld + k0;
+    if (vec && k0 + 3 < kend) {
+      float4 t = __ldg(reinterpret_cast<const float4*>(q));
+      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = (k0 + i < kend) ? __ldg(q + i) : 0.f;
+    }
+  }
+};
+struct MatMN {  // element(row, k) = p[k * ld + row]
+  static constexpr bool kContigK = false;
+  const float* p;
+  int64_t ld;
+  int rows;
+  bool vec;
+  __device__ __forceinline__ void load_r4(int r0, int k, int kend, float (&v)[4]) const {
+    if (k >= kend || r0 >= rows) {
+      v[0] = v[1] = v[2] = v[3] = 0.f;
+      return;
+    }
+    const float* q = p + (int64_t)k * ld + r0;
+    if (vec && r0 + 3 < rows) {
+      float4 t = __ldg(reinterpret_cast<const float4*>(q));
+      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[i] = (r0 + i < rows) ? __ldg(q + i) : 0.f;
+    }
+  }
+};
+
+// ---- epilogues -------------------------------------------------------------------------------
+struct PlainOut {  // c[z * split_stride + m * ld + n]
+  float* c;
+  int64_t ld, split_stride;
+  int M, N;
+  bool accumulate;
+  __device__ __forceinline__ void store32(int m, int n0, const float (&v)[32], int z) const {
+    if (m >= M) return;
+    float* q = c + z * split_stride + (int64_t)m * ld + n0;
+    bool vec4 = (n0 + 31 < N) && ((reinterpret_cast<uintptr_t>(q) & 15) == 0);
+    if (vec4 && !accumulate) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(q + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (n0 + j < N) q[j] = accumulate ? q[j] + v[j] : v[j];
+    }
+  }
+};
+
+// Stores one operand tile (ROWS x BK) as hi and lo into shared memory.
+template <int ROWS, class L>
+__device__ __forceinline__ void produce_tile(const L& ld, int row0, int k0, int kend, char* hi, char* lo, int warp, int lane) {
+  if constexpr (L::kContigK) {
+    // item = (row group of 8, row in group, group of 8 k): lanes run along rows so that each
+    // quarter-warp writes one whole 128-byte core matrix (conflict free); each lane reads 32 B.
+    const int r8 = lane & 7, kg = lane >> 3;
+#pragma unroll
+    for (int rg = warp; rg < ROWS / 8; rg += kProducerWarps) {
+      const int row = rg * 8 + r8;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float v[4];
+        ld.load_k4(row0 + row, k0 + kg * 8 + h * 4, kend, v);
+        float4 vh, vl;
+        split4(v, vh, vl);
+        const uint32_t off = (uint32_t)rg * SBO + (uint32_t)(kg * 2 + h) * LBO + (uint32_t)r8 * 16;
+        *reinterpret_cast<float4*>(hi + off) = vh;
+        *reinterpret_cast<float4*>(lo + off) = vl;
+      }
+    }
+  } else {
+    // item = (quad of rows, quad of k): a 4x4 block is loaded as four row-vectors, transposed in
+    // registers and written as four 16-byte K-vectors.
+#pragma unroll
+    for (int item = warp * 32 + lane; item < (ROWS / 4) * (BK / 4); item += kProducerWarps * 32) {
+      const int rq = item % (ROWS / 4), kq = item / (ROWS / 4);
+      float t[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ld.load_r4(row0 + rq * 4, k0 + kq * 4 + i, kend, t[i]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v[4] = {t[0][i], t[1][i], t[2][i], t[3][i]};
+        float4 vh, vl;
+        split4(v, vh, vl);
+        const int row = rq * 4 + i;
+        const uint32_t off = (uint32_t)(row >> 3) * SBO + (uint32_t)kq * LBO + (uint32_t)(row & 7) * 16;
+        *reinterpret_cast<float4*>(hi + off) = vh;
+        *reinterpret_cast<float4*>(lo + off) = vl;
+      }
+    }
+  }
+}
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr uint32_t a_bytes = tile_bytes(BM), b_bytes = tile_bytes(BN);
+  static constexpr uint32_t stage_bytes = 2 * a_bytes + 2 * b_bytes;  // A hi, A lo, B hi, B lo
+  static constexpr uint32_t bar_offset = STAGES * stage_bytes;
+  static constexpr uint32_t total = bar_offset + (2 * STAGES + 1) * 8 + 16;
+};
+
+template <int BN, int STAGES, class LA, class LB, class EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_gemm_kernel(const LA la, const LB lb, const EPI epi, int K, int k_per_split, int* status) {
+  extern __shared__ __align__(128) char smem[];
+  using SL = SmemLayout<BN, STAGES>;
+  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int kbeg = blockIdx.z * k_per_split;
+  const int kend = min(K, kbeg + k_per_split);
+  const int nkb = (kend - kbeg + BK - 1) / BK;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bars = smem_base + SL::bar_offset;  // full[s], empty[s], acc
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SL::bar_offset + (2 * STAGES + 1) * 8);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bars + 8 * s, kProducerWarps);
+      mbar_init(bars + 8 * (STAGES + s), 1);
+    }
+    mbar_init(bars + 8 * (2 * STAGES), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kProducerWarps) tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  bool ok = true;
+  if (warp < kProducerWarps) {
+    // ---------------- producers ----------------
+    for (int it = 0; it < nkb && ok; ++it) {
+      const int s = it % STAGES;
+      if (it >= STAGES) ok = mbar_wait(bars + 8 * (STAGES + s), ((it / STAGES) - 1) & 1, status, 1);
+      if (!ok) break;
+      char* st = smem + s * SL::stage_bytes;
+      const int k0 = kbeg + it * BK;
+      produce_tile<BM>(la, m0, k0, kend, st, st + SL::a_bytes, warp, lane);
+      produce_tile<BN>(lb, n0, k0, kend, st + 2 * SL::a_bytes, st + 2 * SL::a_bytes + SL::b_bytes, warp, lane);
+      fence_async_smem();  // make the generic-proxy stores visible to the tensor-core (async) proxy
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8 * s);
+    }
+    // ---------------- epilogue ----------------
+    if (ok && nkb > 0) ok = mbar_wait(bars + 8 * (2 * STAGES), 0, status, 2);
+    tc_fence_after();
+    if (ok) {
+      const int quad = warp & 3, half = warp >> 2;
+      constexpr int chunks = BN / 32 > 0 ? BN / 32 : 1;
+      const int m = m0 + quad * 32 + lane;
+      for (int c = half; c < chunks; c += 2) {
+        float v[32];
+        if (nkb > 0) {
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.f;
+        }
+        epi.store32(m, n0 + c * 32, v, blockIdx.z);
+      }
+    }
+  } else if (lane == 0) {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t idesc = make_idesc(BN);
+    for (int it = 0; it < nkb && ok; ++it) {
+      const int s = it % STAGES;
+      ok = mbar_wait(bars + 8 * s, (it / STAGES) & 1, status, 3);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t a_hi = smem_base + s * SL::stage_bytes, a_lo = a_hi + SL::a_bytes;
+      const uint32_t b_hi = a_hi + 2 * SL::a_bytes, b_lo = b_hi + SL::b_bytes;
+#pragma unroll
+      for (int j = 0; j < BK / 8; ++j) {
+        const uint32_t koff = (uint32_t)j * 2 * LBO;
+        const uint64_t dah = make_desc(a_hi + koff), dal = make_desc(a_lo + koff);
+        const uint64_t dbh = make_desc(b_hi + koff), dbl = make_desc(b_lo + koff);
+        umma_tf32(tmem_base, dal, dbh, idesc, (it | j) != 0);  // small terms first
+        umma_tf32(tmem_base, dah, dbl, idesc, 1);
+        umma_tf32(tmem_base, dah, dbh, idesc, 1);
+      }
+      umma_commit(bars + 8 * (STAGES + s));  // frees the stage when these MMAs have read it
+    }
+    if (ok && nkb > 0) umma_commit(bars + 8 * (2 * STAGES));  // accumulator complete
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarps) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int BN, int STAGES, class LA, class LB, class EPI>
+rt_status launch(rt_ctx* ctx, const LA& la, const LB& lb, const EPI& epi, int M, int N, int K, int splits, int kps) {
+  using SL = SmemLayout<BN, STAGES>;
+  auto kern = tc_gemm_kernel<BN, STAGES, LA, LB, EPI>;
+  RT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SL::total));
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, splits);
+  kern<<<grid, kThreads, SL::total, ctx->stream>>>(la, lb, epi, K, kps, ctx->device_status);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+template <class LA, class LB, class EPI>
+rt_status dispatch_bn(rt_ctx* ctx, const LA& la, const LB& lb, const EPI& epi, int M, int N, int K, int splits, int kps) {
+  if (N <= 32) return launch<32, 4>(ctx, la, lb, epi, M, N, K, splits, kps);
+  if (N <= 64) return launch<64, 4>(ctx, la, lb, epi, M, N, K, splits, kps);
+  return launch<128, 3>(ctx, la, lb, epi, M, N, K, splits, kps);
+}
+
+inline int n_tiles(int64_t M, int64_t N) {
+  int bn = N <= 32 ? 32 : (N <= 64 ? 64 : 128);
+  return (int)(((M + BM - 1) / BM) * ((N + bn - 1) / bn));
+}
+
+// Split-K policy: about two CTAs per SM in flight, at least 4 K-blocks per split.
+inline void choose_split(rt_ctx* ctx, int64_t M, int64_t N, int64_t K, int* splits, int* kps) {
+  int tiles = n_tiles(M, N);
+  int64_t want = ((int64_t)ctx->sm_count * 2 + tiles - 1) / tiles;
+  int64_t max_s = K / (4 * BK);
+  if (max_s < 1) max_s = 1;
+  int64_t s = want < max_s ? want : max_s;
+  if (s < 1) s = 1;
+  if (s > 512) s = 512;
+  int64_t per = (K + s - 1) / s;
+  per = (per + BK - 1) / BK * BK;
+  s = (K + per - 1) / per;
+  *splits = (int)(s < 1 ? 1 : s);
+  *kps = (int)per;
+}
+
+// C[M,N] row-major = A x B with the given loaders; split-K through a workspace when useful.
+template <class LA, class LB>
+rt_status gemm_plain(rt_ctx* ctx, const LA& la, const LB& lb, float* c, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                     bool accumulate) {
+  int splits = 1, kps = (int)((K + BK - 1) / BK * BK);
+  if (!accumulate && ldc == N) choose_split(ctx, M, N, K, &splits, &kps);
+  if (splits == 1) {
+    PlainOut epi{c, ldc, 0, (int)M, (int)N, accumulate};
+    return dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, (int)K, 1, kps);
+  }
+  RtScratch ws(ctx);
+  rt_status st = ws.alloc(sizeof(float) * (size_t)splits * M * N);
+  if (st != RT_OK) return st;
+  PlainOut epi{ws.as<float>(), N, M * N, (int)M, (int)N, false};
+  st = dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, (int)K, splits, kps);
+  if (st != RT_OK) return st;
+  return rt_sum_axis_internal(ctx, ws.as<float>(), 1, splits, M * N, c, 1.f);
+}
+
+inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace tc
+
+// Tensor-core GEMM with the rt_gemm contract.  Returns RT_ERR_UNIMPLEMENTED when the shape is
+// not worth / not possible on this path, so that the caller can use the FP32 kernel.
+rt_status rt_gemm_tc_internal(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, int64_t n, int64_t k, const float* a,
+                              int64_t lda, const float* b, int64_t ldb, float* c, int64_t ldc, int accumulate) {
+  using namespace tc;
+  if (m <= 0 || n <= 0 || k <= 0) return RT_ERR_UNIMPLEMENTED;
+  if (m >= (1ll << 31) || n >= (1ll << 31) || k >= (1ll << 31)) return RT_ERR_UNIMPLEMENTED;
+  bool acc = accumulate != 0;
+  // A(row=m, k): not transposed -> K-contiguous; transposed ([K,M] storage) -> M-contiguous
+  // B(row=n, k): not transposed ([K,N] storage) -> N-contiguous; transposed ([N,K]) -> K-contiguous
+  if (!trans_a && !trans_b)
+    return gemm_plain(ctx, MatK{a, lda, (int)m, al16(a) && lda % 4 == 0}, MatMN{b, ldb, (int)n, al16(b) && ldb % 4 == 0}, c, ldc, m, n, k, acc);
+  if (!trans_a && trans_b)
+    return gemm_plain(ctx, MatK{a, lda, (int)m, al16(a) && lda % 4 == 0}, MatK{b, ldb, (int)n, al16(b) && ldb % 4 == 0}, c, ldc, m, n, k, acc);
+  if (trans_a && !trans_b)
+    return gemm_plain(ctx, MatMN{a, lda, (int)m, al16(a) && lda % 4 == 0}, MatMN{b, ldb, (int)n, al16(b) && ldb % 4 == 0}, c, ldc, m, n, k, acc);
+  return gemm_plain(ctx, MatMN{a, lda, (int)m, al16(a) && lda % 4 == 0}, MatK{b, ldb, (int)n, al16(b) && ldb % 4 == 0}, c, ldc, m, n, k, acc);
+}

@@ -2,6 +2,7 @@
 // gradient all-reduce of librt_b200.so.
 #include <dlfcn.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "rt_internal.cuh"
@@ -38,6 +39,13 @@ rt_status rt_ctx_create(int device, rt_ctx** out) {
   if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
   cudaEventCreate(&ctx->ev_start);
   cudaEventCreate(&ctx->ev_stop);
+  if (cudaMalloc(&ctx->device_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->device_status, 0, sizeof(int)) != cudaSuccess) {
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return RT_ERR_CUDA;
+  }
+  const char* no_tc = getenv("RT_B200_DISABLE_TENSOR_CORES");
+  if (no_tc && no_tc[0] == '1') ctx->use_tensor_cores = false;
   *out = ctx;
   return RT_OK;
 }
@@ -50,6 +58,7 @@ rt_status rt_ctx_destroy(rt_ctx* ctx) {
   for (auto& kv : ctx->free_blocks) cudaFree(kv.second);
   for (auto& kv : ctx->capture_free) cudaFree(kv.second);
   for (auto& kv : ctx->live_blocks) cudaFree(kv.first);
+  if (ctx->device_status) cudaFree(ctx->device_status);
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
   if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
   cudaStreamDestroy(ctx->stream);
@@ -206,6 +215,24 @@ rt_status rt_sync(rt_ctx* ctx) {
 }
 
 void* rt_stream(rt_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+rt_status rt_device_status(rt_ctx* ctx, int* code) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, code);
+  RT_CUDA(ctx, cudaMemcpyAsync(code, ctx->device_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  if (*code != 0) {
+    RT_CUDA(ctx, cudaMemsetAsync(ctx->device_status, 0, sizeof(int), ctx->stream));
+    RT_FAIL(ctx, RT_ERR_TIMEOUT, "a kernel gave up a bounded wait (code %d)", *code);
+  }
+  return RT_OK;
+}
+
+rt_status rt_set_tensor_cores(rt_ctx* ctx, int enable) {
+  RT_CHECK_CTX(ctx);
+  ctx->use_tensor_cores = enable != 0;
+  return RT_OK;
+}
 
 // ---- CUDA graphs -----------------------------------------------------------------
 rt_status rt_graph_begin(rt_ctx* ctx) {

@@ -33,7 +33,11 @@ struct rt_ctx {
   bool capturing = false;
   std::multimap<size_t, void*> capture_free;  // released during capture: reusable only inside it
   cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
-  // NCCL (loaded at run time, see rt_dp.cu)
+  // Error word written by kernels whose bounded waits expire (0 = none); see rt_device_status.
+  int* device_status = nullptr;
+  // Route large contractions to the tcgen05 3xTF32 kernels (k_gemm_tc.cu).
+  bool use_tensor_cores = true;
+  // NCCL (loaded at run time on first use)
   void* nccl_comm = nullptr;
   int dp_rank = 0, dp_world = 1;
 };
