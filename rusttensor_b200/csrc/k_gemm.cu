@@ -12,37 +12,20 @@
 // This file is the exact-FP32 path.  Large, tile-aligned shapes are routed to the
 // tcgen05 3xTF32 kernels in k_gemm_tc.cu by the dispatchers at the bottom.
 #include "rt_internal.cuh"
+#include "conv_geom.cuh"
 
 rt_status rt_sum_axis_internal(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out,
                                float scale);
 rt_status rt_gemm_tc_internal(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, int64_t n, int64_t k, const float* a,
                               int64_t lda, const float* b, int64_t ldb, float* c, int64_t ldc, int accumulate);
 
-namespace {
+rt_status rt_conv_forward_tc_internal(rt_ctx* ctx, const float* x, const float* w, const float* bias, const ConvGeom& g,
+                                      float* y);
+rt_status rt_conv_gather_tc_internal(rt_ctx* ctx, const float* y, const float* w, const float* bias, const ConvGeom& g,
+                                     int cm, float* out);
+rt_status rt_conv_weight_grad_tc_internal(rt_ctx* ctx, const float* x, const float* y, const ConvGeom& g, float* dw);
 
-// Division by a run-time constant through a multiply-high and a shift
-// (valid for dividends below 2^31).
-struct FastDiv {
-  uint32_t d, mul, shr;
-  void init(uint32_t div) {
-    d = div;
-    if (div <= 1) {
-      mul = 0;
-      shr = 0;
-      return;
-    }
-    uint32_t l = 0;
-    while ((1u << l) < div) ++l;
-    uint32_t p = 31 + l;
-    mul = (uint32_t)((((uint64_t)1 << p) + div - 1) / div);
-    shr = p - 32;
-  }
-  __device__ __forceinline__ uint32_t div(uint32_t n) const { return d <= 1 ? n : (__umulhi(n, mul) >> shr); }
-  __device__ __forceinline__ void divmod(uint32_t n, uint32_t& q, uint32_t& r) const {
-    q = div(n);
-    r = n - q * d;
-  }
-};
+namespace {
 
 // ---- operand loaders ---------------------------------------------------------------
 // A-side loaders implement load(m, k); B-side loaders implement load(k, n).
@@ -62,24 +45,6 @@ struct MatB {
   const float* p;
   int64_t ld;
   __device__ __forceinline__ float load(int k, int n) const { return TRANS ? __ldg(p + (int64_t)n * ld + k) : __ldg(p + (int64_t)k * ld + n); }
-};
-
-// Geometry of a convolution between a "wide" tensor X[Nb, Cx, Hx, Wx] and a "narrow"
-// tensor Y[Nb, Cy, Hy, Wy] with Hy = (Hx + 2*ph - kh)/sh + 1: y(b,cy,yo,xo) touches
-// x(b,cx, yo*sh-ph+ky, xo*sw-pw+kx).
-struct ConvGeom {
-  int Nb, Cx, Hx, Wx, Cy, Hy, Wy, kh, kw, sh, sw, ph, pw;
-  FastDiv d_khw, d_kw, d_HyWy, d_Wy, d_HxWx, d_Wx, d_sh, d_sw;
-  void finish() {
-    d_khw.init(kh * kw);
-    d_kw.init(kw);
-    d_HyWy.init(Hy * Wy);
-    d_Wy.init(Wy);
-    d_HxWx.init(Hx * Wx);
-    d_Wx.init(Wx);
-    d_sh.init(sh);
-    d_sw.init(sw);
-  }
 };
 
 // im2col view of X: rows k = (cx,ky,kx), columns n = (b,yo,xo).  Used as the B operand
@@ -371,17 +336,6 @@ rt_status gemm_plain(rt_ctx* ctx, const LA& la, const LB& lb, float* c, int64_t 
   return rt_sum_axis_internal(ctx, ws.as<float>(), 1, splits, M * N, c, 1.f);
 }
 
-ConvGeom make_geom(int64_t nb, int64_t cx, int64_t hx, int64_t wx, int64_t cy, int kh, int kw, int sh, int sw, int ph,
-                   int pw) {
-  ConvGeom g;
-  g.Nb = (int)nb; g.Cx = (int)cx; g.Hx = (int)hx; g.Wx = (int)wx; g.Cy = (int)cy;
-  g.kh = kh; g.kw = kw; g.sh = sh; g.sw = sw; g.ph = ph; g.pw = pw;
-  g.Hy = (int)((hx + 2 * ph - kh) / sh + 1);
-  g.Wy = (int)((wx + 2 * pw - kw) / sw + 1);
-  g.finish();
-  return g;
-}
-
 rt_status check_conv_args(rt_ctx* ctx, int64_t n, int64_t cin, int64_t h, int64_t w, int64_t cout, int kh, int kw, int sh,
                           int sw, int ph, int pw) {
   if (n < 0 || cin < 0 || h < 0 || w < 0 || cout < 0) RT_FAIL(ctx, RT_ERR_INVALID_INDEX, "conv: negative extent");
@@ -394,6 +348,10 @@ rt_status check_conv_args(rt_ctx* ctx, int64_t n, int64_t cin, int64_t h, int64_
 rt_status conv_forward_like(rt_ctx* ctx, const float* x, const float* w, const float* bias, const ConvGeom& g, float* y) {
   int64_t M = g.Cy, N = (int64_t)g.Nb * g.Hy * g.Wy, K = (int64_t)g.Cx * g.kh * g.kw;
   if (M == 0 || N == 0) return RT_OK;
+  if (ctx->use_tensor_cores) {
+    rt_status st = rt_conv_forward_tc_internal(ctx, x, w, bias, g, y);
+    if (st != RT_ERR_UNIMPLEMENTED) return st;
+  }
   MatA<false> la{w, K};
   Im2colB lb{x, g};
   ImageC sc{y, bias, g.Cy, g.Hy * g.Wy, {}};
@@ -404,6 +362,10 @@ rt_status conv_forward_like(rt_ctx* ctx, const float* x, const float* w, const f
 // dw[Cy, Cx*kh*kw] = sum over (b,yo,xo) of y * im2col(x)
 rt_status conv_weight_grad_like(rt_ctx* ctx, const float* x, const float* y, const ConvGeom& g, float* dw) {
   int64_t M = g.Cy, N = (int64_t)g.Cx * g.kh * g.kw, K = (int64_t)g.Nb * g.Hy * g.Wy;
+  if (ctx->use_tensor_cores && M > 0 && N > 0) {
+    rt_status st = rt_conv_weight_grad_tc_internal(ctx, x, y, g, dw);
+    if (st != RT_ERR_UNIMPLEMENTED) return st;
+  }
   NarrowA la{y, g};
   Im2colK lb{x, g};
   return gemm_plain(ctx, la, lb, dw, N, M, N, K, false, true);
@@ -414,6 +376,10 @@ rt_status conv_gather_like(rt_ctx* ctx, const float* y, const float* w, const fl
                            float* out) {
   int64_t M = cm, N = (int64_t)g.Nb * g.Hx * g.Wx, K = (int64_t)g.Cy * g.kh * g.kw;
   if (M == 0 || N == 0) return RT_OK;
+  if (ctx->use_tensor_cores) {
+    rt_status st = rt_conv_gather_tc_internal(ctx, y, w, bias, g, cm, out);
+    if (st != RT_ERR_UNIMPLEMENTED) return st;
+  }
   WeightSecondIndexA la{w, cm, g};
   GatherB lb{y, g};
   ImageC sc{out, bias, cm, g.Hx * g.Wx, {}};

@@ -18,6 +18,7 @@
 // records an error code in the context's status word, skips the rest of its work, still
 // frees its TMEM columns and returns.
 #include "rt_internal.cuh"
+#include "conv_geom.cuh"
 
 rt_status rt_sum_axis_internal(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out,
                                float scale);
@@ -190,6 +191,213 @@ struct PlainOut {  // c[z * split_stride + m * ld + n]
   }
 };
 
+
+// ---- implicit-GEMM views of a convolution -----------------------------------------------------
+// Geometry (conv_geom.cuh): wide tensor X[Nb,Cx,Hx,Wx], narrow tensor Y[Nb,Cy,Hy,Wy],
+// y(b,cy,yo,xo) touches x(b,cx,yo*sh-ph+ky,xo*sw-pw+kx).
+
+// Rows = output pixels (b,yo,xo), k = (cx,ky,kx): the im2col matrix of X, pixel-contiguous.
+struct Im2colRows {
+  static constexpr bool kContigK = false;
+  const float* x;
+  ConvGeom g;
+  int rows;
+  __device__ __forceinline__ void load_r4(int r0, int k, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (k >= kend || r0 >= rows) return;
+    uint32_t cx, r, ky, kx, b, p, yo, xo;
+    g.d_khw.divmod(k, cx, r);
+    g.d_kw.divmod(r, ky, kx);
+    g.d_HyWy.divmod(r0, b, p);
+    g.d_Wy.divmod(p, yo, xo);
+    if ((int)xo + 3 < g.Wy && r0 + 3 < rows) {  // four pixels of one output row
+      int iy = (int)(yo * g.sh + ky) - g.ph;
+      if (iy < 0 || iy >= g.Hx) return;
+      const float* q = x + (((int64_t)b * g.Cx + cx) * g.Hx + iy) * g.Wx;
+      int ix = (int)(xo * g.sw + kx) - g.pw;
+#pragma unroll
+      for (int i = 0; i < 4; ++i, ix += g.sw)
+        if (ix >= 0 && ix < g.Wx) v[i] = __ldg(q + ix);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int rr = r0 + i;
+        if (rr >= rows) break;
+        g.d_HyWy.divmod(rr, b, p);
+        g.d_Wy.divmod(p, yo, xo);
+        int iy = (int)(yo * g.sh + ky) - g.ph, ix = (int)(xo * g.sw + kx) - g.pw;
+        if (iy >= 0 && iy < g.Hx && ix >= 0 && ix < g.Wx) v[i] = __ldg(x + (((int64_t)b * g.Cx + cx) * g.Hx + iy) * g.Wx + ix);
+      }
+    }
+  }
+};
+
+// Rows = input pixels (b,iy,ix), k = (cy,ky,kx): the gather of Y used by the input gradient and
+// by the transposed convolution; element = y(b,cy,(iy+ph-ky)/sh,(ix+pw-kx)/sw) when exact and in range.
+struct GatherRows {
+  static constexpr bool kContigK = false;
+  const float* y;
+  ConvGeom g;
+  int rows;
+  __device__ __forceinline__ float one(uint32_t b, uint32_t cy, int iy, int ix, int ky, int kx) const {
+    int ty = iy + g.ph - ky, tx = ix + g.pw - kx;
+    if (ty < 0 || tx < 0) return 0.f;
+    uint32_t yo, ry, xo, rx;
+    g.d_sh.divmod(ty, yo, ry);
+    g.d_sw.divmod(tx, xo, rx);
+    if (ry != 0 || rx != 0 || (int)yo >= g.Hy || (int)xo >= g.Wy) return 0.f;
+    return __ldg(y + (((int64_t)b * g.Cy + cy) * g.Hy + yo) * g.Wy + xo);
+  }
+  __device__ __forceinline__ void load_r4(int r0, int k, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (k >= kend || r0 >= rows) return;
+    uint32_t cy, r, ky, kx, b, p, iy, ix;
+    g.d_khw.divmod(k, cy, r);
+    g.d_kw.divmod(r, ky, kx);
+    g.d_HxWx.divmod(r0, b, p);
+    g.d_Wx.divmod(p, iy, ix);
+    if ((int)ix + 3 < g.Wx && r0 + 3 < rows) {
+      if (g.sh == 1 && g.sw == 1) {  // unit stride: one row of Y, consecutive columns
+        int yo = (int)iy + g.ph - (int)ky;
+        if (yo < 0 || yo >= g.Hy) return;
+        const float* q = y + (((int64_t)b * g.Cy + cy) * g.Hy + yo) * g.Wy;
+        int xo = (int)ix + g.pw - (int)kx;
+#pragma unroll
+        for (int i = 0; i < 4; ++i, ++xo)
+          if (xo >= 0 && xo < g.Wy) v[i] = __ldg(q + xo);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = one(b, cy, (int)iy, (int)ix + i, (int)ky, (int)kx);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int rr = r0 + i;
+        if (rr >= rows) break;
+        g.d_HxWx.divmod(rr, b, p);
+        g.d_Wx.divmod(p, iy, ix);
+        v[i] = one(b, cy, (int)iy, (int)ix, (int)ky, (int)kx);
+      }
+    }
+  }
+};
+
+// Rows = cm, k = (cy, tap): weights stored [Cy, Cm, kh, kw] read with the second index as the row.
+struct WeightSecondRows {
+  static constexpr bool kContigK = true;
+  const float* w;
+  ConvGeom g;
+  int rows;  // Cm
+  __device__ __forceinline__ void load_k4(int row, int k0, int kend, float (&v)[4]) const {
+    const int khw = g.kh * g.kw;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int k = k0 + i;
+      if (row < rows && k < kend) {
+        uint32_t cy, r;
+        g.d_khw.divmod(k, cy, r);
+        v[i] = __ldg(w + ((int64_t)cy * rows + row) * khw + r);
+      } else {
+        v[i] = 0.f;
+      }
+    }
+  }
+};
+
+// Rows = (cx,ky,kx), k = output pixels (b,yo,xo): the im2col matrix with the pixel index as the
+// reduction (weight gradient).
+struct Im2colK4 {
+  static constexpr bool kContigK = true;
+  const float* x;
+  ConvGeom g;
+  int rows;  // Cx*kh*kw
+  __device__ __forceinline__ void load_k4(int row, int k0, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (row >= rows || k0 >= kend) return;
+    uint32_t cx, r, ky, kx, b, p, yo, xo;
+    g.d_khw.divmod(row, cx, r);
+    g.d_kw.divmod(r, ky, kx);
+    g.d_HyWy.divmod(k0, b, p);
+    g.d_Wy.divmod(p, yo, xo);
+    if ((int)xo + 3 < g.Wy && k0 + 3 < kend) {
+      int iy = (int)(yo * g.sh + ky) - g.ph;
+      if (iy < 0 || iy >= g.Hx) return;
+      const float* q = x + (((int64_t)b * g.Cx + cx) * g.Hx + iy) * g.Wx;
+      int ix = (int)(xo * g.sw + kx) - g.pw;
+#pragma unroll
+      for (int i = 0; i < 4; ++i, ix += g.sw)
+        if (ix >= 0 && ix < g.Wx) v[i] = __ldg(q + ix);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int kk = k0 + i;
+        if (kk >= kend) break;
+        g.d_HyWy.divmod(kk, b, p);
+        g.d_Wy.divmod(p, yo, xo);
+        int iy = (int)(yo * g.sh + ky) - g.ph, ix = (int)(xo * g.sw + kx) - g.pw;
+        if (iy >= 0 && iy < g.Hx && ix >= 0 && ix < g.Wx) v[i] = __ldg(x + (((int64_t)b * g.Cx + cx) * g.Hx + iy) * g.Wx + ix);
+      }
+    }
+  }
+};
+
+// Rows = cy, k = pixels (b,p): the narrow tensor with the pixel index as the reduction.
+struct NarrowK4 {
+  static constexpr bool kContigK = true;
+  const float* y;
+  ConvGeom g;
+  int rows;  // Cy
+  bool vec;  // Hy*Wy % 4 == 0 and y is 16-byte aligned
+  __device__ __forceinline__ void load_k4(int row, int k0, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (row >= rows || k0 >= kend) return;
+    const int hw = g.Hy * g.Wy;
+    uint32_t b, p;
+    g.d_HyWy.divmod(k0, b, p);
+    if (vec && k0 + 3 < kend) {  // k0 % 4 == 0 and hw % 4 == 0: the four pixels share one image
+      float4 t = __ldg(reinterpret_cast<const float4*>(y + ((int64_t)b * g.Cy + row) * hw + p));
+      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        int kk = k0 + i;
+        if (kk >= kend) break;
+        g.d_HyWy.divmod(kk, b, p);
+        v[i] = __ldg(y + ((int64_t)b * g.Cy + row) * hw + p);
+      }
+    }
+  }
+};
+
+struct ImageOut {  // out[b, n, p] for row m = (b,p), optional per-channel bias
+  float* out;
+  const float* bias;
+  int C, HW, M;
+  FastDiv d_HW;
+  __device__ __forceinline__ void store32(int m, int n0, const float (&v)[32], int) const {
+    if (m >= M) return;
+    uint32_t b, p;
+    d_HW.divmod(m, b, p);
+    float* q = out + ((int64_t)b * C + n0) * HW + p;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (n0 + j < C) q[(int64_t)j * HW] = bias ? v[j] + __ldg(bias + n0 + j) : v[j];
+  }
+};
+
+struct TransposedOut {  // c[z * split_stride + n * ld + m]: the tile is written transposed
+  float* c;
+  int64_t ld, split_stride;
+  int M, N;
+  __device__ __forceinline__ void store32(int m, int n0, const float (&v)[32], int z) const {
+    if (m >= M) return;
+    float* q = c + z * split_stride + (int64_t)n0 * ld + m;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (n0 + j < N) q[(int64_t)j * ld] = v[j];
+  }
+};
+
 // Stores one operand tile (ROWS x BK) as hi and lo into shared memory.
 template <int ROWS, class L>
 __device__ __forceinline__ void produce_tile(const L& ld, int row0, int k0, int kend, char* hi, char* lo, int warp, int lane) {
@@ -247,7 +455,14 @@ __global__ void __launch_bounds__(kThreads, 1)
 tc_gemm_kernel(const LA la, const LB lb, const EPI epi, int K, int k_per_split, int* status) {
   extern __shared__ __align__(128) char smem[];
   using SL = SmemLayout<BN, STAGES>;
-  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+  // Four accumulators per tile, BN columns each.  The tensor core adds every K=8 partial product
+  // into the fp32 accumulator with truncation, an error that grows linearly with the number of
+  // additions and with the accumulator's magnitude; spreading the hi*hi products round-robin over
+  // three accumulators and keeping the small cross terms (hi*lo, lo*hi) in a fourth one cuts that
+  // error several times.  The epilogue adds the four in round-to-nearest fp32.
+  constexpr int kAccs = 4;
+  constexpr uint32_t kTmemCols = kAccs * BN;
+  static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM allocation must be a power of two <= 512");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int kbeg = blockIdx.z * k_per_split;
@@ -297,7 +512,15 @@ tc_gemm_kernel(const LA la, const LB lb, const EPI epi, int K, int k_per_split, 
       for (int c = half; c < chunks; c += 2) {
         float v[32];
         if (nkb > 0) {
-          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), v);
+          const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
+          tmem_ld32(t0, v);  // cross terms
+#pragma unroll
+          for (int a = 1; a < kAccs; ++a) {
+            float u[32];
+            tmem_ld32(t0 + (uint32_t)(a * BN), u);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += u[j];
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
@@ -320,9 +543,10 @@ tc_gemm_kernel(const LA la, const LB lb, const EPI epi, int K, int k_per_split, 
         const uint32_t koff = (uint32_t)j * 2 * LBO;
         const uint64_t dah = make_desc(a_hi + koff), dal = make_desc(a_lo + koff);
         const uint64_t dbh = make_desc(b_hi + koff), dbl = make_desc(b_lo + koff);
-        umma_tf32(tmem_base, dal, dbh, idesc, (it | j) != 0);  // small terms first
+        const int t = it * (BK / 8) + j;  // K-step counter of this tile
+        umma_tf32(tmem_base, dal, dbh, idesc, t != 0);  // cross terms -> accumulator 0
         umma_tf32(tmem_base, dah, dbl, idesc, 1);
-        umma_tf32(tmem_base, dah, dbh, idesc, 1);
+        umma_tf32(tmem_base + (uint32_t)((1 + t % 3) * BN), dah, dbh, idesc, t >= 3);  // hi*hi -> accumulators 1..3
       }
       umma_commit(bars + 8 * (STAGES + s));  // frees the stage when these MMAs have read it
     }
@@ -415,4 +639,60 @@ rt_status rt_gemm_tc_internal(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, 
   if (trans_a && !trans_b)
     return gemm_plain(ctx, MatMN{a, lda, (int)m, al16(a) && lda % 4 == 0}, MatMN{b, ldb, (int)n, al16(b) && ldb % 4 == 0}, c, ldc, m, n, k, acc);
   return gemm_plain(ctx, MatMN{a, lda, (int)m, al16(a) && lda % 4 == 0}, MatK{b, ldb, (int)n, al16(b) && ldb % 4 == 0}, c, ldc, m, n, k, acc);
+}
+
+// y[Nb,Cy,Hy,Wy] = conv(x, w[Cy,Cx,kh,kw]) (+bias) on the tensor cores.
+rt_status rt_conv_forward_tc_internal(rt_ctx* ctx, const float* x, const float* w, const float* bias, const ConvGeom& g,
+                                      float* y) {
+  using namespace tc;
+  int64_t M = (int64_t)g.Nb * g.Hy * g.Wy, N = g.Cy, K = (int64_t)g.Cx * g.kh * g.kw;
+  if (M <= 0 || N <= 0 || K < 8 || M >= (1ll << 31) || (int64_t)g.Nb * g.Cx * g.Hx * g.Wx >= (1ll << 31)) return RT_ERR_UNIMPLEMENTED;
+  Im2colRows la{x, g, (int)M};
+  MatK lb{w, K, (int)N, al16(w) && K % 4 == 0};
+  ImageOut epi{y, bias, (int)N, g.Hy * g.Wy, (int)M, {}};
+  epi.d_HW.init(g.Hy * g.Wy);
+  return dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, (int)K, 1, (int)((K + BK - 1) / BK * BK));
+}
+
+// out[Nb,Cm,Hx,Wx] (+bias) = gather of y[Nb,Cy,Hy,Wy] with w[Cy,Cm,kh,kw] on the tensor cores
+// (input gradient of a convolution; forward of a transposed convolution).
+rt_status rt_conv_gather_tc_internal(rt_ctx* ctx, const float* y, const float* w, const float* bias, const ConvGeom& g,
+                                     int cm, float* out) {
+  using namespace tc;
+  int64_t M = (int64_t)g.Nb * g.Hx * g.Wx, N = cm, K = (int64_t)g.Cy * g.kh * g.kw;
+  if (M <= 0 || N <= 0 || K < 8 || M >= (1ll << 31) || (int64_t)g.Nb * g.Cy * g.Hy * g.Wy >= (1ll << 31)) return RT_ERR_UNIMPLEMENTED;
+  GatherRows la{y, g, (int)M};
+  WeightSecondRows lb{w, g, cm};
+  ImageOut epi{out, bias, cm, g.Hx * g.Wx, (int)M, {}};
+  epi.d_HW.init(g.Hx * g.Wx);
+  return dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, (int)K, 1, (int)((K + BK - 1) / BK * BK));
+}
+
+// dw[Cy, Cx*kh*kw] = sum over pixels of y * im2col(x) on the tensor cores.  The product is computed
+// transposed (rows = taps, columns = Cy) so that the long side fills the 128-row tile, split along
+// the pixel axis, written transposed into a workspace and summed deterministically.
+rt_status rt_conv_weight_grad_tc_internal(rt_ctx* ctx, const float* x, const float* y, const ConvGeom& g, float* dw) {
+  using namespace tc;
+  int64_t M = (int64_t)g.Cx * g.kh * g.kw, N = g.Cy, K = (int64_t)g.Nb * g.Hy * g.Wy;
+  if (M <= 0 || N <= 0 || K < 64 || K >= (1ll << 31) || (int64_t)g.Nb * g.Cx * g.Hx * g.Wx >= (1ll << 31)) return RT_ERR_UNIMPLEMENTED;
+  int splits, kps;
+  choose_split(ctx, M, N, K, &splits, &kps);
+  // keep each accumulation chain short: at most 2048 reduction steps per split
+  if (kps > 2048) {
+    kps = 2048;
+    splits = (int)((K + kps - 1) / kps);
+  }
+  Im2colK4 la{x, g, (int)M};
+  NarrowK4 lb{y, g, (int)N, al16(y) && (g.Hy * g.Wy) % 4 == 0};
+  if (splits == 1) {
+    TransposedOut epi{dw, M, 0, (int)M, (int)N};
+    return dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, (int)K, 1, kps);
+  }
+  RtScratch ws(ctx);
+  rt_status st = ws.alloc(sizeof(float) * (size_t)splits * M * N);
+  if (st != RT_OK) return st;
+  TransposedOut epi{ws.as<float>(), M, M * N, (int)M, (int)N};
+  st = dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, (int)K, splits, kps);
+  if (st != RT_OK) return st;
+  return rt_sum_axis_internal(ctx, ws.as<float>(), 1, splits, M * N, dw, 1.f);
 }

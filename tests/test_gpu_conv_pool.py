@@ -15,12 +15,13 @@ TOL = 1e-4
 CONV = [
     (2, 3, 8, 8, 4, 3, (1, 1), (1, 1)), (1, 1, 7, 5, 2, 3, (1, 1), (0, 0)), (2, 2, 9, 9, 3, 3, (2, 2), (1, 1)),
     (1, 4, 6, 6, 5, 5, (1, 1), (2, 2)), (4, 1, 28, 28, 32, 3, (1, 1), (1, 1)), (3, 32, 14, 14, 64, 3, (1, 1), (1, 1)),
-    (2, 5, 11, 13, 7, 3, (2, 1), (0, 1)), (1, 64, 12, 12, 128, 3, (1, 1), (1, 1)),
+    (2, 5, 11, 13, 7, 3, (2, 1), (0, 1)), (1, 64, 12, 12, 128, 3, (1, 1), (1, 1)), (16, 32, 14, 14, 64, 3, (1, 1), (1, 1)),
+    (8, 1, 28, 28, 32, 3, (1, 1), (1, 1)), (2, 64, 20, 20, 128, 3, (1, 1), (1, 1)), (3, 8, 10, 9, 16, 5, (1, 1), (2, 2)),
 ]
 
 
 @pytest.mark.parametrize("n,cin,h,w,cout,k,stride,pad", CONV, ids=str)
-def test_conv2d_forward_backward(oracle_engine, gpu_engine, n, cin, h, w, cout, k, stride, pad):
+def test_conv2d_forward_backward(oracle_engine, gpu_engine, contraction_path, n, cin, h, w, cout, k, stride, pad):
     r = rng(41)
     x = r.standard_normal((n, cin, h, w)).astype(np.float32)
     wt = (r.standard_normal((cout, cin, k, k)) / np.sqrt(cin * k * k)).astype(np.float32)
@@ -46,7 +47,7 @@ def test_conv2d_forward_backward(oracle_engine, gpu_engine, n, cin, h, w, cout, 
     assert_close(res["gpu"][2], dw64, TOL, "conv2d dW vs float64")
 
 
-def test_conv2d_without_bias_and_frozen_input(oracle_engine, gpu_engine):
+def test_conv2d_without_bias_and_frozen_input(oracle_engine, gpu_engine, contraction_path):
     r = rng(43)
     x = r.standard_normal((2, 3, 6, 6)).astype(np.float32)
     w = r.standard_normal((4, 3, 3, 3)).astype(np.float32)
@@ -61,11 +62,12 @@ def test_conv2d_without_bias_and_frozen_input(oracle_engine, gpu_engine):
 
 
 CONVT = [(2, 3, 4, 4, 2, 4, (2, 2), (1, 1)), (1, 2, 5, 3, 3, 3, (1, 1), (0, 0)), (1, 2, 3, 3, 2, 3, (2, 2), (0, 0)),
-         (2, 1, 4, 4, 1, 2, (2, 2), (0, 0)), (2, 16, 7, 7, 8, 4, (2, 2), (1, 1)), (1, 128, 6, 6, 64, 4, (2, 2), (1, 1))]
+         (2, 1, 4, 4, 1, 2, (2, 2), (0, 0)), (2, 16, 7, 7, 8, 4, (2, 2), (1, 1)), (1, 128, 6, 6, 64, 4, (2, 2), (1, 1)),
+         (4, 128, 14, 14, 64, 4, (2, 2), (1, 1)), (2, 6, 5, 7, 4, 3, (1, 2), (1, 0))]
 
 
 @pytest.mark.parametrize("n,cin,h,w,cout,k,stride,pad", CONVT, ids=str)
-def test_conv2d_transpose_forward_backward(oracle_engine, gpu_engine, n, cin, h, w, cout, k, stride, pad):
+def test_conv2d_transpose_forward_backward(oracle_engine, gpu_engine, contraction_path, n, cin, h, w, cout, k, stride, pad):
     r = rng(44)
     x = r.standard_normal((n, cin, h, w)).astype(np.float32)
     wt = (r.standard_normal((cin, cout, k, k)) / np.sqrt(cin * k * k)).astype(np.float32)
@@ -117,7 +119,7 @@ MATMUL = [(2, 2, 2), (64, 784, 128), (64, 128, 10), (256, 3136, 128), (64, 577, 
 
 
 @pytest.mark.parametrize("m,k,n", MATMUL, ids=str)
-def test_matmul_forward_backward(oracle_engine, gpu_engine, m, k, n):
+def test_matmul_forward_backward(oracle_engine, gpu_engine, contraction_path, m, k, n):
     r = rng(48)
     a = r.standard_normal((m, k)).astype(np.float32)
     b = (r.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32)

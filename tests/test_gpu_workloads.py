@@ -58,7 +58,7 @@ def compare_runs(cpu, gpu, what, tol=TOL, lr=0.0):
 
 
 @pytest.mark.parametrize("config", [1, 2, 3, 4, 5])
-def test_small_workload_matches_oracle(oracle_engine, gpu_engine, config):
+def test_small_workload_matches_oracle(oracle_engine, gpu_engine, contraction_path, config):
     dims = SMALL[config]
     params, inputs = workload_data(config, dims, seed=0)
     # conv input gradients: the CUDA kernels are mathematically correct, so configs whose
