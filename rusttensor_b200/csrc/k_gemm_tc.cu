@@ -125,26 +125,30 @@ __device__ __forceinline__ void split4(const float (&v)[4], float4& hi, float4& 
 }
 
 // ---- operand loaders -----------------------------------------------------------------------
-// Rows are the M (A operand) or N (B operand) index.  kContigK loaders return 4 consecutive k
-// of one row; the others return 4 consecutive rows of one k.  Out-of-range elements are 0.
+// Rows are the M (A operand) or N (B operand) index.  A producer thread works on the same rows
+// for the whole K loop, so everything that depends only on the row is decoded once into a small
+// State (prep_*); the per-K-block fetch then costs a handful of integer instructions per load.
+//   kContigK loaders:  State prep_row(row);        fetch_k4(state, k0, kend, v): 4 consecutive k
+//   other loaders:      State prep_quad(first_row); fetch_r4(state, k, kend, v):  4 consecutive rows
+// Out-of-range elements read as 0.
 struct MatK {  // element(row, k) = p[row * ld + k]
   static constexpr bool kContigK = true;
   const float* p;
   int64_t ld;
   int rows;
   bool vec;  // base and ld allow 16-byte loads
-  __device__ __forceinline__ void load_k4(int row, int k0, int kend, float (&v)[4]) const {
-    if (row >= rows) {
-      v[0] = v[1] = v[2] = v[3] = 0.f;
-      return;
-    }
-    const float* q = p + (int64_t)row * ld + k0;
+  struct State { const float* q; };
+  __device__ __forceinline__ State prep_row(int row) const { return State{row < rows ? p + (int64_t)row * ld : nullptr}; }
+  __device__ __forceinline__ void fetch_k4(const State& s, int k0, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (!s.q || k0 >= kend) return;
     if (vec && k0 + 3 < kend) {
-      float4 t = __ldg(reinterpret_cast<const float4*>(q));
+      float4 t = __ldg(reinterpret_cast<const float4*>(s.q + k0));
       v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
     } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = (k0 + i < kend) ? __ldg(q + i) : 0.f;
+      for (int i = 0; i < 4; ++i)
+        if (k0 + i < kend) v[i] = __ldg(s.q + k0 + i);
     }
   }
 };
@@ -154,18 +158,218 @@ struct MatMN {  // element(row, k) = p[k * ld + row]
   int64_t ld;
   int rows;
   bool vec;
-  __device__ __forceinline__ void load_r4(int r0, int k, int kend, float (&v)[4]) const {
-    if (k >= kend || r0 >= rows) {
-      v[0] = v[1] = v[2] = v[3] = 0.f;
-      return;
-    }
-    const float* q = p + (int64_t)k * ld + r0;
-    if (vec && r0 + 3 < rows) {
+  struct State { int r0; };
+  __device__ __forceinline__ State prep_quad(int r0) const { return State{r0}; }
+  __device__ __forceinline__ void fetch_r4(const State& s, int k, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (k >= kend || s.r0 >= rows) return;
+    const float* q = p + (int64_t)k * ld + s.r0;
+    if (vec && s.r0 + 3 < rows) {
       float4 t = __ldg(reinterpret_cast<const float4*>(q));
       v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
     } else {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = (r0 + i < rows) ? __ldg(q + i) : 0.f;
+      for (int i = 0; i < 4; ++i)
+        if (s.r0 + i < rows) v[i] = __ldg(q + i);
+    }
+  }
+};
+
+// ---- implicit-GEMM views of a convolution -----------------------------------------------------
+// Geometry (conv_geom.cuh): wide tensor X[Nb,Cx,Hx,Wx], narrow tensor Y[Nb,Cy,Hy,Wy],
+// y(b,cy,yo,xo) touches x(b,cx,yo*sh-ph+ky,xo*sw-pw+kx).  All element offsets fit in 31 bits
+// (checked by the host dispatchers).
+
+// Rows = output pixels (b,yo,xo), k = (cx,ky,kx): the im2col matrix of X, pixel-contiguous.
+struct Im2colRows {
+  static constexpr bool kContigK = false;
+  const float* x;
+  ConvGeom g;
+  int rows;
+  struct State {
+    int base[4];   // offset of x(b, 0, yo*sh-ph, xo*sw-pw) (may point outside the image)
+    int iy0[4], ix0[4];
+    int n;         // number of valid rows in the quad
+  };
+  __device__ __forceinline__ State prep_quad(int r0) const {
+    State s;
+    s.n = rows - r0 < 0 ? 0 : (rows - r0 > 4 ? 4 : rows - r0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t b = 0, p = 0, yo = 0, xo = 0;
+      if (i < s.n) {
+        g.d_HyWy.divmod(r0 + i, b, p);
+        g.d_Wy.divmod(p, yo, xo);
+      }
+      s.iy0[i] = (int)(yo * g.sh) - g.ph;
+      s.ix0[i] = (int)(xo * g.sw) - g.pw;
+      s.base[i] = ((int)b * g.Cx * g.Hx + s.iy0[i]) * g.Wx + s.ix0[i];
+    }
+    return s;
+  }
+  __device__ __forceinline__ void fetch_r4(const State& s, int k, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (k >= kend) return;
+    uint32_t cx, r, ky, kx;
+    g.d_khw.divmod(k, cx, r);
+    g.d_kw.divmod(r, ky, kx);
+    const int koff = ((int)cx * g.Hx + (int)ky) * g.Wx + (int)kx;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int iy = s.iy0[i] + (int)ky, ix = s.ix0[i] + (int)kx;
+      if (i < s.n && iy >= 0 && iy < g.Hx && ix >= 0 && ix < g.Wx) v[i] = __ldg(x + s.base[i] + koff);
+    }
+  }
+};
+
+// Rows = input pixels (b,iy,ix), k = (cy,ky,kx): the gather of Y used by the input gradient and
+// by the transposed convolution; element = y(b,cy,(iy+ph-ky)/sh,(ix+pw-kx)/sw) when exact and in range.
+struct GatherRows {
+  static constexpr bool kContigK = false;
+  const float* y;
+  ConvGeom g;
+  int rows;
+  struct State {
+    int base[4];  // offset of y(b, 0, 0, 0)
+    int ty0[4], tx0[4];  // iy + ph, ix + pw
+    int n;
+  };
+  __device__ __forceinline__ State prep_quad(int r0) const {
+    State s;
+    s.n = rows - r0 < 0 ? 0 : (rows - r0 > 4 ? 4 : rows - r0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t b = 0, p = 0, iy = 0, ix = 0;
+      if (i < s.n) {
+        g.d_HxWx.divmod(r0 + i, b, p);
+        g.d_Wx.divmod(p, iy, ix);
+      }
+      s.ty0[i] = (int)iy + g.ph;
+      s.tx0[i] = (int)ix + g.pw;
+      s.base[i] = (int)b * g.Cy * g.Hy * g.Wy;
+    }
+    return s;
+  }
+  __device__ __forceinline__ void fetch_r4(const State& s, int k, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (k >= kend) return;
+    uint32_t cy, r, ky, kx;
+    g.d_khw.divmod(k, cy, r);
+    g.d_kw.divmod(r, ky, kx);
+    const int coff = (int)cy * g.Hy * g.Wy;
+    const bool unit = g.sh == 1 && g.sw == 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      int ty = s.ty0[i] - (int)ky, tx = s.tx0[i] - (int)kx;
+      if (i >= s.n || ty < 0 || tx < 0) continue;
+      int yo = ty, xo = tx;
+      if (!unit) {
+        uint32_t q, rem;
+        g.d_sh.divmod((uint32_t)ty, q, rem);
+        if (rem) continue;
+        yo = (int)q;
+        g.d_sw.divmod((uint32_t)tx, q, rem);
+        if (rem) continue;
+        xo = (int)q;
+      }
+      if (yo < g.Hy && xo < g.Wy) v[i] = __ldg(y + s.base[i] + coff + yo * g.Wy + xo);
+    }
+  }
+};
+
+// Rows = cm, k = (cy, tap): weights stored [Cy, Cm, kh, kw] read with the second index as the row.
+struct WeightSecondRows {
+  static constexpr bool kContigK = true;
+  const float* w;
+  ConvGeom g;
+  int rows;  // Cm
+  struct State { int off; };  // row * kh*kw, or -1
+  __device__ __forceinline__ State prep_row(int row) const { return State{row < rows ? row * g.kh * g.kw : -1}; }
+  __device__ __forceinline__ void fetch_k4(const State& s, int k0, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (s.off < 0 || k0 >= kend) return;
+    const int khw = g.kh * g.kw;
+    uint32_t cy, r;
+    g.d_khw.divmod(k0, cy, r);
+    int o = (int)cy * rows * khw + s.off + (int)r, rr = (int)r;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (k0 + i < kend) v[i] = __ldg(w + o);
+      ++o;
+      if (++rr == khw) {  // next channel of the narrow tensor
+        rr = 0;
+        o += (rows - 1) * khw;
+      }
+    }
+  }
+};
+
+// Rows = (cx,ky,kx), k = output pixels (b,yo,xo): the im2col matrix with the pixel index as the
+// reduction (weight gradient).
+struct Im2colK4 {
+  static constexpr bool kContigK = true;
+  const float* x;
+  ConvGeom g;
+  int rows;  // Cx*kh*kw
+  struct State { int coff, ky, kx; };  // coff = cx*Hx*Wx + (ky-ph)*Wx + (kx-pw), or ky = -1 when out of range
+  __device__ __forceinline__ State prep_row(int row) const {
+    if (row >= rows) return State{0, -1, 0};
+    uint32_t cx, r, ky, kx;
+    g.d_khw.divmod(row, cx, r);
+    g.d_kw.divmod(r, ky, kx);
+    return State{((int)cx * g.Hx + (int)ky - g.ph) * g.Wx + (int)kx - g.pw, (int)ky, (int)kx};
+  }
+  __device__ __forceinline__ void fetch_k4(const State& s, int k0, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (s.ky < 0 || k0 >= kend) return;
+    uint32_t b, p, yo, xo;
+    g.d_HyWy.divmod(k0, b, p);
+    g.d_Wy.divmod(p, yo, xo);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (k0 + i < kend) {
+        int iy = (int)(yo * g.sh) + s.ky - g.ph, ix = (int)(xo * g.sw) + s.kx - g.pw;
+        if (iy >= 0 && iy < g.Hx && ix >= 0 && ix < g.Wx)
+          v[i] = __ldg(x + ((int)b * g.Cx * g.Hx + (int)(yo * g.sh)) * g.Wx + (int)(xo * g.sw) + s.coff);
+      }
+      if ((int)++xo == g.Wy) {  // next output row / next image
+        xo = 0;
+        if ((int)++yo == g.Hy) {
+          yo = 0;
+          ++b;
+        }
+      }
+    }
+  }
+};
+
+// Rows = cy, k = pixels (b,p): the narrow tensor with the pixel index as the reduction.
+struct NarrowK4 {
+  static constexpr bool kContigK = true;
+  const float* y;
+  ConvGeom g;
+  int rows;  // Cy
+  bool vec;  // Hy*Wy % 4 == 0 and y is 16-byte aligned
+  struct State { int off; };  // row * Hy*Wy or -1
+  __device__ __forceinline__ State prep_row(int row) const { return State{row < rows ? row * g.Hy * g.Wy : -1}; }
+  __device__ __forceinline__ void fetch_k4(const State& s, int k0, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (s.off < 0 || k0 >= kend) return;
+    const int hw = g.Hy * g.Wy;
+    uint32_t b, p;
+    g.d_HyWy.divmod(k0, b, p);
+    if (vec && k0 + 3 < kend) {  // k0 % 4 == 0 and hw % 4 == 0: the four pixels share one image
+      float4 t = __ldg(reinterpret_cast<const float4*>(y + (int)b * g.Cy * hw + s.off + (int)p));
+      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (k0 + i < kend) v[i] = __ldg(y + (int)b * g.Cy * hw + s.off + (int)p);
+        if ((int)++p == hw) {
+          p = 0;
+          ++b;
+        }
+      }
     }
   }
 };
@@ -190,185 +394,6 @@ struct PlainOut {  // c[z * split_stride + m * ld + n]
     }
   }
 };
-
-
-// ---- implicit-GEMM views of a convolution -----------------------------------------------------
-// Geometry (conv_geom.cuh): wide tensor X[Nb,Cx,Hx,Wx], narrow tensor Y[Nb,Cy,Hy,Wy],
-// y(b,cy,yo,xo) touches x(b,cx,yo*sh-ph+ky,xo*sw-pw+kx).
-
-// Rows = output pixels (b,yo,xo), k = (cx,ky,kx): the im2col matrix of X, pixel-contiguous.
-struct Im2colRows {
-  static constexpr bool kContigK = false;
-  const float* x;
-  ConvGeom g;
-  int rows;
-  __device__ __forceinline__ void load_r4(int r0, int k, int kend, float (&v)[4]) const {
-    v[0] = v[1] = v[2] = v[3] = 0.f;
-    if (k >= kend || r0 >= rows) return;
-    uint32_t cx, r, ky, kx, b, p, yo, xo;
-    g.d_khw.divmod(k, cx, r);
-    g.d_kw.divmod(r, ky, kx);
-    g.d_HyWy.divmod(r0, b, p);
-    g.d_Wy.divmod(p, yo, xo);
-    if ((int)xo + 3 < g.Wy && r0 + 3 < rows) {  // four pixels of one output row
-      int iy = (int)(yo * g.sh + ky) - g.ph;
-      if (iy < 0 || iy >= g.Hx) return;
-      const float* q = x + (((int64_t)b * g.Cx + cx) * g.Hx + iy) * g.Wx;
-      int ix = (int)(xo * g.sw + kx) - g.pw;
-#pragma unroll
-      for (int i = 0; i < 4; ++i, ix += g.sw)
-        if (ix >= 0 && ix < g.Wx) v[i] = __ldg(q + ix);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        int rr = r0 + i;
-        if (rr >= rows) break;
-        g.d_HyWy.divmod(rr, b, p);
-        g.d_Wy.divmod(p, yo, xo);
-        int iy = (int)(yo * g.sh + ky) - g.ph, ix = (int)(xo * g.sw + kx) - g.pw;
-        if (iy >= 0 && iy < g.Hx && ix >= 0 && ix < g.Wx) v[i] = __ldg(x + (((int64_t)b * g.Cx + cx) * g.Hx + iy) * g.Wx + ix);
-      }
-    }
-  }
-};
-
-// Rows = input pixels (b,iy,ix), k = (cy,ky,kx): the gather of Y used by the input gradient and
-// by the transposed convolution; element = y(b,cy,(iy+ph-ky)/sh,(ix+pw-kx)/sw) when exact and in range.
-struct GatherRows {
-  static constexpr bool kContigK = false;
-  const float* y;
-  ConvGeom g;
-  int rows;
-  __device__ __forceinline__ float one(uint32_t b, uint32_t cy, int iy, int ix, int ky, int kx) const {
-    int ty = iy + g.ph - ky, tx = ix + g.pw - kx;
-    if (ty < 0 || tx < 0) return 0.f;
-    uint32_t yo, ry, xo, rx;
-    g.d_sh.divmod(ty, yo, ry);
-    g.d_sw.divmod(tx, xo, rx);
-    if (ry != 0 || rx != 0 || (int)yo >= g.Hy || (int)xo >= g.Wy) return 0.f;
-    return __ldg(y + (((int64_t)b * g.Cy + cy) * g.Hy + yo) * g.Wy + xo);
-  }
-  __device__ __forceinline__ void load_r4(int r0, int k, int kend, float (&v)[4]) const {
-    v[0] = v[1] = v[2] = v[3] = 0.f;
-    if (k >= kend || r0 >= rows) return;
-    uint32_t cy, r, ky, kx, b, p, iy, ix;
-    g.d_khw.divmod(k, cy, r);
-    g.d_kw.divmod(r, ky, kx);
-    g.d_HxWx.divmod(r0, b, p);
-    g.d_Wx.divmod(p, iy, ix);
-    if ((int)ix + 3 < g.Wx && r0 + 3 < rows) {
-      if (g.sh == 1 && g.sw == 1) {  // unit stride: one row of Y, consecutive columns
-        int yo = (int)iy + g.ph - (int)ky;
-        if (yo < 0 || yo >= g.Hy) return;
-        const float* q = y + (((int64_t)b * g.Cy + cy) * g.Hy + yo) * g.Wy;
-        int xo = (int)ix + g.pw - (int)kx;
-#pragma unroll
-        for (int i = 0; i < 4; ++i, ++xo)
-          if (xo >= 0 && xo < g.Wy) v[i] = __ldg(q + xo);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = one(b, cy, (int)iy, (int)ix + i, (int)ky, (int)kx);
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        int rr = r0 + i;
-        if (rr >= rows) break;
-        g.d_HxWx.divmod(rr, b, p);
-        g.d_Wx.divmod(p, iy, ix);
-        v[i] = one(b, cy, (int)iy, (int)ix, (int)ky, (int)kx);
-      }
-    }
-  }
-};
-
-// Rows = cm, k = (cy, tap): weights stored [Cy, Cm, kh, kw] read with the second index as the row.
-struct WeightSecondRows {
-  static constexpr bool kContigK = true;
-  const float* w;
-  ConvGeom g;
-  int rows;  // Cm
-  __device__ __forceinline__ void load_k4(int row, int k0, int kend, float (&v)[4]) const {
-    const int khw = g.kh * g.kw;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      int k = k0 + i;
-      if (row < rows && k < kend) {
-        uint32_t cy, r;
-        g.d_khw.divmod(k, cy, r);
-        v[i] = __ldg(w + ((int64_t)cy * rows + row) * khw + r);
-      } else {
-        v[i] = 0.f;
-      }
-    }
-  }
-};
-
-// Rows = (cx,ky,kx), k = output pixels (b,yo,xo): the im2col matrix with the pixel index as the
-// reduction (weight gradient).
-struct Im2colK4 {
-  static constexpr bool kContigK = true;
-  const float* x;
-  ConvGeom g;
-  int rows;  // Cx*kh*kw
-  __device__ __forceinline__ void load_k4(int row, int k0, int kend, float (&v)[4]) const {
-    v[0] = v[1] = v[2] = v[3] = 0.f;
-    if (row >= rows || k0 >= kend) return;
-    uint32_t cx, r, ky, kx, b, p, yo, xo;
-    g.d_khw.divmod(row, cx, r);
-    g.d_kw.divmod(r, ky, kx);
-    g.d_HyWy.divmod(k0, b, p);
-    g.d_Wy.divmod(p, yo, xo);
-    if ((int)xo + 3 < g.Wy && k0 + 3 < kend) {
-      int iy = (int)(yo * g.sh + ky) - g.ph;
-      if (iy < 0 || iy >= g.Hx) return;
-      const float* q = x + (((int64_t)b * g.Cx + cx) * g.Hx + iy) * g.Wx;
-      int ix = (int)(xo * g.sw + kx) - g.pw;
-#pragma unroll
-      for (int i = 0; i < 4; ++i, ix += g.sw)
-        if (ix >= 0 && ix < g.Wx) v[i] = __ldg(q + ix);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        int kk = k0 + i;
-        if (kk >= kend) break;
-        g.d_HyWy.divmod(kk, b, p);
-        g.d_Wy.divmod(p, yo, xo);
-        int iy = (int)(yo * g.sh + ky) - g.ph, ix = (int)(xo * g.sw + kx) - g.pw;
-        if (iy >= 0 && iy < g.Hx && ix >= 0 && ix < g.Wx) v[i] = __ldg(x + (((int64_t)b * g.Cx + cx) * g.Hx + iy) * g.Wx + ix);
-      }
-    }
-  }
-};
-
-// Rows = cy, k = pixels (b,p): the narrow tensor with the pixel index as the reduction.
-struct NarrowK4 {
-  static constexpr bool kContigK = true;
-  const float* y;
-  ConvGeom g;
-  int rows;  // Cy
-  bool vec;  // Hy*Wy % 4 == 0 and y is 16-byte aligned
-  __device__ __forceinline__ void load_k4(int row, int k0, int kend, float (&v)[4]) const {
-    v[0] = v[1] = v[2] = v[3] = 0.f;
-    if (row >= rows || k0 >= kend) return;
-    const int hw = g.Hy * g.Wy;
-    uint32_t b, p;
-    g.d_HyWy.divmod(k0, b, p);
-    if (vec && k0 + 3 < kend) {  // k0 % 4 == 0 and hw % 4 == 0: the four pixels share one image
-      float4 t = __ldg(reinterpret_cast<const float4*>(y + ((int64_t)b * g.Cy + row) * hw + p));
-      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        int kk = k0 + i;
-        if (kk >= kend) break;
-        g.d_HyWy.divmod(kk, b, p);
-        v[i] = __ldg(y + ((int64_t)b * g.Cy + row) * hw + p);
-      }
-    }
-  }
-};
-
 struct ImageOut {  // out[b, n, p] for row m = (b,p), optional per-channel bias
   float* out;
   const float* bias;
@@ -384,7 +409,6 @@ struct ImageOut {  // out[b, n, p] for row m = (b,p), optional per-channel bias
       if (n0 + j < C) q[(int64_t)j * HW] = bias ? v[j] + __ldg(bias + n0 + j) : v[j];
   }
 };
-
 struct TransposedOut {  // c[z * split_stride + n * ld + m]: the tile is written transposed
   float* c;
   int64_t ld, split_stride;
@@ -398,49 +422,103 @@ struct TransposedOut {  // c[z * split_stride + n * ld + m]: the tile is written
   }
 };
 
-// Stores one operand tile (ROWS x BK) as hi and lo into shared memory.
+// ---- per-thread producer of one operand tile (ROWS x BK) --------------------------------------
+// fetch() reads this thread's share of a K-block from global memory into registers; commit()
+// splits it into hi / lo and stores both in the UMMA layout.  The kernel keeps two register
+// buffers so that the loads of K-block i+1 are in flight while K-block i is converted.
+template <int ROWS, class L, bool CONTIG = L::kContigK>
+struct Producer;
+
+// K-contiguous source: item = (row group of 8, row in group, group of 8 k).  Lanes run along rows
+// so that each quarter-warp writes one whole 128-byte core matrix (conflict free); a lane reads 32 B.
 template <int ROWS, class L>
-__device__ __forceinline__ void produce_tile(const L& ld, int row0, int k0, int kend, char* hi, char* lo, int warp, int lane) {
-  if constexpr (L::kContigK) {
-    // item = (row group of 8, row in group, group of 8 k): lanes run along rows so that each
-    // quarter-warp writes one whole 128-byte core matrix (conflict free); each lane reads 32 B.
-    const int r8 = lane & 7, kg = lane >> 3;
+struct Producer<ROWS, L, true> {
+  static constexpr int kItems = (ROWS / 8 + kProducerWarps - 1) / kProducerWarps;
+  typename L::State st[kItems];
+  int warp, r8, kg;
+  struct Buf { float v[kItems][2][4]; };
+  __device__ __forceinline__ void init(const L& ld, int row0, int w, int lane) {
+    warp = w; r8 = lane & 7; kg = lane >> 3;
 #pragma unroll
-    for (int rg = warp; rg < ROWS / 8; rg += kProducerWarps) {
-      const int row = rg * 8 + r8;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float v[4];
-        ld.load_k4(row0 + row, k0 + kg * 8 + h * 4, kend, v);
-        float4 vh, vl;
-        split4(v, vh, vl);
-        const uint32_t off = (uint32_t)rg * SBO + (uint32_t)(kg * 2 + h) * LBO + (uint32_t)r8 * 16;
-        *reinterpret_cast<float4*>(hi + off) = vh;
-        *reinterpret_cast<float4*>(lo + off) = vl;
-      }
+    for (int j = 0; j < kItems; ++j) {
+      int rg = warp + j * kProducerWarps;
+      st[j] = ld.prep_row(rg < ROWS / 8 ? row0 + rg * 8 + r8 : 0x7fffffff);
     }
-  } else {
-    // item = (quad of rows, quad of k): a 4x4 block is loaded as four row-vectors, transposed in
-    // registers and written as four 16-byte K-vectors.
+  }
+  __device__ __forceinline__ void fetch(const L& ld, int k0, int kend, Buf& b) const {
 #pragma unroll
-    for (int item = warp * 32 + lane; item < (ROWS / 4) * (BK / 4); item += kProducerWarps * 32) {
-      const int rq = item % (ROWS / 4), kq = item / (ROWS / 4);
-      float t[4][4];
+    for (int j = 0; j < kItems; ++j)
+      if (warp + j * kProducerWarps < ROWS / 8) {
+        ld.fetch_k4(st[j], k0 + kg * 8, kend, b.v[j][0]);
+        ld.fetch_k4(st[j], k0 + kg * 8 + 4, kend, b.v[j][1]);
+      }
+  }
+  __device__ __forceinline__ void commit(const Buf& b, char* hi, char* lo) const {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) ld.load_r4(row0 + rq * 4, k0 + kq * 4 + i, kend, t[i]);
+    for (int j = 0; j < kItems; ++j) {
+      int rg = warp + j * kProducerWarps;
+      if (rg < ROWS / 8) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float v[4] = {t[0][i], t[1][i], t[2][i], t[3][i]};
-        float4 vh, vl;
-        split4(v, vh, vl);
-        const int row = rq * 4 + i;
-        const uint32_t off = (uint32_t)(row >> 3) * SBO + (uint32_t)kq * LBO + (uint32_t)(row & 7) * 16;
-        *reinterpret_cast<float4*>(hi + off) = vh;
-        *reinterpret_cast<float4*>(lo + off) = vl;
+        for (int h = 0; h < 2; ++h) {
+          float4 vh, vl;
+          split4(b.v[j][h], vh, vl);
+          const uint32_t off = (uint32_t)rg * SBO + (uint32_t)(kg * 2 + h) * LBO + (uint32_t)r8 * 16;
+          *reinterpret_cast<float4*>(hi + off) = vh;
+          *reinterpret_cast<float4*>(lo + off) = vl;
+        }
       }
     }
   }
-}
+};
+
+// Row-contiguous source: item = (quad of rows, quad of k): a 4x4 block is fetched as four
+// row-vectors, transposed in registers and written as four 16-byte K-vectors.
+template <int ROWS, class L>
+struct Producer<ROWS, L, false> {
+  static constexpr int kTotal = (ROWS / 4) * (BK / 4);
+  static constexpr int kItems = (kTotal + kProducerWarps * 32 - 1) / (kProducerWarps * 32);
+  typename L::State st[kItems];
+  int tid;
+  struct Buf { float v[kItems][4][4]; };
+  __device__ __forceinline__ void init(const L& ld, int row0, int w, int lane) {
+    tid = w * 32 + lane;
+#pragma unroll
+    for (int j = 0; j < kItems; ++j) {
+      int item = tid + j * kProducerWarps * 32;
+      st[j] = ld.prep_quad(item < kTotal ? row0 + (item % (ROWS / 4)) * 4 : 0x7ffffff0);
+    }
+  }
+  __device__ __forceinline__ void fetch(const L& ld, int k0, int kend, Buf& b) const {
+#pragma unroll
+    for (int j = 0; j < kItems; ++j) {
+      int item = tid + j * kProducerWarps * 32;
+      if (item < kTotal) {
+        int kq = item / (ROWS / 4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ld.fetch_r4(st[j], k0 + kq * 4 + i, kend, b.v[j][i]);
+      }
+    }
+  }
+  __device__ __forceinline__ void commit(const Buf& b, char* hi, char* lo) const {
+#pragma unroll
+    for (int j = 0; j < kItems; ++j) {
+      int item = tid + j * kProducerWarps * 32;
+      if (item < kTotal) {
+        int rq = item % (ROWS / 4), kq = item / (ROWS / 4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float v[4] = {b.v[j][0][i], b.v[j][1][i], b.v[j][2][i], b.v[j][3][i]};
+          float4 vh, vl;
+          split4(v, vh, vl);
+          const int row = rq * 4 + i;
+          const uint32_t off = (uint32_t)(row >> 3) * SBO + (uint32_t)kq * LBO + (uint32_t)(row & 7) * 16;
+          *reinterpret_cast<float4*>(hi + off) = vh;
+          *reinterpret_cast<float4*>(lo + off) = vl;
+        }
+      }
+    }
+  }
+};
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -451,7 +529,7 @@ struct SmemLayout {
 };
 
 template <int BN, int STAGES, class LA, class LB, class EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, (BN <= 64 && STAGES <= 2) ? 2 : 1)
 tc_gemm_kernel(const LA la, const LB lb, const EPI epi, int K, int k_per_split, int* status) {
   extern __shared__ __align__(128) char smem[];
   using SL = SmemLayout<BN, STAGES>;
@@ -490,17 +568,40 @@ tc_gemm_kernel(const LA la, const LB lb, const EPI epi, int K, int k_per_split, 
   bool ok = true;
   if (warp < kProducerWarps) {
     // ---------------- producers ----------------
-    for (int it = 0; it < nkb && ok; ++it) {
+    Producer<BM, LA> pa;
+    Producer<BN, LB> pb;
+    pa.init(la, m0, warp, lane);
+    pb.init(lb, n0, warp, lane);
+    typename Producer<BM, LA>::Buf a0, a1;
+    typename Producer<BN, LB>::Buf b0, b1;
+    auto stage_out = [&](int it, const typename Producer<BM, LA>::Buf& ba, const typename Producer<BN, LB>::Buf& bb) -> bool {
       const int s = it % STAGES;
-      if (it >= STAGES) ok = mbar_wait(bars + 8 * (STAGES + s), ((it / STAGES) - 1) & 1, status, 1);
-      if (!ok) break;
+      if (it >= STAGES && !mbar_wait(bars + 8 * (STAGES + s), ((it / STAGES) - 1) & 1, status, 1)) return false;
       char* st = smem + s * SL::stage_bytes;
-      const int k0 = kbeg + it * BK;
-      produce_tile<BM>(la, m0, k0, kend, st, st + SL::a_bytes, warp, lane);
-      produce_tile<BN>(lb, n0, k0, kend, st + 2 * SL::a_bytes, st + 2 * SL::a_bytes + SL::b_bytes, warp, lane);
+      pa.commit(ba, st, st + SL::a_bytes);
+      pb.commit(bb, st + 2 * SL::a_bytes, st + 2 * SL::a_bytes + SL::b_bytes);
       fence_async_smem();  // make the generic-proxy stores visible to the tensor-core (async) proxy
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + 8 * s);
+      return true;
+    };
+    if (nkb > 0) {
+      pa.fetch(la, kbeg, kend, a0);
+      pb.fetch(lb, kbeg, kend, b0);
+    }
+    for (int it = 0; it < nkb && ok; it += 2) {
+      if (it + 1 < nkb) {
+        pa.fetch(la, kbeg + (it + 1) * BK, kend, a1);
+        pb.fetch(lb, kbeg + (it + 1) * BK, kend, b1);
+      }
+      ok = stage_out(it, a0, b0);
+      if (ok && it + 1 < nkb) {
+        if (it + 2 < nkb) {
+          pa.fetch(la, kbeg + (it + 2) * BK, kend, a0);
+          pb.fetch(lb, kbeg + (it + 2) * BK, kend, b0);
+        }
+        ok = stage_out(it + 1, a1, b1);
+      }
     }
     // ---------------- epilogue ----------------
     if (ok && nkb > 0) ok = mbar_wait(bars + 8 * (2 * STAGES), 0, status, 2);
@@ -573,9 +674,11 @@ rt_status launch(rt_ctx* ctx, const LA& la, const LB& lb, const EPI& epi, int M,
 
 template <class LA, class LB, class EPI>
 rt_status dispatch_bn(rt_ctx* ctx, const LA& la, const LB& lb, const EPI& epi, int M, int N, int K, int splits, int kps) {
-  if (N <= 32) return launch<32, 4>(ctx, la, lb, epi, M, N, K, splits, kps);
-  if (N <= 64) return launch<64, 4>(ctx, la, lb, epi, M, N, K, splits, kps);
-  return launch<128, 3>(ctx, la, lb, epi, M, N, K, splits, kps);
+  // Two shared-memory stages everywhere (the register double buffer hides the global latency);
+  // tiles up to 64 columns then fit two CTAs per SM.
+  if (N <= 32) return launch<32, 2>(ctx, la, lb, epi, M, N, K, splits, kps);
+  if (N <= 64) return launch<64, 2>(ctx, la, lb, epi, M, N, K, splits, kps);
+  return launch<128, 2>(ctx, la, lb, epi, M, N, K, splits, kps);
 }
 
 inline int n_tiles(int64_t M, int64_t N) {
