@@ -19,6 +19,7 @@
 // frees its TMEM columns and returns.
 #include "rt_internal.cuh"
 #include "conv_geom.cuh"
+#include <type_traits>
 
 rt_status rt_sum_axis_internal(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out,
                                float scale);
@@ -128,11 +129,13 @@ __device__ __forceinline__ void split4(const float (&v)[4], float4& hi, float4& 
 // Rows are the M (A operand) or N (B operand) index.  A producer thread works on the same rows
 // for the whole K loop, so everything that depends only on the row is decoded once into a small
 // State (prep_*); the per-K-block fetch then costs a handful of integer instructions per load.
-//   kContigK loaders:  State prep_row(row);        fetch_k4(state, k0, kend, v): 4 consecutive k
-//   other loaders:      State prep_quad(first_row); fetch_r4(state, k, kend, v):  4 consecutive rows
+//   kKind 0 (K-contiguous):   State prep_row(row);        fetch_k4(state, k0, kend, v): 4 consecutive k
+//   kKind 1 (row-contiguous): State prep_quad(first_row); fetch_r4(state, k, kend, v):  4 consecutive rows
+//   kKind 2 (pixel rows):     State prep_quad(first_row); fetch_c4(state, q, qend, v):  for 4 consecutive rows the
+//                             4 consecutive k of chunk q (k = 4q .. 4q+3)
 // Out-of-range elements read as 0.
 struct MatK {  // element(row, k) = p[row * ld + k]
-  static constexpr bool kContigK = true;
+  static constexpr int kKind = 0;
   const float* p;
   int64_t ld;
   int rows;
@@ -153,7 +156,7 @@ struct MatK {  // element(row, k) = p[row * ld + k]
   }
 };
 struct MatMN {  // element(row, k) = p[k * ld + row]
-  static constexpr bool kContigK = false;
+  static constexpr int kKind = 1;
   const float* p;
   int64_t ld;
   int rows;
@@ -182,7 +185,7 @@ struct MatMN {  // element(row, k) = p[k * ld + row]
 
 // Rows = output pixels (b,yo,xo), k = (cx,ky,kx): the im2col matrix of X, pixel-contiguous.
 struct Im2colRows {
-  static constexpr bool kContigK = false;
+  static constexpr int kKind = 1;
   const float* x;
   ConvGeom g;
   int rows;
@@ -225,7 +228,7 @@ struct Im2colRows {
 // Rows = input pixels (b,iy,ix), k = (cy,ky,kx): the gather of Y used by the input gradient and
 // by the transposed convolution; element = y(b,cy,(iy+ph-ky)/sh,(ix+pw-kx)/sw) when exact and in range.
 struct GatherRows {
-  static constexpr bool kContigK = false;
+  static constexpr int kKind = 1;
   const float* y;
   ConvGeom g;
   int rows;
@@ -279,7 +282,7 @@ struct GatherRows {
 
 // Rows = cm, k = (cy, tap): weights stored [Cy, Cm, kh, kw] read with the second index as the row.
 struct WeightSecondRows {
-  static constexpr bool kContigK = true;
+  static constexpr int kKind = 0;
   const float* w;
   ConvGeom g;
   int rows;  // Cm
@@ -305,38 +308,51 @@ struct WeightSecondRows {
 };
 
 // Rows = (cx,ky,kx), k = output pixels (b,yo,xo): the im2col matrix with the pixel index as the
-// reduction (weight gradient).
+// reduction (weight gradient).  A thread walks eight consecutive pixels of its row with running
+// coordinates, so the pixel index is decoded once per eight elements.
 struct Im2colK4 {
-  static constexpr bool kContigK = true;
+  static constexpr int kKind = 0;
+  static constexpr int kInvalid = -(1 << 30);
   const float* x;
   ConvGeom g;
-  int rows;  // Cx*kh*kw
-  struct State { int coff, ky, kx; };  // coff = cx*Hx*Wx + (ky-ph)*Wx + (kx-pw), or ky = -1 when out of range
+  int rows;      // Cx*kh*kw
+  int row_jump;  // offset change from the end of one output row to the start of the next: sh*Wx - Wy*sw
+  int img_jump;  // from the end of one image to the start of the next: (Cx*Hx - Hy*sh)*Wx
+  struct State { int coff, dy, dx; };  // dy = ky-ph, dx = kx-pw, coff = (cx*Hx + dy)*Wx + dx
   __device__ __forceinline__ State prep_row(int row) const {
-    if (row >= rows) return State{0, -1, 0};
+    if (row >= rows) return State{0, kInvalid, 0};
     uint32_t cx, r, ky, kx;
     g.d_khw.divmod(row, cx, r);
     g.d_kw.divmod(r, ky, kx);
-    return State{((int)cx * g.Hx + (int)ky - g.ph) * g.Wx + (int)kx - g.pw, (int)ky, (int)kx};
+    const int dy = (int)ky - g.ph, dx = (int)kx - g.pw;
+    return State{((int)cx * g.Hx + dy) * g.Wx + dx, dy, dx};
   }
-  __device__ __forceinline__ void fetch_k4(const State& s, int k0, int kend, float (&v)[4]) const {
-    v[0] = v[1] = v[2] = v[3] = 0.f;
-    if (s.ky < 0 || k0 >= kend) return;
+  __device__ __forceinline__ void fetch_k8(const State& s, int k0, int kend, float (&v0)[4], float (&v1)[4]) const {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v0[i] = v1[i] = 0.f;
+    if (s.dy == kInvalid || k0 >= kend) return;
+    const int n = kend - k0;
     uint32_t b, p, yo, xo;
     g.d_HyWy.divmod(k0, b, p);
     g.d_Wy.divmod(p, yo, xo);
+    int iy = (int)yo * g.sh + s.dy, ix = (int)xo * g.sw + s.dx;
+    int off = ((int)b * g.Cx * g.Hx + (int)yo * g.sh) * g.Wx + (int)xo * g.sw + s.coff;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (k0 + i < kend) {
-        int iy = (int)(yo * g.sh) + s.ky - g.ph, ix = (int)(xo * g.sw) + s.kx - g.pw;
-        if (iy >= 0 && iy < g.Hx && ix >= 0 && ix < g.Wx)
-          v[i] = __ldg(x + ((int)b * g.Cx * g.Hx + (int)(yo * g.sh)) * g.Wx + (int)(xo * g.sw) + s.coff);
-      }
+    for (int i = 0; i < 8; ++i) {
+      float t = 0.f;
+      if (i < n && (unsigned)iy < (unsigned)g.Hx && (unsigned)ix < (unsigned)g.Wx) t = __ldg(x + off);
+      if (i < 4) v0[i] = t; else v1[i - 4] = t;
+      ix += g.sw;
+      off += g.sw;
       if ((int)++xo == g.Wy) {  // next output row / next image
         xo = 0;
+        ix = s.dx;
+        off += row_jump;
+        iy += g.sh;
         if ((int)++yo == g.Hy) {
           yo = 0;
-          ++b;
+          iy = s.dy;
+          off += img_jump;
         }
       }
     }
@@ -345,7 +361,7 @@ struct Im2colK4 {
 
 // Rows = cy, k = pixels (b,p): the narrow tensor with the pixel index as the reduction.
 struct NarrowK4 {
-  static constexpr bool kContigK = true;
+  static constexpr int kKind = 0;
   const float* y;
   ConvGeom g;
   int rows;  // Cy
@@ -370,6 +386,97 @@ struct NarrowK4 {
           ++b;
         }
       }
+    }
+  }
+};
+
+// Rows = pixels (b,yo,xo) of the narrow side of a convolution-shaped gather from src[Nb,C,H,W]:
+// the row reads src(b, c, yo*sh-ph+ky, xo*sw-pw+kx).  The reduction index is laid out as
+// k = ((c*kh + ky)*kwq + kxq)*4 + j with the kernel columns padded to kwq*4 >= kw, so that one
+// 16-byte K-chunk of a row is four consecutive source columns of one source row: a chunk costs one
+// row test, one address and four predicated loads; the column tests are a per-pixel bit mask
+// computed once.  The padding columns are zeros in both operands.
+struct PixelTapRows {
+  static constexpr int kKind = 2;
+  const float* src;
+  int C, H, W;           // source channels / height / width
+  int kh, kw, kwq;       // kernel extent, number of 4-wide column chunks
+  int sh, sw, ph, pw;
+  int rows;              // Nb * rows_h * rows_w
+  FastDiv d_hw, d_w;     // pixels per image / per row on the row side
+  FastDiv d_kh, d_kwq;
+  struct State {
+    int base[4];         // offset of src(b, 0, yo*sh-ph, xo*sw-pw) (may lie outside the image)
+    int iy0[4];
+    uint32_t cmask[4];   // bit t: kernel column t exists and falls inside the source row
+  };
+  __device__ __forceinline__ State prep_quad(int r0) const {
+    State s;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      s.base[i] = 0;
+      s.iy0[i] = 0;
+      s.cmask[i] = 0;
+      if (r0 + i < rows) {
+        uint32_t b, p, yo, xo;
+        d_hw.divmod(r0 + i, b, p);
+        d_w.divmod(p, yo, xo);
+        const int iy0 = (int)yo * sh - ph, ix0 = (int)xo * sw - pw;
+        s.iy0[i] = iy0;
+        s.base[i] = ((int)b * C * H + iy0) * W + ix0;
+        uint32_t m = 0;
+        for (int t = 0; t < kw; ++t)
+          if ((unsigned)(ix0 + t) < (unsigned)W) m |= 1u << t;
+        s.cmask[i] = m;
+      }
+    }
+    return s;
+  }
+  __device__ __forceinline__ void fetch_c4(const State& s, int q, int qend, float (&v)[4][4]) const {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[i][j] = 0.f;
+    if (q >= qend) return;
+    uint32_t ck, kxq, c, ky;
+    d_kwq.divmod(q, ck, kxq);
+    d_kh.divmod(ck, c, ky);
+    const int koff = ((int)c * H + (int)ky) * W + (int)kxq * 4;
+    const int shift = (int)kxq * 4;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int iy = s.iy0[i] + (int)ky;
+      const uint32_t m = (unsigned)iy < (unsigned)H ? (s.cmask[i] >> shift) & 15u : 0u;
+      const float* p = src + s.base[i] + koff;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (m & (1u << j)) v[i][j] = __ldg(p + j);
+    }
+  }
+};
+
+// Weights in the padded tap order of PixelTapRows: element(row n, k = ((c*kh+ky)*kwq+kxq)*4+j) =
+// w[n*sn + c*sc + ky*sky + kx*skx + off0] for kx = kxq*4+j < kw, else 0.  Strides may be negative
+// (flipped kernels of the input gradient).
+struct TapWeights {
+  static constexpr int kKind = 0;
+  const float* w;
+  int rows, kh, kw, kwq;
+  int sn, sc, sky, skx, off0;
+  FastDiv d_kh, d_kwq;
+  struct State { int off; };  // n*sn + off0, or -1
+  __device__ __forceinline__ State prep_row(int row) const { return State{row < rows ? row * sn + off0 : -1}; }
+  __device__ __forceinline__ void fetch_k4(const State& s, int k0, int kend, float (&v)[4]) const {
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    if (s.off < 0 || k0 >= kend) return;
+    uint32_t ck, kxq, c, ky;
+    d_kwq.divmod(k0 >> 2, ck, kxq);
+    d_kh.divmod(ck, c, ky);
+    const float* p = w + s.off + (int)c * sc + (int)ky * sky;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int kx = (int)kxq * 4 + j;
+      if (kx < kw) v[j] = __ldg(p + kx * skx);
     }
   }
 };
@@ -426,13 +533,28 @@ struct TransposedOut {  // c[z * split_stride + n * ld + m]: the tile is written
 // fetch() reads this thread's share of a K-block from global memory into registers; commit()
 // splits it into hi / lo and stores both in the UMMA layout.  The kernel keeps two register
 // buffers so that the loads of K-block i+1 are in flight while K-block i is converted.
-template <int ROWS, class L, bool CONTIG = L::kContigK>
+template <class L, class = void>
+struct HasFetchK8 : std::false_type {};
+template <class L>
+struct HasFetchK8<L, std::void_t<decltype(&L::fetch_k8)>> : std::true_type {};
+template <class L>
+__device__ __forceinline__ void fetch_k8(const L& ld, const typename L::State& s, int k0, int kend, float (&v0)[4],
+                                         float (&v1)[4]) {
+  if constexpr (HasFetchK8<L>::value) {
+    ld.fetch_k8(s, k0, kend, v0, v1);
+  } else {
+    ld.fetch_k4(s, k0, kend, v0);
+    ld.fetch_k4(s, k0 + 4, kend, v1);
+  }
+}
+
+template <int ROWS, class L, int KIND = L::kKind>
 struct Producer;
 
 // K-contiguous source: item = (row group of 8, row in group, group of 8 k).  Lanes run along rows
 // so that each quarter-warp writes one whole 128-byte core matrix (conflict free); a lane reads 32 B.
 template <int ROWS, class L>
-struct Producer<ROWS, L, true> {
+struct Producer<ROWS, L, 0> {
   static constexpr int kItems = (ROWS / 8 + kProducerWarps - 1) / kProducerWarps;
   typename L::State st[kItems];
   int warp, r8, kg;
@@ -449,8 +571,7 @@ struct Producer<ROWS, L, true> {
 #pragma unroll
     for (int j = 0; j < kItems; ++j)
       if (warp + j * kProducerWarps < ROWS / 8) {
-        ld.fetch_k4(st[j], k0 + kg * 8, kend, b.v[j][0]);
-        ld.fetch_k4(st[j], k0 + kg * 8 + 4, kend, b.v[j][1]);
+        fetch_k8(ld, st[j], k0 + kg * 8, kend, b.v[j][0], b.v[j][1]);
       }
   }
   __device__ __forceinline__ void commit(const Buf& b, char* hi, char* lo) const {
@@ -474,7 +595,7 @@ struct Producer<ROWS, L, true> {
 // Row-contiguous source: item = (quad of rows, quad of k): a 4x4 block is fetched as four
 // row-vectors, transposed in registers and written as four 16-byte K-vectors.
 template <int ROWS, class L>
-struct Producer<ROWS, L, false> {
+struct Producer<ROWS, L, 1> {
   static constexpr int kTotal = (ROWS / 4) * (BK / 4);
   static constexpr int kItems = (kTotal + kProducerWarps * 32 - 1) / (kProducerWarps * 32);
   typename L::State st[kItems];
@@ -510,6 +631,50 @@ struct Producer<ROWS, L, false> {
           float v[4] = {b.v[j][0][i], b.v[j][1][i], b.v[j][2][i], b.v[j][3][i]};
           float4 vh, vl;
           split4(v, vh, vl);
+          const int row = rq * 4 + i;
+          const uint32_t off = (uint32_t)(row >> 3) * SBO + (uint32_t)kq * LBO + (uint32_t)(row & 7) * 16;
+          *reinterpret_cast<float4*>(hi + off) = vh;
+          *reinterpret_cast<float4*>(lo + off) = vl;
+        }
+      }
+    }
+  }
+};
+
+// Pixel-row source with K-chunks: item = (quad of rows, chunk of 4 k).  The loader already returns
+// each row's four consecutive k, so the registers go to shared memory without a transpose.
+template <int ROWS, class L>
+struct Producer<ROWS, L, 2> {
+  static constexpr int kTotal = (ROWS / 4) * (BK / 4);
+  static constexpr int kItems = (kTotal + kProducerWarps * 32 - 1) / (kProducerWarps * 32);
+  typename L::State st[kItems];
+  int tid;
+  struct Buf { float v[kItems][4][4]; };
+  __device__ __forceinline__ void init(const L& ld, int row0, int w, int lane) {
+    tid = w * 32 + lane;
+#pragma unroll
+    for (int j = 0; j < kItems; ++j) {
+      int item = tid + j * kProducerWarps * 32;
+      st[j] = ld.prep_quad(item < kTotal ? row0 + (item % (ROWS / 4)) * 4 : 0x7ffffff0);
+    }
+  }
+  __device__ __forceinline__ void fetch(const L& ld, int k0, int kend, Buf& b) const {
+#pragma unroll
+    for (int j = 0; j < kItems; ++j) {
+      int item = tid + j * kProducerWarps * 32;
+      if (item < kTotal) ld.fetch_c4(st[j], (k0 >> 2) + item / (ROWS / 4), (kend + 3) >> 2, b.v[j]);
+    }
+  }
+  __device__ __forceinline__ void commit(const Buf& b, char* hi, char* lo) const {
+#pragma unroll
+    for (int j = 0; j < kItems; ++j) {
+      int item = tid + j * kProducerWarps * 32;
+      if (item < kTotal) {
+        int rq = item % (ROWS / 4), kq = item / (ROWS / 4);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float4 vh, vl;
+          split4(b.v[j][i], vh, vl);
           const int row = rq * 4 + i;
           const uint32_t off = (uint32_t)(row >> 3) * SBO + (uint32_t)kq * LBO + (uint32_t)(row & 7) * 16;
           *reinterpret_cast<float4*>(hi + off) = vh;
@@ -723,6 +888,28 @@ rt_status gemm_plain(rt_ctx* ctx, const LA& la, const LB& lb, float* c, int64_t 
 
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+inline PixelTapRows pixel_rows(const float* src, int C, int H, int W, int rows_h, int rows_w, int kh, int kw, int sh, int sw,
+                               int ph, int pw, int rows) {
+  PixelTapRows l;
+  l.src = src; l.C = C; l.H = H; l.W = W;
+  l.kh = kh; l.kw = kw; l.kwq = (kw + 3) / 4;
+  l.sh = sh; l.sw = sw; l.ph = ph; l.pw = pw;
+  l.rows = rows;
+  l.d_hw.init(rows_h * rows_w);
+  l.d_w.init(rows_w);
+  l.d_kh.init(kh);
+  l.d_kwq.init(l.kwq);
+  return l;
+}
+inline TapWeights tap_weights(const float* w, int rows, int kh, int kw, int sn, int sc, int sky, int skx, int off0) {
+  TapWeights l;
+  l.w = w; l.rows = rows; l.kh = kh; l.kw = kw; l.kwq = (kw + 3) / 4;
+  l.sn = sn; l.sc = sc; l.sky = sky; l.skx = skx; l.off0 = off0;
+  l.d_kh.init(kh);
+  l.d_kwq.init(l.kwq);
+  return l;
+}
+
 }  // namespace tc
 
 // Tensor-core GEMM with the rt_gemm contract.  Returns RT_ERR_UNIMPLEMENTED when the shape is
@@ -750,10 +937,16 @@ rt_status rt_conv_forward_tc_internal(rt_ctx* ctx, const float* x, const float* 
   using namespace tc;
   int64_t M = (int64_t)g.Nb * g.Hy * g.Wy, N = g.Cy, K = (int64_t)g.Cx * g.kh * g.kw;
   if (M <= 0 || N <= 0 || K < 8 || M >= (1ll << 31) || (int64_t)g.Nb * g.Cx * g.Hx * g.Wx >= (1ll << 31)) return RT_ERR_UNIMPLEMENTED;
-  Im2colRows la{x, g, (int)M};
-  MatK lb{w, K, (int)N, al16(w) && K % 4 == 0};
   ImageOut epi{y, bias, (int)N, g.Hy * g.Wy, (int)M, {}};
   epi.d_HW.init(g.Hy * g.Wy);
+  if (g.kw <= 32) {  // padded-tap order: cheap pixel-row producer
+    PixelTapRows la = pixel_rows(x, g.Cx, g.Hx, g.Wx, g.Hy, g.Wy, g.kh, g.kw, g.sh, g.sw, g.ph, g.pw, (int)M);
+    TapWeights lb = tap_weights(w, (int)N, g.kh, g.kw, g.Cx * g.kh * g.kw, g.kh * g.kw, g.kw, 1, 0);
+    const int Kp = g.Cx * g.kh * la.kwq * 4;
+    return dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, Kp, 1, (Kp + BK - 1) / BK * BK);
+  }
+  Im2colRows la{x, g, (int)M};
+  MatK lb{w, K, (int)N, al16(w) && K % 4 == 0};
   return dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, (int)K, 1, (int)((K + BK - 1) / BK * BK));
 }
 
@@ -764,10 +957,18 @@ rt_status rt_conv_gather_tc_internal(rt_ctx* ctx, const float* y, const float* w
   using namespace tc;
   int64_t M = (int64_t)g.Nb * g.Hx * g.Wx, N = cm, K = (int64_t)g.Cy * g.kh * g.kw;
   if (M <= 0 || N <= 0 || K < 8 || M >= (1ll << 31) || (int64_t)g.Nb * g.Cy * g.Hy * g.Wy >= (1ll << 31)) return RT_ERR_UNIMPLEMENTED;
-  GatherRows la{y, g, (int)M};
-  WeightSecondRows lb{w, g, cm};
   ImageOut epi{out, bias, cm, g.Hx * g.Wx, (int)M, {}};
   epi.d_HW.init(g.Hx * g.Wx);
+  if (g.sh == 1 && g.sw == 1 && g.kw <= 32) {
+    // unit stride: the gather is a convolution of y with the kernel flipped in both directions and
+    // padding (kh-1-ph, kw-1-pw), so the cheap pixel-row producer applies
+    PixelTapRows la = pixel_rows(y, g.Cy, g.Hy, g.Wy, g.Hx, g.Wx, g.kh, g.kw, 1, 1, g.kh - 1 - g.ph, g.kw - 1 - g.pw, (int)M);
+    TapWeights lb = tap_weights(w, cm, g.kh, g.kw, g.kh * g.kw, cm * g.kh * g.kw, -g.kw, -1, g.kh * g.kw - 1);
+    const int Kp = g.Cy * g.kh * la.kwq * 4;
+    return dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, Kp, 1, (Kp + BK - 1) / BK * BK);
+  }
+  GatherRows la{y, g, (int)M};
+  WeightSecondRows lb{w, g, cm};
   return dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, (int)K, 1, (int)((K + BK - 1) / BK * BK));
 }
 
@@ -785,7 +986,7 @@ rt_status rt_conv_weight_grad_tc_internal(rt_ctx* ctx, const float* x, const flo
     kps = 2048;
     splits = (int)((K + kps - 1) / kps);
   }
-  Im2colK4 la{x, g, (int)M};
+  Im2colK4 la{x, g, (int)M, g.sh * g.Wx - g.Wy * g.sw, (g.Cx * g.Hx - g.Hy * g.sh) * g.Wx};
   NarrowK4 lb{y, g, (int)N, al16(y) && (g.Hy * g.Wy) % 4 == 0};
   if (splits == 1) {
     TransposedOut epi{dw, M, 0, (int)M, (int)N};
