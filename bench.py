@@ -271,7 +271,7 @@ def main():
         capi.call("mem_stats", C.byref(res), C.byref(in_use), C.byref(nalloc))
         roof = measure_dominant_kernel(rt, capi, config, dims, pk)
         cpu = None
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:  # reported on the single-GPU run only
             steps_cpu = 15 if args.workload in ("c3", "c1") else 1
             sec = cpu_step_time(config, dims, 0, steps_cpu)
             cpu = {"value": per_gpu / sec, "unit": "samples/s", "cores": 1, "kind": "port",
@@ -285,7 +285,7 @@ def main():
             "config": {"workload": desc, "per_gpu_batch": per_gpu, "global_batch": total, "parallelism": f"dp{world}",
                        "l2": f"no explicit flush: device memory in use by one step is {in_use.value / 1e6:.0f} MB (L2 is 126 MB); steps run back to back",
                        "step": "CUDA-graph replay of forward+backward, one NCCL all-reduce of the flat gradients (N>1), one fused optimizer launch"},
-            "e2e": {"value": total * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+            "e2e": {"value": total * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(gpu_launches), "final_loss": loss, "clocks": clocks,
         }
