@@ -166,6 +166,19 @@ rt_status rt_log_softmax(rt_ctx* ctx, const float* x, int64_t outer, int64_t len
 rt_status rt_log_softmax_backward(rt_ctx* ctx, const float* x, const float* g, int64_t outer, int64_t len,
                                   int64_t inner, float* dx);
 
+/* out[outer, inner] = sum over the middle axis of x[outer, len, inner], like rt_reduce(RT_RED_SUM), but the
+ * call allocates nothing: the partial sums of a split reduction go to a fixed 1 MiB array in device memory
+ * (one per device) instead of a block from the context's allocator.  No counterpart in the reference; it
+ * serves callers that must not allocate while enqueueing (for example during stream capture).
+ *  - A shape that needs more than 262144 partial sums, or outer > 65535 with inner > 1, returns
+ *    RT_ERR_INVALID_OPERATION with a message; use rt_reduce for those.
+ *  - The first call on a device looks up the array's address (cudaGetSymbolAddress), which may load the
+ *    module: make one call (any shape, outer = 0 is enough) before starting a stream capture.
+ *  - Calls that overlap on one device (other streams or contexts) share the array and race; calls on one
+ *    stream are ordered. */
+rt_status rt_reduce_sum_static_scratch(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner,
+                                       float* out);
+
 /* ---- pooling (max_pool2d mod.rs:144, max_pool2d_backward mod.rs:151) -------------------------
  * idx holds the in-window position ky*kw+kx of the first maximum as f32 (strict >, padding = -inf). */
 rt_status rt_max_pool2d(rt_ctx* ctx, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, int kh, int kw,

@@ -12,6 +12,7 @@
 // run-to-run deterministic.
 #include <cfloat>
 #include <cmath>
+#include <mutex>
 
 #include "rt_internal.cuh"
 
@@ -595,3 +596,135 @@ rt_status rt_log_softmax_backward(rt_ctx* ctx, const float* x, const float* g, i
 }
 
 }  // extern "C"
+
+// ---- axis sum whose workspace is a fixed array in device memory --------------------------------
+// Some callers may not touch the allocator at all while they enqueue work: a stream that is being
+// captured into a graph (an allocation made during capture belongs to no replay), or a host loop
+// that promised its latency budget no driver call that can block.  For them the split partial sums
+// of the axis reduction live in the array below instead of a block from the context's allocator.
+// The array exists once per device (it is part of the loaded module), so two calls that overlap on
+// one device - different streams, different contexts, or a graph replay next to an eager call -
+// would write each other's partial sums; calls on one stream are ordered and safe.  It keeps
+// whatever the previous call left in it: the first pass writes every slot the second pass reads,
+// so nothing has to start at zero and nothing is cleared.
+namespace {
+
+constexpr int64_t kStaticScratchFloats = int64_t(1) << 18;  // 1 MiB of partial sums
+__device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_ptr[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+// Address of the array on the context's device, looked up once per device with that device current.
+// The first lookup may make the runtime load the module, so it belongs before any stream capture.
+rt_status static_scratch(rt_ctx* ctx, float** out) {
+  if (ctx->device < 0 || ctx->device >= kMaxDevices)
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_reduce_sum_static_scratch: device ordinal %d out of range", ctx->device);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_ptr[ctx->device]) {
+    int current = -1;
+    RT_CUDA(ctx, cudaGetDevice(&current));
+    if (current != ctx->device) RT_CUDA(ctx, cudaSetDevice(ctx->device));
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (current != ctx->device) cudaSetDevice(current);
+    if (e != cudaSuccess || !p)
+      RT_FAIL(ctx, RT_ERR_CUDA, "rt_reduce_sum_static_scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    g_static_scratch_ptr[ctx->device] = p;
+  }
+  *out = g_static_scratch_ptr[ctx->device];
+  return RT_OK;
+}
+
+}  // namespace
+
+extern "C" rt_status rt_reduce_sum_static_scratch(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner,
+                                                  float* out) {
+  RT_CHECK_CTX(ctx);
+  if (outer < 0 || len < 0 || inner < 0) RT_FAIL(ctx, RT_ERR_INVALID_INDEX, "rt_reduce_sum_static_scratch: negative extent");
+  float* scratch = nullptr;
+  rt_status st = static_scratch(ctx, &scratch);  // also serves as the set-up call
+  if (st != RT_OK) return st;
+  if (outer * inner == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, out);
+  if (len == 0) return rt_fill(ctx, out, 0.f, outer * inner);
+  RT_CHECK_PTR(ctx, x);
+  if (outer > 65535 && inner > 1)
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_reduce_sum_static_scratch: outer extent %lld exceeds 65535", (long long)outer);
+  const int64_t target_blocks = (int64_t)ctx->sm_count * 4;
+  if (inner == 1) {
+    const int64_t rows = outer;
+    if (len <= 16) {
+      row_reduce_thread<RT_RED_SUM><<<rt_grid_for(ctx, rows, kThreads), kThreads, 0, ctx->stream>>>(x, out, rows, (int)len, 1.f);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
+    if (len <= 1024) {
+      row_reduce_warp<RT_RED_SUM><<<rt_grid_for(ctx, rows, kThreads / 32), kThreads, 0, ctx->stream>>>(x, out, rows, len, 1.f);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
+    // long rows: cut each into chunks of at least 4096 elements, one partial sum per chunk
+    int64_t chunks = 1;
+    if (rows < target_blocks) {
+      chunks = (target_blocks + rows - 1) / rows;
+      const int64_t max_chunks = (len + 4095) / 4096;
+      if (chunks > max_chunks) chunks = max_chunks;
+      if (chunks > 1024) chunks = 1024;  // the second pass is one warp per row
+      if (chunks < 1) chunks = 1;
+    }
+    int64_t chunk_len = (len + chunks - 1) / chunks;
+    chunk_len = (chunk_len + 3) & ~int64_t(3);
+    chunks = (len + chunk_len - 1) / chunk_len;
+    const int grid = (int)((rows * chunks < target_blocks * 2) ? rows * chunks : target_blocks * 2);
+    if (chunks == 1) {
+      row_reduce_block<RT_RED_SUM><<<grid, kThreads, 0, ctx->stream>>>(x, out, rows, len, 1, chunk_len, 1.f);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
+    if (rows * chunks > kStaticScratchFloats)
+      RT_FAIL(ctx, RT_ERR_INVALID_OPERATION,
+              "rt_reduce_sum_static_scratch: %lld partial sums needed, the fixed workspace holds %lld", (long long)(rows * chunks),
+              (long long)kStaticScratchFloats);
+    row_reduce_block<RT_RED_SUM><<<grid, kThreads, 0, ctx->stream>>>(x, scratch, rows, len, chunks, chunk_len, 1.f);
+    RT_LAUNCHED(ctx);
+    if (chunks <= 16)
+      row_reduce_thread<RT_RED_SUM><<<rt_grid_for(ctx, rows, kThreads), kThreads, 0, ctx->stream>>>(scratch, out, rows, (int)chunks, 1.f);
+    else
+      row_reduce_warp<RT_RED_SUM><<<rt_grid_for(ctx, rows, kThreads / 32), kThreads, 0, ctx->stream>>>(scratch, out, rows, chunks, 1.f);
+    RT_LAUNCHED(ctx);
+    return RT_OK;
+  }
+  // inner > 1: column sums, the reduced axis cut into splits of at least 64 rows
+  const bool vec = (inner % 4 == 0) && rt_aligned16(x);
+  const int64_t tiles = (inner + (vec ? 128 : 32) - 1) / (vec ? 128 : 32);
+  int64_t splits = 1;
+  if (tiles * outer < target_blocks) {
+    splits = (target_blocks + tiles * outer - 1) / (tiles * outer);
+    const int64_t max_splits = (len + 63) / 64;
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    if (splits > 65535) splits = 65535;
+  }
+  const int64_t rps = (len + splits - 1) / splits;
+  splits = (len + rps - 1) / rps;
+  if (splits > 1 && outer * splits * inner > kStaticScratchFloats)
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION,
+            "rt_reduce_sum_static_scratch: %lld partial sums needed, the fixed workspace holds %lld",
+            (long long)(outer * splits * inner), (long long)kStaticScratchFloats);
+  dim3 grid((unsigned)tiles, (unsigned)splits, (unsigned)outer), block(32, 8);
+  float* dst = splits > 1 ? scratch : out;
+  if (vec) col_reduce<RT_RED_SUM, true><<<grid, block, 0, ctx->stream>>>(x, dst, len, inner, splits, rps, 1.f);
+  else col_reduce<RT_RED_SUM, false><<<grid, block, 0, ctx->stream>>>(x, dst, len, inner, splits, rps, 1.f);
+  RT_LAUNCHED(ctx);
+  if (splits > 1) {
+    // second pass in one launch: the partial sums [outer, splits, inner] are 256-byte aligned, inner % 4 decides the width
+    const bool vec2 = inner % 4 == 0;
+    dim3 grid2((unsigned)((inner + (vec2 ? 128 : 32) - 1) / (vec2 ? 128 : 32)), 1, (unsigned)outer);
+    if (vec2) col_reduce<RT_RED_SUM, true><<<grid2, block, 0, ctx->stream>>>(scratch, out, splits, inner, 1, splits, 1.f);
+    else col_reduce<RT_RED_SUM, false><<<grid2, block, 0, ctx->stream>>>(scratch, out, splits, inner, 1, splits, 1.f);
+    RT_LAUNCHED(ctx);
+  }
+  return RT_OK;
+}
