@@ -707,29 +707,30 @@ tc_gemm_kernel(const LA la, const LB lb, const EPI epi, int K, int k_per_split, 
         epi.store32(m, n0 + c * 32, v, blockIdx.z);
       }
     }
-  } else if (lane == 0) {
-    // ---------------- MMA issuer ----------------
+  } else {
+    // ---------------- MMA issuer: the whole warp runs the loop (operands stay warp-uniform), one elected lane issues ----
     constexpr uint32_t idesc = make_idesc(BN);
+    const uint32_t hi32 = desc_hi32(SBO);
+    uint32_t rot = 0;  // hi*hi accumulator 1 + rot
     for (int it = 0; it < nkb && ok; ++it) {
       const int s = it % STAGES;
-      ok = mbar_wait(bars + 8 * s, (it / STAGES) & 1, status, 3);
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * s, (it / STAGES) & 1, status, 3));
       if (!ok) break;
       tc_fence_after();
-      const uint32_t a_hi = smem_base + s * SL::stage_bytes, a_lo = a_hi + SL::a_bytes;
-      const uint32_t b_hi = a_hi + 2 * SL::a_bytes, b_lo = b_hi + SL::b_bytes;
+      const uint32_t a_hi = desc_lo32(smem_base + s * SL::stage_bytes, LBO), a_lo = a_hi + (SL::a_bytes >> 4);
+      const uint32_t b_hi = a_hi + ((2 * SL::a_bytes) >> 4), b_lo = b_hi + (SL::b_bytes >> 4);
 #pragma unroll
       for (int j = 0; j < BK / 8; ++j) {
-        const uint32_t koff = (uint32_t)j * 2 * LBO;
-        const uint64_t dah = make_desc(a_hi + koff), dal = make_desc(a_lo + koff);
-        const uint64_t dbh = make_desc(b_hi + koff), dbl = make_desc(b_lo + koff);
+        const uint32_t ko = (uint32_t)j * ((2 * LBO) >> 4);
         const int t = it * (BK / 8) + j;  // K-step counter of this tile
-        umma_tf32(tmem_base, dal, dbh, idesc, t != 0);  // cross terms -> accumulator 0
-        umma_tf32(tmem_base, dah, dbl, idesc, 1);
-        umma_tf32(tmem_base + (uint32_t)((1 + t % 3) * BN), dah, dbh, idesc, t >= 3);  // hi*hi -> accumulators 1..3
+        // cross terms -> accumulator 0, hi*hi round-robin -> accumulators 1..3
+        umma_tf32_step_elect(tmem_base, tmem_base + (1 + rot) * BN, a_hi + ko, a_lo + ko, hi32, b_hi + ko, b_lo + ko, hi32, idesc,
+                             t != 0 ? 1u : 0u, t >= 3 ? 1u : 0u);
+        rot = rot == 2 ? 0 : rot + 1;
       }
-      umma_commit(bars + 8 * (STAGES + s));  // frees the stage when these MMAs have read it
+      umma_commit_elect(bars + 8 * (STAGES + s));  // frees the stage when these MMAs have read it
     }
-    if (ok && nkb > 0) umma_commit(bars + 8 * (2 * STAGES));  // accumulator complete
+    if (ok && nkb > 0) umma_commit_elect(bars + 8 * (2 * STAGES));  // accumulator complete
   }
   tc_fence_before();
   __syncthreads();
