@@ -1,0 +1,211 @@
+// Convolutions whose reduction is tiny (Cin*kh*kw <= 16 taps, e.g. the first layer of a CNN on
+// single-channel images): a GEMM formulation would fill a tile with zeros, so these run as direct
+// FP32 kernels.  A thread owns one output pixel and keeps its taps in registers.
+//   forward:          y[b,n,p] = bias[n] + sum_t tap_t(b,p) * w[n,t]
+//   weight gradient:  dw[n,t]  = sum_{b,p} g[b,n,p] * tap_t(b,p)   (per-warp partial sums over a pixel
+//                     range, then a deterministic second pass)
+// tap_t(b,p) = x[b, c, yo*sh-ph+ky, xo*sw-pw+kx] for t = (c,ky,kx), zero outside the image.
+#include "rt_internal.cuh"
+#include "conv_geom.cuh"
+
+rt_status rt_sum_axis_internal(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out,
+                               float scale);
+
+namespace {
+
+constexpr int kMaxTaps = 16;
+constexpr int kThreads = 256;
+
+struct ThinParams {
+  const float* x;   // [Nb, C, H, W]
+  int Nb, C, H, W, N, Ho, Wo, sh, sw;
+  int T;            // C*kh*kw
+  int64_t pixels;   // Nb*Ho*Wo
+  FastDiv d_HoWo, d_Wo;
+  int dy[kMaxTaps], dx[kMaxTaps], off[kMaxTaps];  // tap t: row / column displacement and c*H*W + dy*W + dx
+};
+
+// Reads the TP taps of output pixel (b, yo, xo); entries t >= T are zero.
+template <int TP>
+__device__ __forceinline__ void load_taps(const ThinParams& p, uint32_t b, uint32_t yo, uint32_t xo, float (&tap)[TP]) {
+  const int y0 = (int)yo * p.sh, x0 = (int)xo * p.sw;
+  const float* base = p.x + ((int64_t)b * p.C * p.H + y0) * p.W + x0;
+#pragma unroll
+  for (int t = 0; t < TP; ++t) {
+    const bool in = t < p.T && (unsigned)(y0 + p.dy[t]) < (unsigned)p.H && (unsigned)(x0 + p.dx[t]) < (unsigned)p.W;
+    tap[t] = in ? __ldg(base + p.off[t]) : 0.f;
+  }
+}
+
+template <int TP>
+__global__ void __launch_bounds__(kThreads) thin_conv_forward_kernel(const ThinParams p, const float* __restrict__ w,
+                                                                      const float* __restrict__ bias, float* __restrict__ y) {
+  extern __shared__ __align__(16) float sm[];  // w_s[N][TP], bias_s[N]
+  float* w_s = sm;
+  float* bias_s = sm + p.N * TP;
+  for (int i = threadIdx.x; i < p.N * TP; i += kThreads) {
+    const int n = i / TP, t = i - n * TP;
+    w_s[i] = t < p.T ? __ldg(w + n * p.T + t) : 0.f;
+  }
+  for (int i = threadIdx.x; i < p.N; i += kThreads) bias_s[i] = bias ? __ldg(bias + i) : 0.f;
+  __syncthreads();
+  const int howo = p.Ho * p.Wo;
+  for (int64_t px = (int64_t)blockIdx.x * kThreads + threadIdx.x; px < p.pixels; px += (int64_t)gridDim.x * kThreads) {
+    uint32_t b, r, yo, xo;
+    p.d_HoWo.divmod((uint32_t)px, b, r);
+    p.d_Wo.divmod(r, yo, xo);
+    float tap[TP];
+    load_taps<TP>(p, b, yo, xo, tap);
+    float* out = y + (int64_t)b * p.N * howo + r;
+    for (int n = 0; n < p.N; ++n) {
+      float acc = bias_s[n];
+      const float4* wr = reinterpret_cast<const float4*>(w_s + n * TP);
+#pragma unroll
+      for (int t4 = 0; t4 < TP / 4; ++t4) {
+        const float4 wv = wr[t4];
+        acc = fmaf(tap[t4 * 4 + 0], wv.x, acc);
+        acc = fmaf(tap[t4 * 4 + 1], wv.y, acc);
+        acc = fmaf(tap[t4 * 4 + 2], wv.z, acc);
+        acc = fmaf(tap[t4 * 4 + 3], wv.w, acc);
+      }
+      out[(int64_t)n * howo] = acc;
+    }
+  }
+}
+
+// One block per range of 512 output pixels.  Phase 1: every thread gathers the taps of two pixels (all
+// loads in flight at once) into shared memory, together with the offset of the pixel in g.  Phase 2:
+// warp w owns output channels w*4 .. w*4+3 (+32, +64, ...): lane = pixel, 4 x TP accumulators per lane
+// fed from shared memory, reduced over the lanes at the end.  part[range][n][t], t < T.
+constexpr int kRangePixels = 512;
+template <int TP>
+__global__ void __launch_bounds__(kThreads) thin_conv_dw_kernel(const ThinParams p, const float* __restrict__ g,
+                                                                 float* __restrict__ part) {
+  __shared__ float taps_s[TP][kRangePixels];
+  __shared__ int goff_s[kRangePixels];  // b*N*Ho*Wo + pixel-in-image, or -1 past the end
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int howo = p.Ho * p.Wo;
+  const int64_t p0 = (int64_t)blockIdx.x * kRangePixels;
+#pragma unroll
+  for (int h = 0; h < kRangePixels / kThreads; ++h) {
+    const int i = threadIdx.x + h * kThreads;
+    const int64_t px = p0 + i;
+    float tap[TP];
+    int go = -1;
+    if (px < p.pixels) {
+      uint32_t b, r, yo, xo;
+      p.d_HoWo.divmod((uint32_t)px, b, r);
+      p.d_Wo.divmod(r, yo, xo);
+      load_taps<TP>(p, b, yo, xo, tap);
+      go = (int)b * p.N * howo + (int)r;
+    } else {
+#pragma unroll
+      for (int t = 0; t < TP; ++t) tap[t] = 0.f;
+    }
+#pragma unroll
+    for (int t = 0; t < TP; ++t) taps_s[t][i] = tap[t];
+    goff_s[i] = go;
+  }
+  __syncthreads();
+  for (int n0 = warp * 4; n0 < p.N; n0 += (kThreads / 32) * 4) {
+    float acc[4][TP];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int t = 0; t < TP; ++t) acc[i][t] = 0.f;
+    constexpr int kUnroll = 4;
+    for (int k0 = 0; k0 < kRangePixels / 32; k0 += kUnroll) {
+      float gv[kUnroll][4];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int go = goff_s[(k0 + u) * 32 + lane];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) gv[u][i] = (go >= 0 && n0 + i < p.N) ? __ldg(g + go + (int64_t)(n0 + i) * howo) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+#pragma unroll
+        for (int t = 0; t < TP; ++t) {
+          const float tv = taps_s[t][(k0 + u) * 32 + lane];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[i][t] = fmaf(gv[u][i], tv, acc[i][t]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int t = 0; t < TP; ++t) {
+        float v = acc[i][t];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && n0 + i < p.N && t < p.T) part[((int64_t)blockIdx.x * p.N + n0 + i) * p.T + t] = v;
+      }
+  }
+}
+
+bool make_params(const ConvGeom& g, const float* x, ThinParams* p) {
+  const int T = g.Cx * g.kh * g.kw;
+  const int64_t pixels = (int64_t)g.Nb * g.Hy * g.Wy;
+  if (T < 1 || T > kMaxTaps || pixels < 1 || pixels >= (1ll << 31) || (int64_t)g.Cx * g.Hx * g.Wx >= (1ll << 30)) return false;
+  p->x = x;
+  p->Nb = g.Nb; p->C = g.Cx; p->H = g.Hx; p->W = g.Wx; p->N = g.Cy; p->Ho = g.Hy; p->Wo = g.Wy; p->sh = g.sh; p->sw = g.sw;
+  p->T = T;
+  p->pixels = pixels;
+  p->d_HoWo.init(g.Hy * g.Wy);
+  p->d_Wo.init(g.Wy);
+  for (int t = 0; t < kMaxTaps; ++t) p->dy[t] = p->dx[t] = p->off[t] = 0;
+  int t = 0;
+  for (int c = 0; c < g.Cx; ++c)
+    for (int ky = 0; ky < g.kh; ++ky)
+      for (int kx = 0; kx < g.kw; ++kx, ++t) {
+        p->dy[t] = ky - g.ph;
+        p->dx[t] = kx - g.pw;
+        p->off[t] = (c * g.Hx + ky - g.ph) * g.Wx + kx - g.pw;
+      }
+  return true;
+}
+
+}  // namespace
+
+// y = conv2d(x, w) + bias for Cx*kh*kw <= 16; RT_ERR_UNIMPLEMENTED otherwise.
+rt_status rt_conv_forward_thin_internal(rt_ctx* ctx, const float* x, const float* w, const float* bias, const ConvGeom& g,
+                                        float* y) {
+  ThinParams p;
+  if (g.Cy < 1 || g.Cy > 512 || !make_params(g, x, &p)) return RT_ERR_UNIMPLEMENTED;
+  const int TP = (p.T + 3) / 4 * 4;
+  const size_t smem = sizeof(float) * (size_t)(g.Cy * TP + g.Cy);
+  const int grid = rt_grid_for(ctx, p.pixels, kThreads, 16);
+  switch (TP) {
+    case 4: thin_conv_forward_kernel<4><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
+    case 8: thin_conv_forward_kernel<8><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
+    case 12: thin_conv_forward_kernel<12><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
+    default: thin_conv_forward_kernel<16><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
+  }
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+// dw[Cy, Cx*kh*kw] = sum over pixels of g * im2col(x) for Cx*kh*kw <= 16; RT_ERR_UNIMPLEMENTED otherwise.
+rt_status rt_conv_weight_grad_thin_internal(rt_ctx* ctx, const float* x, const float* gy, const ConvGeom& g, float* dw) {
+  ThinParams p;
+  if (g.Cy < 1 || !make_params(g, x, &p)) return RT_ERR_UNIMPLEMENTED;
+  const int TP = (p.T + 3) / 4 * 4;
+  const int ranges = (int)((p.pixels + kRangePixels - 1) / kRangePixels);
+  RtScratch part(ctx);
+  float* dst = dw;
+  if (ranges > 1) {
+    rt_status st = part.alloc(sizeof(float) * (size_t)ranges * g.Cy * p.T);
+    if (st != RT_OK) return st;
+    dst = part.as<float>();
+  }
+  if ((int64_t)g.Nb * g.Cy * g.Hy * g.Wy >= (1ll << 31)) return RT_ERR_UNIMPLEMENTED;
+  switch (TP) {
+    case 4: thin_conv_dw_kernel<4><<<ranges, kThreads, 0, ctx->stream>>>(p, gy, dst); break;
+    case 8: thin_conv_dw_kernel<8><<<ranges, kThreads, 0, ctx->stream>>>(p, gy, dst); break;
+    case 12: thin_conv_dw_kernel<12><<<ranges, kThreads, 0, ctx->stream>>>(p, gy, dst); break;
+    default: thin_conv_dw_kernel<16><<<ranges, kThreads, 0, ctx->stream>>>(p, gy, dst); break;
+  }
+  RT_LAUNCHED(ctx);
+  if (ranges > 1) return rt_sum_axis_internal(ctx, dst, 1, ranges, (int64_t)g.Cy * p.T, dw, 1.f);
+  return RT_OK;
+}

@@ -24,6 +24,9 @@ rt_status rt_conv_forward_tc_internal(rt_ctx* ctx, const float* x, const float* 
 rt_status rt_conv_gather_tc_internal(rt_ctx* ctx, const float* y, const float* w, const float* bias, const ConvGeom& g,
                                      int cm, float* out);
 rt_status rt_conv_weight_grad_tc_internal(rt_ctx* ctx, const float* x, const float* y, const ConvGeom& g, float* dw);
+rt_status rt_conv_forward_thin_internal(rt_ctx* ctx, const float* x, const float* w, const float* bias, const ConvGeom& g,
+                                        float* y);
+rt_status rt_conv_weight_grad_thin_internal(rt_ctx* ctx, const float* x, const float* gy, const ConvGeom& g, float* dw);
 rt_status rt_conv_window_tc_internal(rt_ctx* ctx, const float* src, int Nb, int C, int H, int W, int ph, int pw, const float* w,
                                      int N, int kh, int kw, int sn, int sc, int sky, int skx, int off0, const float* bias,
                                      float* out);
@@ -351,6 +354,10 @@ rt_status check_conv_args(rt_ctx* ctx, int64_t n, int64_t cin, int64_t h, int64_
 rt_status conv_forward_like(rt_ctx* ctx, const float* x, const float* w, const float* bias, const ConvGeom& g, float* y) {
   int64_t M = g.Cy, N = (int64_t)g.Nb * g.Hy * g.Wy, K = (int64_t)g.Cx * g.kh * g.kw;
   if (M == 0 || N == 0) return RT_OK;
+  if (ctx->use_tensor_cores) {  // tiny reductions: direct FP32 kernel
+    rt_status st = rt_conv_forward_thin_internal(ctx, x, w, bias, g, y);
+    if (st != RT_ERR_UNIMPLEMENTED) return st;
+  }
   if (ctx->use_tensor_cores && g.sh == 1 && g.sw == 1) {
     rt_status st = rt_conv_window_tc_internal(ctx, x, g.Nb, g.Cx, g.Hx, g.Wx, g.ph, g.pw, w, g.Cy, g.kh, g.kw, g.Cx * g.kh * g.kw,
                                               g.kh * g.kw, g.kw, 1, 0, bias, y);
@@ -370,6 +377,10 @@ rt_status conv_forward_like(rt_ctx* ctx, const float* x, const float* w, const f
 // dw[Cy, Cx*kh*kw] = sum over (b,yo,xo) of y * im2col(x)
 rt_status conv_weight_grad_like(rt_ctx* ctx, const float* x, const float* y, const ConvGeom& g, float* dw) {
   int64_t M = g.Cy, N = (int64_t)g.Cx * g.kh * g.kw, K = (int64_t)g.Nb * g.Hy * g.Wy;
+  if (ctx->use_tensor_cores && M > 0 && N > 0 && K > 0) {  // tiny reductions: direct FP32 kernel
+    rt_status st = rt_conv_weight_grad_thin_internal(ctx, x, y, g, dw);
+    if (st != RT_ERR_UNIMPLEMENTED) return st;
+  }
   if (ctx->use_tensor_cores && M > 0 && N > 0) {
     rt_status st = rt_conv_weight_grad_tc_internal(ctx, x, y, g, dw);
     if (st != RT_ERR_UNIMPLEMENTED) return st;
