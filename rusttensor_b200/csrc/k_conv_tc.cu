@@ -30,7 +30,9 @@ namespace conv {
 constexpr int kProducerWarps = 8;
 constexpr int kThreads = (kProducerWarps + 1) * 32;
 constexpr int kTileM = 128;
-constexpr int kAccs = 4;  // accumulator 0: cross terms; 1..3: hi*hi round-robin (bounds the truncating-add error)
+// Accumulator columns per set: [hi*hi | hi*lo] (2*BN, one MMA against the stacked hi/lo weight tile) and lo*hi (BN).
+// The reduction of one tile is at most a few hundred K-steps, short enough for a single accumulation chain.
+constexpr int kAccCols = 3;
 constexpr uint32_t kSmemLimit = 227 * 1024;
 // after the window stages: 9 mbarriers, the tensor-memory address slot (16 bytes), 64 bias values
 constexpr uint32_t kTmemSlotOffset = 9 * 8, kBiasOffset = kTmemSlotOffset + 16, kTailBytes = kBiasOffset + 64 * 4;
@@ -53,7 +55,7 @@ struct Params {
 };
 
 // Packs w into the shared-memory image of the B operand: for tap t the K-major tile
-// [BN rows x 4*NQ channels], core matrices of 8 rows x 4 channels, K-chunks 128 bytes apart,
+// [2*BN rows x 4*NQ channels] (BN hi rows, then BN lo rows), core matrices of 8 rows x 4 channels, K-chunks 128 bytes apart,
 // 8-row groups NQ*128 bytes apart.  value(n, c, t) = w[n*sn + c*sc + ky*sky + kx*skx + off0].
 __global__ void pack_weights_kernel(const float* __restrict__ w, float* __restrict__ img, int N, int C, int BN, int NQ,
                                     int kh, int kw, int sn, int sc, int sky, int skx, int off0) {
@@ -67,24 +69,24 @@ __global__ void pack_weights_kernel(const float* __restrict__ w, float* __restri
     float v = 0.f;
     if (n < N && c < C) v = __ldg(w + n * sn + c * sc + ky * sky + kx * skx + off0);
     const float hi = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
-    const int dst = t * per_tap + (n >> 3) * (NQ * 32) + (c >> 2) * 32 + (n & 7) * 4 + (c & 3);
+    const int dst = t * 2 * per_tap + (n >> 3) * (NQ * 32) + (c >> 2) * 32 + (n & 7) * 4 + (c & 3);
     img[dst] = hi;
-    img[total + dst] = v - hi;
+    img[per_tap + dst] = v - hi;  // the lo tile follows the hi tile of the same tap: together a 2*BN-row operand
   }
 }
 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p, int* status) {
   extern __shared__ __align__(128) char smem[];
-  constexpr uint32_t kTmemCols = 2 * kAccs * BN;  // two accumulator sets
-  static_assert(kTmemCols <= 512, "tensor memory holds 512 columns");
+  constexpr uint32_t kTmemCols = BN == 32 ? 256 : 512;  // two accumulator sets of 3*BN columns, rounded to a power of two
+  static_assert(2 * kAccCols * BN <= kTmemCols, "accumulator sets must fit the allocation");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int taps = p.kh * p.kw;
   const uint32_t plane = (uint32_t)p.win * 16;               // bytes of one channel-quad plane
   const uint32_t a_half = (uint32_t)p.CGQ * plane;           // hi (or lo) part of a window stage
   const uint32_t a_stage = 2 * a_half;
   const uint32_t b_half = (uint32_t)p.wimg_floats * 4;       // hi (or lo) weight image
-  const uint32_t tap_bytes = (uint32_t)BN * p.NQ * 16;       // one tap of one image
+  const uint32_t tap_bytes = 2u * BN * p.NQ * 16;            // one tap: hi tile + lo tile
   // shared memory: weights (hi, lo) | window stage 0 | window stage 1 | barriers | tmem slot
   const uint32_t off_a = 2 * b_half;
   const uint32_t off_bar = off_a + 2 * a_stage;
@@ -134,17 +136,16 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
 #pragma unroll
       for (int c0 = 0; c0 < CW; c0 += 16) {
         const int col = half * CW + c0;
-        const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(set * kAccs * BN + col);
-        uint32_t r[kAccs][16];
+        const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(set * kAccCols * BN + col);
+        uint32_t r[kAccCols][16];
 #pragma unroll
-        for (int a = 0; a < kAccs; ++a) tmem_ld16_nowait(t0 + (uint32_t)(a * BN), r[a]);
+        for (int a = 0; a < kAccCols; ++a) tmem_ld16_nowait(t0 + (uint32_t)(a * BN), r[a]);
         tmem_wait_ld();
         if (valid) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int n = col + j;
-            const float v = ((__uint_as_float(r[0][j]) + __uint_as_float(r[1][j])) + __uint_as_float(r[2][j])) +
-                            __uint_as_float(r[3][j]);
+            const float v = __uint_as_float(r[0][j]) + (__uint_as_float(r[1][j]) + __uint_as_float(r[2][j]));
             if (n < p.N) q[(int64_t)n * howo] = v + bias_s[n];
           }
         }
@@ -231,10 +232,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
     // ---------------- MMA issuer: the whole warp runs the loop, one elected lane issues ----------------
     // Descriptors are kept as 32-bit low words (start address, in 16-byte units, plus the constant
     // leading-dimension field) that advance by additions; the issue loop has no divisions.
-    constexpr uint32_t idesc = make_idesc(BN);
+    constexpr uint32_t idesc_n = make_idesc(BN), idesc_2n = make_idesc(2 * BN);
     const uint32_t a_hi32 = desc_hi32(128), b_hi32 = desc_hi32((uint32_t)p.NQ * 128);
     const uint32_t a_kstep = (2 * plane) >> 4, b_kstep = 256 >> 4;   // two channel quads per K-step
-    const uint32_t a_lo_delta = a_half >> 4, b_lo_delta = b_half >> 4;  // hi image -> lo image
+    const uint32_t a_lo_delta = a_half >> 4;  // hi window -> lo window
     const uint32_t tap_step = tap_bytes >> 4;
     // resident weights: bulk copies of the packed image, in pieces of at most 32 KiB
     {
@@ -255,9 +256,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
       if (i >= 2) ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * (6 + set), ((i >> 1) - 1) & 1, status, 6));
       if (!ok) break;
       tc_fence_after();
-      const uint32_t acc = tmem_base + (uint32_t)(set * kAccs * BN);
-      uint32_t first = 0;          // becomes 1 after the first K-step of the tile
-      uint32_t rot = 0, seen = 0;  // hi*hi accumulator 1 + rot; `seen` counts K-steps up to 3
+      const uint32_t acc = tmem_base + (uint32_t)(set * kAccCols * BN);
+      uint32_t first = 0;  // becomes 1 after the first K-step of the tile
       for (int g = 0; g < p.groups && ok; ++g, ++scnt) {
         const int slot = scnt & 1;
         ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * slot, (scnt >> 1) & 1, status, 7));
@@ -272,11 +272,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
           for (int kx = 0; kx < p.kw; ++kx, ++a_tap, b_tap += tap_step) {
             uint32_t a = a_tap, b = b_tap;
             for (int j = 0; j < nk; ++j, a += a_kstep, b += b_kstep) {
-              umma_tf32_step_elect(acc, acc + (1 + rot) * BN, a, a + a_lo_delta, a_hi32, b, b + b_lo_delta, b_hi32, idesc, first,
-                             seen >= 3 ? 1u : 0u);
+              umma_tf32_pair_elect(acc, acc + 2 * BN, a, a + a_lo_delta, a_hi32, b, b_hi32, idesc_2n, idesc_n, first);
               first = 1;
-              rot = rot == 2 ? 0 : rot + 1;
-              seen = seen < 3 ? seen + 1 : 3;
             }
           }
         }
@@ -308,7 +305,6 @@ rt_status rt_conv_window_tc_internal(rt_ctx* ctx, const float* src, int Nb, int 
   const int Hp = H + 2 * ph, Wp = W + 2 * pw;
   const int Ho = Hp - kh + 1, Wo = Wp - kw + 1;
   if (Ho < 1 || Wo < 1) return RT_ERR_UNIMPLEMENTED;
-  if (kh * kw * ((C + 7) / 8) < 3) return RT_ERR_UNIMPLEMENTED;  // every hi*hi accumulator must be written at least once
   const int64_t positions = (int64_t)Nb * Hp * Wp;
   if (positions + kTileM >= (1ll << 31) || (int64_t)Nb * C * H * W >= (1ll << 31) || (int64_t)Nb * N * Ho * Wo >= (1ll << 31))
     return RT_ERR_UNIMPLEMENTED;

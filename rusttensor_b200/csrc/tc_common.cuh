@@ -136,6 +136,27 @@ __device__ __forceinline__ void umma_tf32_step_elect(uint32_t d_cross, uint32_t 
         "r"(idesc), "r"(acc_cross), "r"(acc_main)
       : "memory");
 }
+// One 3xTF32 K-step as two MMAs: the B operand tile holds the hi rows followed by the lo rows
+// (2N rows), so A_hi x [B_hi; B_lo] yields hi*hi and hi*lo side by side in `d_wide` (2N columns), and
+// A_lo x B_hi goes to `d_cross` (N columns).  An MMA with N <= 128 costs the same whatever N is, so
+// this is a third cheaper than three separate MMAs.  Issued by one elected lane of a converged warp.
+__device__ __forceinline__ void umma_tf32_pair_elect(uint32_t d_wide, uint32_t d_cross, uint32_t a_hi_lo32, uint32_t a_lo_lo32,
+                                                     uint32_t a_hi32, uint32_t b_lo32, uint32_t b_hi32, uint32_t idesc_2n,
+                                                     uint32_t idesc_n, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred pa, pe;\n\t"
+      ".reg .b64 dah, dal, db;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "setp.ne.b32 pa, %9, 0;\n\t"
+      "mov.b64 dah, {%2, %4};\n\t"
+      "mov.b64 dal, {%3, %4};\n\t"
+      "mov.b64 db, {%5, %6};\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::tf32 [%0], dah, db, %7, pa;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::tf32 [%1], dal, db, %8, pa;\n\t}"
+      ::"r"(d_wide), "r"(d_cross), "r"(a_hi_lo32), "r"(a_lo_lo32), "r"(a_hi32), "r"(b_lo32), "r"(b_hi32), "r"(idesc_2n),
+        "r"(idesc_n), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
   asm volatile(
       "{\n\t.reg .pred pe;\n\t"
