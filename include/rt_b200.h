@@ -64,6 +64,24 @@ rt_status rt_fill(rt_ctx* ctx, float* dst, float value, int64_t n);             
 rt_status rt_host_alloc(rt_ctx* ctx, size_t bytes, void** out);                      /* pinned host memory */
 rt_status rt_host_free(rt_ctx* ctx, void* ptr);
 rt_status rt_sync(rt_ctx* ctx);
+/* ---- overlapping the next step's input upload with the running step (new; the reference uploads synchronously
+ * in Backend::from_vec).  An rt_upload owns two pinned host buffers and two device staging buffers of `bytes` each
+ * and a copy stream.  rt_upload_host_buffer returns the pinned buffer to fill for the next submit (it first waits
+ * until the copy that last read this buffer has finished).  rt_upload_submit copies it to its staging buffer on the
+ * copy stream, makes the context's stream wait for that copy, then copies staging -> dst on the context's stream and
+ * switches to the other buffer pair.  Work already queued on the context's stream that reads `dst` is not disturbed,
+ * so the host can submit step i+1 while step i is still running. */
+typedef struct rt_upload rt_upload;
+rt_status rt_upload_create(rt_ctx* ctx, size_t bytes, rt_upload** out);
+rt_status rt_upload_destroy(rt_ctx* ctx, rt_upload* up);
+rt_status rt_upload_host_buffer(rt_ctx* ctx, rt_upload* up, void** pinned);
+rt_status rt_upload_submit(rt_ctx* ctx, rt_upload* up, void* dst);
+/* Events on the context's stream: record after queued work, wait on the host later. */
+typedef struct rt_event rt_event;
+rt_status rt_event_create(rt_ctx* ctx, rt_event** out);
+rt_status rt_event_destroy(rt_ctx* ctx, rt_event* ev);
+rt_status rt_event_record(rt_ctx* ctx, rt_event* ev);
+rt_status rt_event_synchronize(rt_ctx* ctx, rt_event* ev);
 void* rt_stream(rt_ctx* ctx);                                                        /* the cudaStream_t */
 rt_status rt_mem_stats(rt_ctx* ctx, int64_t* bytes_reserved, int64_t* bytes_in_use, int64_t* n_device_allocs);
 rt_status rt_kernel_launch_count(rt_ctx* ctx, int64_t* launches);                    /* kernels launched by this library so far */

@@ -40,10 +40,20 @@ struct DpTrainer {
   Tensor captured_loss;
   rt_graph* graph = nullptr;
   bool have_loss = false;
+  // pipelined steps: double-buffered uploads, two loss slots with completion events
+  std::vector<rt_upload*> uploads;
+  float* pipe_loss[2] = {nullptr, nullptr};
+  rt_event* pipe_done[2] = {nullptr, nullptr};
+  int64_t pipe_steps = 0;
 
   ~DpTrainer() {
     rt_ctx* c = B200Backend::ctx_slot();
     if (!c) return;
+    for (rt_upload* u : uploads) rt_upload_destroy(c, u);
+    for (int i = 0; i < 2; ++i) {
+      if (pipe_loss[i]) rt_host_free(c, pipe_loss[i]);
+      if (pipe_done[i]) rt_event_destroy(c, pipe_done[i]);
+    }
     if (graph) rt_graph_destroy(c, graph);
     for (float* p : pinned_in) rt_host_free(c, p);
     if (pinned_loss) rt_host_free(c, pinned_loss);
@@ -179,6 +189,58 @@ struct DpTrainer {
     exchange_and_update();
     if (host_inputs) B200Backend::check(rt_memcpy_d2h_async(c, pinned_loss, captured_loss.data().ptr(), sizeof(float)));
   }
+
+  // ---- pipelined steps: the host runs one step ahead of the device ----
+  void pipe_setup() {
+    if (!uploads.empty()) return;
+    rt_ctx* c = B200Backend::ctx();
+    for (auto& x : inputs) {
+      rt_upload* u = nullptr;
+      B200Backend::check(rt_upload_create(c, sizeof(float) * x.size(), &u));
+      uploads.push_back(u);
+    }
+    for (int i = 0; i < 2; ++i) {
+      void* lp = nullptr;
+      B200Backend::check(rt_host_alloc(c, sizeof(float), &lp));
+      pipe_loss[i] = (float*)lp;
+      B200Backend::check(rt_event_create(c, &pipe_done[i]));
+    }
+  }
+  float* pipe_buffer(int i) {
+    pipe_setup();
+    void* p = nullptr;
+    B200Backend::check(rt_upload_host_buffer(B200Backend::ctx(), uploads.at(i), &p));
+    return (float*)p;
+  }
+  // Submits the buffers handed out by pipe_buffer, enqueues the step and the read-back of its loss, and
+  // returns the loss of the PREVIOUS pipelined step (its work finished while this one was being enqueued).
+  bool step_pipelined(float* prev_loss) {
+    pipe_setup();
+    if (!graph) capture();
+    rt_ctx* c = B200Backend::ctx();
+    for (size_t i = 0; i < inputs.size(); ++i) {
+      B200Backend::make_unique(inputs[i].data_mut());
+      B200Backend::check(rt_upload_submit(c, uploads[i], inputs[i].data().ptr()));
+    }
+    B200Backend::check(rt_graph_launch(c, graph));
+    exchange_and_update();
+    const int k = (int)(pipe_steps & 1);
+    B200Backend::check(rt_memcpy_d2h_async(c, pipe_loss[k], captured_loss.data().ptr(), sizeof(float)));
+    B200Backend::check(rt_event_record(c, pipe_done[k]));
+    const bool have_prev = pipe_steps > 0;
+    if (have_prev) {
+      B200Backend::check(rt_event_synchronize(c, pipe_done[k ^ 1]));
+      *prev_loss = *pipe_loss[k ^ 1];
+    }
+    ++pipe_steps;
+    return have_prev;
+  }
+  float pipe_flush() {
+    if (pipe_steps == 0) throw Error::invalid_op("no pipelined step has run yet");
+    const int k = (int)((pipe_steps - 1) & 1);
+    B200Backend::check(rt_event_synchronize(B200Backend::ctx(), pipe_done[k]));
+    return *pipe_loss[k];
+  }
 };
 
 std::map<int64_t, std::shared_ptr<DpTrainer>>& dp_table() {
@@ -296,6 +358,19 @@ int rth_dp_last_loss(int64_t h, float* loss) {
     B200Backend::check(rt_sync(B200Backend::ctx()));
     *loss = *dp_get(h).pinned_loss;
   });
+}
+// Pipelined steps (the host enqueues step i+1 while step i runs; the upload of step i+1 overlaps step i).
+// rth_dp_pipeline_buffer: pinned buffer to fill with input i of the next step.
+int rth_dp_pipeline_buffer(int64_t h, int i, float** out) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { *out = dp_get(h).pipe_buffer(i); });
+}
+// Enqueues one step from the pipeline buffers; *has_prev tells whether *prev_loss (the previous step's loss) is valid.
+int rth_dp_step_pipelined(int64_t h, float* prev_loss, int* has_prev) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { *has_prev = dp_get(h).step_pipelined(prev_loss) ? 1 : 0; });
+}
+// Waits for the last pipelined step and returns its loss.
+int rth_dp_pipeline_flush(int64_t h, float* loss) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { *loss = dp_get(h).pipe_flush(); });
 }
 int rth_dp_loss_tensor(int64_t h, int64_t* out) {
   return rt::capi::guarded<B200Backend>([&](auto& r) {

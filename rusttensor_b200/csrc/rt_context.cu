@@ -216,6 +216,120 @@ rt_status rt_sync(rt_ctx* ctx) {
 
 void* rt_stream(rt_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
+// ---- double-buffered input upload ------------------------------------------------------------
+struct rt_upload {
+  size_t bytes = 0;
+  cudaStream_t copy_stream = nullptr;
+  void* pinned[2] = {nullptr, nullptr};
+  void* staging[2] = {nullptr, nullptr};
+  cudaEvent_t copied[2] = {nullptr, nullptr};    // H2D of this pair finished (copy stream)
+  cudaEvent_t consumed[2] = {nullptr, nullptr};  // staging -> dst of this pair finished (context stream)
+  bool used[2] = {false, false};
+  int next = 0;
+};
+
+rt_status rt_upload_destroy(rt_ctx* ctx, rt_upload* up) {
+  RT_CHECK_CTX(ctx);
+  if (!up) return RT_OK;
+  if (up->copy_stream) cudaStreamSynchronize(up->copy_stream);
+  cudaStreamSynchronize(ctx->stream);
+  for (int i = 0; i < 2; ++i) {
+    if (up->pinned[i]) cudaFreeHost(up->pinned[i]);
+    if (up->staging[i]) cudaFree(up->staging[i]);
+    if (up->copied[i]) cudaEventDestroy(up->copied[i]);
+    if (up->consumed[i]) cudaEventDestroy(up->consumed[i]);
+  }
+  if (up->copy_stream) cudaStreamDestroy(up->copy_stream);
+  delete up;
+  return RT_OK;
+}
+
+rt_status rt_upload_create(rt_ctx* ctx, size_t bytes, rt_upload** out) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, out);
+  *out = nullptr;
+  rt_upload* up = new rt_upload();
+  up->bytes = bytes ? bytes : 1;
+  cudaError_t e = cudaStreamCreateWithFlags(&up->copy_stream, cudaStreamNonBlocking);
+  for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
+    e = cudaHostAlloc(&up->pinned[i], up->bytes, cudaHostAllocDefault);
+    if (e == cudaSuccess) e = cudaMalloc(&up->staging[i], up->bytes);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&up->copied[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&up->consumed[i], cudaEventDisableTiming);
+  }
+  if (e != cudaSuccess) {
+    rt_upload_destroy(ctx, up);
+    RT_FAIL(ctx, e == cudaErrorMemoryAllocation ? RT_ERR_OOM : RT_ERR_CUDA, "rt_upload_create: %s", cudaGetErrorString(e));
+  }
+  *out = up;
+  return RT_OK;
+}
+
+rt_status rt_upload_host_buffer(rt_ctx* ctx, rt_upload* up, void** pinned) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, up);
+  RT_CHECK_PTR(ctx, pinned);
+  const int k = up->next;
+  if (up->used[k]) RT_CUDA(ctx, cudaEventSynchronize(up->copied[k]));  // the copy that last read this buffer
+  *pinned = up->pinned[k];
+  return RT_OK;
+}
+
+rt_status rt_upload_submit(rt_ctx* ctx, rt_upload* up, void* dst) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, up);
+  RT_CHECK_PTR(ctx, dst);
+  if (ctx->capturing) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_upload_submit during graph capture");
+  const int k = up->next;
+  // the staging buffer may still be read by the staging -> dst copy of two submits ago
+  if (up->used[k]) RT_CUDA(ctx, cudaStreamWaitEvent(up->copy_stream, up->consumed[k], 0));
+  RT_CUDA(ctx, cudaMemcpyAsync(up->staging[k], up->pinned[k], up->bytes, cudaMemcpyHostToDevice, up->copy_stream));
+  RT_CUDA(ctx, cudaEventRecord(up->copied[k], up->copy_stream));
+  RT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, up->copied[k], 0));
+  RT_CUDA(ctx, cudaMemcpyAsync(dst, up->staging[k], up->bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  RT_CUDA(ctx, cudaEventRecord(up->consumed[k], ctx->stream));
+  up->used[k] = true;
+  up->next = k ^ 1;
+  return RT_OK;
+}
+
+// ---- events on the context's stream -----------------------------------------------------------
+struct rt_event {
+  cudaEvent_t ev = nullptr;
+};
+rt_status rt_event_create(rt_ctx* ctx, rt_event** out) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, out);
+  rt_event* e = new rt_event();
+  cudaError_t err = cudaEventCreateWithFlags(&e->ev, cudaEventDisableTiming);
+  if (err != cudaSuccess) {
+    delete e;
+    RT_FAIL(ctx, RT_ERR_CUDA, "rt_event_create: %s", cudaGetErrorString(err));
+  }
+  *out = e;
+  return RT_OK;
+}
+rt_status rt_event_destroy(rt_ctx* ctx, rt_event* ev) {
+  RT_CHECK_CTX(ctx);
+  if (ev) {
+    if (ev->ev) cudaEventDestroy(ev->ev);
+    delete ev;
+  }
+  return RT_OK;
+}
+rt_status rt_event_record(rt_ctx* ctx, rt_event* ev) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, ev);
+  RT_CUDA(ctx, cudaEventRecord(ev->ev, ctx->stream));
+  return RT_OK;
+}
+rt_status rt_event_synchronize(rt_ctx* ctx, rt_event* ev) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, ev);
+  RT_CUDA(ctx, cudaEventSynchronize(ev->ev));
+  return RT_OK;
+}
+
 rt_status rt_device_status(rt_ctx* ctx, int* code) {
   RT_CHECK_CTX(ctx);
   RT_CHECK_PTR(ctx, code);

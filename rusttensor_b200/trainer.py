@@ -109,6 +109,27 @@ class DataParallelTrainer:
         self._call("dp_last_loss", C.c_int64(self.handle), C.byref(loss))
         return loss.value
 
+    # ---- pipelined steps: the upload of step i+1 overlaps the device work of step i ----
+    def pipeline_buffer(self, i):
+        """numpy view of the pinned host buffer to fill with input ``i`` of the NEXT pipelined step
+        (two buffers alternate; the call waits until the copy that last read this one has finished)."""
+        p = _f32p()
+        self._call("dp_pipeline_buffer", C.c_int64(self.handle), C.c_int(i), C.byref(p))
+        return np.ctypeslib.as_array(p, shape=tuple(self.inputs[i].shape))
+
+    def step_pipelined(self):
+        """Enqueues one step from the pipeline buffers and returns the loss of the previous pipelined
+        step (None for the first one): the host never waits for the step it has just enqueued."""
+        loss, has = C.c_float(0), C.c_int(0)
+        self._call("dp_step_pipelined", C.c_int64(self.handle), C.byref(loss), C.byref(has))
+        return loss.value if has.value else None
+
+    def pipeline_flush(self):
+        """Waits for the last pipelined step and returns its loss."""
+        loss = C.c_float(0)
+        self._call("dp_pipeline_flush", C.c_int64(self.handle), C.byref(loss))
+        return loss.value
+
     def loss_tensor(self):
         h = C.c_int64(0)
         self._call("dp_loss_tensor", C.c_int64(self.handle), C.byref(h))

@@ -156,3 +156,37 @@ def test_graph_replay_is_deterministic_and_uses_fresh_inputs(gpu_engine):
     assert runs[0][0][0] != runs[0][0][1]
     for a, b in zip(runs[0][1], runs[1][1]):
         assert np.array_equal(a, b)
+
+
+def test_pipelined_steps_equal_plain_steps(gpu_engine):
+    """step_pipelined (double-buffered upload on a copy stream, loss read one step late) computes exactly what
+    step() + last_loss() computes, also when the host runs several steps ahead of the device."""
+    dims = SMALL[3]
+    params, in_a = workload_data(3, dims, seed=6)
+    _, in_b = workload_data(3, dims, seed=7)
+    _, in_c = workload_data(3, dims, seed=8)
+    sequence = [in_a, in_b, in_c, in_a, in_b]
+
+    def fresh():
+        tr = rusttensor_b200.DataParallelTrainer(3, dims)
+        for t, p in zip(tr.params, params):
+            t.update_from_host(p)
+        return tr
+
+    plain = fresh()
+    ref = []
+    for ins in sequence:
+        plain.step(ins)
+        ref.append(plain.last_loss())
+    piped = fresh()
+    got = []
+    for ins in sequence:
+        for i, a in enumerate(ins):
+            piped.pipeline_buffer(i)[...] = a
+        prev = piped.step_pipelined()
+        if prev is not None:
+            got.append(prev)
+    got.append(piped.pipeline_flush())
+    assert got == ref
+    for a, b in zip(plain.params, piped.params):
+        assert np.array_equal(a.numpy(), b.numpy())
