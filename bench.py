@@ -173,6 +173,77 @@ def measure_dominant_kernel(rt, capi, config, dims, pk):
             "peak_source": f"{pk['source']} bf16 burst {pk['bf16']} TFLOP/s / 6 (TF32 = bf16/2, three TF32 MMAs per fp32 product)"}
 
 
+def kernel_bandwidth_table(capi, pk, rows=4096, cols=4096):
+    """Times the HBM-bound kernels of the path one by one at the shapes of the element-wise / reduction
+    micro-benchmark (X [4096,4096], b [4096]): CUDA events on the library's stream, an L2 flush (256 MB fill)
+    before every timed launch, mean of 10.  Bytes are the algorithmic ones: 4 x (elements of each distinct operand
+    read at its un-broadcast size + elements written)."""
+    from rusttensor_b200.capi import BINARY, REDUCE, UNARY
+
+    r = np.random.default_rng(0)
+    n = rows * cols
+    X = capi.to_device(r.standard_normal((rows, cols)).astype(np.float32))
+    G = capi.to_device(r.standard_normal((rows, cols)).astype(np.float32))
+    A = capi.to_device(r.standard_normal((rows, cols)).astype(np.float32))
+    bvec = capi.to_device(r.standard_normal((cols,)).astype(np.float32))
+    grow = capi.to_device(r.standard_normal((rows,)).astype(np.float32))
+    D1, D2 = capi.empty((rows, cols)), capi.empty((rows, cols))
+    dcol, drow = capi.empty((cols,)), capi.empty((rows,))
+    m, v = capi.to_device(np.zeros((rows, cols), np.float32)), capi.to_device(np.zeros((rows, cols), np.float32))
+    pn, pc, ph = 256, 32, 28
+    pool_g = capi.to_device(r.standard_normal((pn, pc, ph // 2, ph // 2)).astype(np.float32))
+    pool_idx = capi.to_device(r.integers(0, 4, (pn, pc, ph // 2, ph // 2)).astype(np.float32))
+    pool_dx = capi.empty((pn, pc, ph, ph))
+    i64, f32, i32 = C.c_int64, C.c_float, C.c_int
+    sh2, sh1 = capi.i64([rows, cols]), capi.i64([cols])
+    cases = [
+        ("unary_backward tanh", 12.0 * n,
+         lambda: capi.call("unary_backward", i32(UNARY["tanh"]), X.ptr, G.ptr, D1.ptr, i64(n), f32(0), f32(0))),
+        ("unary exp (forward)", 8.0 * n, lambda: capi.call("unary", i32(UNARY["exp"]), X.ptr, D1.ptr, i64(n), f32(0), f32(0))),
+        ("binary_backward mul [R,C]*[C] (fused column sum)", 4.0 * (3 * n + 2 * cols),
+         lambda: capi.call("binary_backward", i32(BINARY["mul"]), X.ptr, sh2, i32(2), bvec.ptr, sh1, i32(1), G.ptr, D1.ptr, dcol.ptr)),
+        ("binary_backward mul same shape", 20.0 * n,
+         lambda: capi.call("binary_backward", i32(BINARY["mul"]), X.ptr, sh2, i32(2), A.ptr, sh2, i32(2), G.ptr, D1.ptr, D2.ptr)),
+        ("reduce sum along rows' axis 1", 4.0 * (n + rows),
+         lambda: capi.call("reduce", i32(REDUCE["sum"]), X.ptr, i64(rows), i64(cols), i64(1), drow.ptr)),
+        ("reduce sum along axis 0", 4.0 * (n + cols),
+         lambda: capi.call("reduce", i32(REDUCE["sum"]), X.ptr, i64(1), i64(rows), i64(cols), dcol.ptr)),
+        ("logsumexp axis 1 (forward)", 4.0 * (n + rows),
+         lambda: capi.call("reduce", i32(REDUCE["logsumexp"]), X.ptr, i64(rows), i64(cols), i64(1), drow.ptr)),
+        ("logsumexp backward", 4.0 * (2 * n + rows),
+         lambda: capi.call("reduce_backward", i32(REDUCE["logsumexp"]), X.ptr, grow.ptr, i64(rows), i64(cols), i64(1), D1.ptr)),
+        ("log_softmax backward", 12.0 * n,
+         lambda: capi.call("log_softmax_backward", X.ptr, G.ptr, i64(rows), i64(cols), i64(1), D1.ptr)),
+        ("max_pool2d backward 2x2 [256,32,28,28]", 4.0 * (2 * pool_g.size + pool_dx.size),
+         lambda: capi.call("max_pool2d_backward", pool_g.ptr, pool_idx.ptr, i64(pn), i64(pc), i64(ph), i64(ph), i32(2), i32(2), i32(2),
+                           i32(2), i32(0), i32(0), pool_dx.ptr)),
+        ("adam step, 16.8 M parameters", 28.0 * n,
+         lambda: capi.call("adam_step", A.ptr, G.ptr, m.ptr, v.ptr, i64(n), f32(1e-3), f32(0.9), f32(0.999), f32(1e-8), i64(1))),
+    ]
+    flush = capi.empty((64 * 1024 * 1024,))
+    flush_sum = capi.empty((1,))
+    ms = C.c_float(0)
+    out = []
+    for name, nbytes, call in cases:
+        for _ in range(3):
+            call()
+        ts = []
+        for _ in range(10):
+            # L2 flush: write 256 MB, then read it back so that the dirty lines are written out before the timed
+            # launch instead of during it
+            capi.call("fill", flush.ptr, C.c_float(1.0), C.c_int64(flush.size))
+            capi.call("reduce", i32(REDUCE["sum"]), flush.ptr, i64(1), i64(flush.size), i64(1), flush_sum.ptr)
+            capi.call("timer_start")
+            call()
+            capi.call("timer_stop", C.byref(ms))
+            ts.append(ms.value)
+        t = float(np.mean(ts)) * 1e-3
+        gbs = nbytes / t / 1e9
+        out.append({"kernel": name, "ms": t * 1e3, "algorithmic_MB": nbytes / 1e6, "GB/s": gbs, "frac_of_measured_hbm": gbs / pk["hbm"],
+                    "frac_of_8TBs": gbs / 8000.0})
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -181,6 +252,9 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernels-size", type=int, default=4096, help="rows = cols of the matrices of --kernels")
+    ap.add_argument("--kernels", action="store_true",
+                    help="print the bandwidth table of the HBM-bound kernels (one GPU) instead of the training-step line")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -194,6 +268,15 @@ def main():
     import rusttensor_b200 as rt
     from helpers import workload_data
 
+    if args.kernels:
+        if rank == 0:
+            rt.init(local_rank)
+            pk = peaks()
+            table = kernel_bandwidth_table(rt.CApi(ctx=rt.context_handle()), pk, args.kernels_size, args.kernels_size)
+            print(json.dumps({"kernel_bandwidth": table, "hbm_peak_GBs": pk["hbm"], "peak_source": pk["source"],
+                              "l2": "256 MB fill, then a read of the same 256 MB, before every timed launch",
+                              "rows": args.kernels_size, "cols": args.kernels_size}))
+        return
     config, dims, per_gpu, desc = WORKLOADS[args.workload]
     dist = None
     nccl_id = None

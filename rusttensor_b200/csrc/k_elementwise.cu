@@ -290,10 +290,7 @@ __global__ void __launch_bounds__(kColTile / 4 * kRowLanes) binary_bwd_rowvec(
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   if (c4 < cols4) {
     float4 v = __ldg(reinterpret_cast<const float4*>(vec) + c4);
-    for (int64_t r = r0 + threadIdx.y; r < r1; r += kRowLanes) {
-      int64_t idx = r * cols4 + c4;
-      float4 f = __ldg(reinterpret_cast<const float4*>(full) + idx);
-      float4 gg = __ldg(reinterpret_cast<const float4*>(g) + idx);
+    auto process = [&](int64_t idx, const float4& f, const float4& gg) {
       float4 df, dv;
       if (!SWAP) {
         df.x = Binary<OP>::da(f.x, v.x, gg.x); df.y = Binary<OP>::da(f.y, v.y, gg.y);
@@ -308,6 +305,23 @@ __global__ void __launch_bounds__(kColTile / 4 * kRowLanes) binary_bwd_rowvec(
       }
       if (d_full) reinterpret_cast<float4*>(d_full)[idx] = df;
       acc.x += dv.x; acc.y += dv.y; acc.z += dv.z; acc.w += dv.w;
+    };
+    int64_t r = r0 + threadIdx.y;
+    // four rows per trip: eight independent 128-bit loads in flight per thread
+    for (; r + 3 * kRowLanes < r1; r += 4 * kRowLanes) {
+      float4 f[4], gg[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t idx = (r + u * kRowLanes) * cols4 + c4;
+        f[u] = __ldg(reinterpret_cast<const float4*>(full) + idx);
+        gg[u] = __ldg(reinterpret_cast<const float4*>(g) + idx);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) process((r + u * kRowLanes) * cols4 + c4, f[u], gg[u]);
+    }
+    for (; r < r1; r += kRowLanes) {
+      const int64_t idx = r * cols4 + c4;
+      process(idx, __ldg(reinterpret_cast<const float4*>(full) + idx), __ldg(reinterpret_cast<const float4*>(g) + idx));
     }
   }
   if (partial == nullptr) return;

@@ -139,15 +139,85 @@ __global__ void __launch_bounds__(kThreads) row_reduce_block(const float* __rest
   }
 }
 
+// ---- inner == 1, long rows with 128-bit loads: a warp per row, eight independent loads in flight per lane, no
+// block-level synchronisation.
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) row_reduce_warp_vec(const float* __restrict__ x, float* __restrict__ out,
+                                                                 int64_t rows, int len, float scale) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const int n4 = len >> 2;
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    const float4* p = reinterpret_cast<const float4*>(x + r * len);
+    float acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = Red<KIND>::init();
+    int k = lane;
+    for (; k + 7 * 32 < n4; k += 8 * 32) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldg(p + k + u * 32);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        acc[0] = Red<KIND>::op(acc[0], v[u].x);
+        acc[1] = Red<KIND>::op(acc[1], v[u].y);
+        acc[2] = Red<KIND>::op(acc[2], v[u].z);
+        acc[3] = Red<KIND>::op(acc[3], v[u].w);
+      }
+    }
+    for (; k < n4; k += 32) {
+      const float4 v = __ldg(p + k);
+      acc[0] = Red<KIND>::op(acc[0], v.x);
+      acc[1] = Red<KIND>::op(acc[1], v.y);
+      acc[2] = Red<KIND>::op(acc[2], v.z);
+      acc[3] = Red<KIND>::op(acc[3], v.w);
+    }
+    float a = Red<KIND>::op(Red<KIND>::op(acc[0], acc[1]), Red<KIND>::op(acc[2], acc[3]));
+    a = warp_reduce<KIND>(a);
+    if (lane == 0) out[r] = a * scale;
+  }
+}
+
+// ---- inner == 1, rows of 1024 < len <= 8192 elements: a block per row, the row in registers -------
+// Every thread issues all of its 128-bit loads before it uses any of them, so one block keeps
+// len*4 bytes in flight; eight resident blocks per SM are enough to cover the HBM latency.
+template <int VPT>
+__device__ __forceinline__ void load_row_vec(const float* __restrict__ p, int n4, float4 (&v)[VPT], float fill) {
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int k = i * kThreads + threadIdx.x;
+    v[i] = k < n4 ? __ldg(reinterpret_cast<const float4*>(p) + k) : make_float4(fill, fill, fill, fill);
+  }
+}
+
+template <int KIND, int VPT>
+__global__ void __launch_bounds__(kThreads) row_reduce_regs(const float* __restrict__ x, float* __restrict__ out,
+                                                             int64_t rows, int len, float scale) {
+  __shared__ float smem[kThreads / 32];
+  const int n4 = len >> 2;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    float4 v[VPT];
+    load_row_vec<VPT>(x + r * len, n4, v, Red<KIND>::init());
+    float acc = Red<KIND>::init();
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      acc = Red<KIND>::op(acc, Red<KIND>::op(Red<KIND>::op(v[i].x, v[i].y), Red<KIND>::op(v[i].z, v[i].w)));
+    acc = block_reduce<KIND>(acc, smem);
+    if (threadIdx.x == 0) out[r] = acc * scale;
+  }
+}
+
 // ---- inner > 1: column reduction -----------------------------------------------------
 // grid: (inner tiles, k-splits, outer); block: (32, 8).  VEC: 4 columns per thread.
-template <int KIND, bool VEC>
+template <int KIND, bool VEC, int TX = 32>
 __global__ void __launch_bounds__(256) col_reduce(const float* __restrict__ x, float* __restrict__ out, int64_t len,
                                                    int64_t inner, int64_t splits, int64_t rows_per_split, float scale) {
   constexpr int W = VEC ? 4 : 1;
-  __shared__ float red[8][32 * W + 1];
+  constexpr int TY = 256 / TX;  // row lanes; a block reads TX*W contiguous columns of TY rows at a time
+  __shared__ float red[TY][TX * W + 1];
   int64_t o = blockIdx.z;
-  int64_t i0 = ((int64_t)blockIdx.x * 32 + threadIdx.x) * W;
+  int64_t i0 = ((int64_t)blockIdx.x * TX + threadIdx.x) * W;
   int64_t k0 = (int64_t)blockIdx.y * rows_per_split, k1 = k0 + rows_per_split;
   if (k1 > len) k1 = len;
   float acc[W];
@@ -155,7 +225,23 @@ __global__ void __launch_bounds__(256) col_reduce(const float* __restrict__ x, f
   for (int j = 0; j < W; ++j) acc[j] = Red<KIND>::init();
   if (i0 < inner) {
     const float* base = x + o * len * inner + i0;
-    for (int64_t k = k0 + threadIdx.y; k < k1; k += 8) {
+    int64_t k = k0 + threadIdx.y;
+    if (VEC) {
+      // four independent 128-bit loads in flight per thread
+      for (; k + 3 * TY < k1; k += 4 * TY) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = __ldg(reinterpret_cast<const float4*>(base + (k + TY * u) * inner));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          acc[0] = Red<KIND>::op(acc[0], v[u].x);
+          acc[1 % W] = Red<KIND>::op(acc[1 % W], v[u].y);
+          acc[2 % W] = Red<KIND>::op(acc[2 % W], v[u].z);
+          acc[3 % W] = Red<KIND>::op(acc[3 % W], v[u].w);
+        }
+      }
+    }
+    for (; k < k1; k += TY) {
       if (VEC) {
         float4 v = __ldg(reinterpret_cast<const float4*>(base + k * inner));
         acc[0] = Red<KIND>::op(acc[0], v.x);
@@ -175,7 +261,7 @@ __global__ void __launch_bounds__(256) col_reduce(const float* __restrict__ x, f
     for (int j = 0; j < W; ++j) {
       float s = red[0][threadIdx.x * W + j];
 #pragma unroll
-      for (int y = 1; y < 8; ++y) s = Red<KIND>::op(s, red[y][threadIdx.x * W + j]);
+      for (int y = 1; y < TY; ++y) s = Red<KIND>::op(s, red[y][threadIdx.x * W + j]);
       // out layout [outer, splits, inner]
       out[(o * splits + blockIdx.y) * inner + i0 + j] = s * scale;
     }
@@ -200,6 +286,20 @@ rt_status reduce_float(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, 
     if (len <= 1024) {
       int grid = rt_grid_for(ctx, rows, kThreads / 32);
       row_reduce_warp<KIND><<<grid, kThreads, 0, ctx->stream>>>(x, out, rows, len, scale);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
+    if (len <= 65536 && (len & 3) == 0 && rt_aligned16(x) && rows >= (int64_t)ctx->sm_count * 16) {
+      // plenty of rows: a warp per row keeps the most loads in flight
+      row_reduce_warp_vec<KIND><<<rt_grid_for(ctx, rows, kThreads / 32), kThreads, 0, ctx->stream>>>(x, out, rows, (int)len, scale);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
+    if (len <= 8192 && (len & 3) == 0 && rt_aligned16(x) && rows >= 64) {
+      const int grid = (int)(rows < (1 << 20) ? rows : (1 << 20));  // a block per row: rows in different phases overlap
+      if (len <= 2048) row_reduce_regs<KIND, 2><<<grid, kThreads, 0, ctx->stream>>>(x, out, rows, (int)len, scale);
+      else if (len <= 4096) row_reduce_regs<KIND, 4><<<grid, kThreads, 0, ctx->stream>>>(x, out, rows, (int)len, scale);
+      else row_reduce_regs<KIND, 8><<<grid, kThreads, 0, ctx->stream>>>(x, out, rows, (int)len, scale);
       RT_LAUNCHED(ctx);
       return RT_OK;
     }
@@ -228,11 +328,15 @@ rt_status reduce_float(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, 
   }
   // inner > 1
   bool vec = (inner % 4 == 0) && rt_aligned16(x);
-  int64_t tiles = (inner + (vec ? 128 : 32) - 1) / (vec ? 128 : 32);
+  // wide rows: 2 KB contiguous per row and block (better DRAM page locality than 512 B)
+  const bool wide = vec && inner >= 2048;
+  const int tile_cols = wide ? 512 : (vec ? 128 : 32);
+  int64_t tiles = (inner + tile_cols - 1) / tile_cols;
   int64_t splits = 1;
   if (tiles * outer < target_blocks) {
     splits = (target_blocks + tiles * outer - 1) / (tiles * outer);
-    int64_t max_splits = (len + 63) / 64;  // at least 64 rows per split
+    const int min_rows = 64;  // rows per split
+    int64_t max_splits = (len + min_rows - 1) / min_rows;
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
     if (splits > 65535) splits = 65535;
@@ -257,7 +361,8 @@ rt_status reduce_float(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, 
     dst = part.as<float>();
   }
   float sc = splits > 1 ? 1.f : scale;
-  if (vec) col_reduce<KIND, true><<<grid, block, 0, ctx->stream>>>(x, dst, len, inner, splits, rps, sc);
+  if (wide) col_reduce<KIND, true, 128><<<grid, dim3(128, 2), 0, ctx->stream>>>(x, dst, len, inner, splits, rps, sc);
+  else if (vec) col_reduce<KIND, true><<<grid, block, 0, ctx->stream>>>(x, dst, len, inner, splits, rps, sc);
   else col_reduce<KIND, false><<<grid, block, 0, ctx->stream>>>(x, dst, len, inner, splits, rps, sc);
   RT_LAUNCHED(ctx);
   if (splits > 1) return reduce_float<KIND>(ctx, dst, outer, splits, inner, out, scale);
@@ -365,6 +470,63 @@ __global__ void __launch_bounds__(kThreads) slice_softmax_kernel(const float* __
   }
 }
 
+// Rows of 1024 < len <= 8192 elements (len % 4 == 0, 16-byte aligned): a block per row with the row
+// (and for log_softmax backward the gradient row) held in registers; global memory is read once and
+// written once.  Same formulas as row_softmax_kernel.
+template <int MODE, int VPT>
+__global__ void __launch_bounds__(kThreads) row_softmax_regs(const float* __restrict__ x, const float* __restrict__ g,
+                                                              float* __restrict__ out, int64_t rows, int len) {
+  __shared__ float smem[kThreads / 32];
+  const int n4 = len >> 2;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    float4 v[VPT], gv[VPT];  // gv is used by the log_softmax backward only
+    load_row_vec<VPT>(x + r * len, n4, v, -INFINITY);
+    if (MODE == ROW_LSM_BWD) load_row_vec<VPT>(g + r * len, n4, gv, 0.f);
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    m = block_reduce<RT_RED_MAX>(m, smem);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)  // padding lanes hold -inf: exp(-inf - m) = 0
+      s += (expf(v[i].x - m) + expf(v[i].y - m)) + (expf(v[i].z - m) + expf(v[i].w - m));
+    s = block_reduce<RT_RED_SUM>(s, smem);
+    if (MODE == ROW_LSE_FWD) {
+      if (threadIdx.x == 0) out[r] = m + logf(s);
+      continue;
+    }
+    float4* o = reinterpret_cast<float4*>(out + r * len);
+    if (MODE == ROW_LSE_BWD) {
+      const float lse = m + logf(s), gr = __ldg(g + r);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int k = i * kThreads + threadIdx.x;
+        if (k < n4) o[k] = make_float4(gr * expf(v[i].x - lse), gr * expf(v[i].y - lse), gr * expf(v[i].z - lse), gr * expf(v[i].w - lse));
+      }
+    } else if (MODE == ROW_LSM_FWD) {
+      const float ls = logf(s);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int k = i * kThreads + threadIdx.x;
+        if (k < n4) o[k] = make_float4((v[i].x - m) - ls, (v[i].y - m) - ls, (v[i].z - m) - ls, (v[i].w - m) - ls);
+      }
+    } else {  // ROW_LSM_BWD: dx = g - exp(y) * sum(g)
+      float sg = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) sg += (gv[i].x + gv[i].y) + (gv[i].z + gv[i].w);
+      sg = block_reduce<RT_RED_SUM>(sg, smem);
+      const float ls = logf(s);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int k = i * kThreads + threadIdx.x;
+        if (k < n4)
+          o[k] = make_float4(gv[i].x - expf((v[i].x - m) - ls) * sg, gv[i].y - expf((v[i].y - m) - ls) * sg,
+                             gv[i].z - expf((v[i].z - m) - ls) * sg, gv[i].w - expf((v[i].w - m) - ls) * sg);
+      }
+    }
+  }
+}
+
 template <int MODE>
 rt_status launch_softmax_family(rt_ctx* ctx, const float* x, const float* g, float* out, int64_t outer, int64_t len,
                                 int64_t inner) {
@@ -373,6 +535,12 @@ rt_status launch_softmax_family(rt_ctx* ctx, const float* x, const float* g, flo
     if (len <= 1024) {
       int grid = rt_grid_for(ctx, outer, kThreads / 32);
       row_softmax_kernel<MODE, 32><<<grid, kThreads, 0, ctx->stream>>>(x, g, out, outer, len);
+    } else if (len <= 8192 && (len & 3) == 0 && rt_aligned16(x) && (MODE == ROW_LSE_FWD || rt_aligned16(out)) &&
+               (MODE != ROW_LSM_BWD || rt_aligned16(g))) {
+      const int grid = (int)(outer < (1 << 20) ? outer : (1 << 20));  // a block per row: rows in different phases overlap
+      if (len <= 2048) row_softmax_regs<MODE, 2><<<grid, kThreads, 0, ctx->stream>>>(x, g, out, outer, (int)len);
+      else if (len <= 4096) row_softmax_regs<MODE, 4><<<grid, kThreads, 0, ctx->stream>>>(x, g, out, outer, (int)len);
+      else row_softmax_regs<MODE, 8><<<grid, kThreads, 0, ctx->stream>>>(x, g, out, outer, (int)len);
     } else {
       int grid = rt_grid_for(ctx, outer, 1);
       row_softmax_kernel<MODE, kThreads><<<grid, kThreads, 0, ctx->stream>>>(x, g, out, outer, len);
