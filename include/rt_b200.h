@@ -76,6 +76,14 @@ rt_status rt_upload_create(rt_ctx* ctx, size_t bytes, rt_upload** out);
 rt_status rt_upload_destroy(rt_ctx* ctx, rt_upload* up);
 rt_status rt_upload_host_buffer(rt_ctx* ctx, rt_upload* up, void** pinned);
 rt_status rt_upload_submit(rt_ctx* ctx, rt_upload* up, void* dst);
+/* A side stream for work that may overlap what follows on the context's stream (new; used to all-reduce the
+ * gradients that are ready while the rest of the backward pass runs).  Between begin and end every rt_* call of this
+ * context is enqueued on the side stream, which first waits for everything queued before `begin`; `join` makes the
+ * context's stream wait for the side work.  Calls inside the section must not allocate (rt_malloc fails there);
+ * sections do not nest; a section opened during graph capture must be joined before the capture ends. */
+rt_status rt_side_stream_begin(rt_ctx* ctx);
+rt_status rt_side_stream_end(rt_ctx* ctx);
+rt_status rt_side_stream_join(rt_ctx* ctx);
 /* Events on the context's stream: record after queued work, wait on the host later. */
 typedef struct rt_event rt_event;
 rt_status rt_event_create(rt_ctx* ctx, rt_event** out);

@@ -239,6 +239,14 @@ class Tensor {
   }
 
   // src/tensor.rs:1150-1220
+  // Optional observer (not in the reference): called by backward() when the walk reaches a leaf that requires a
+  // gradient, i.e. when that gradient is final.  The data-parallel trainer uses it to start exchanging the gradients
+  // that are ready while the rest of the backward pass is still being enqueued.
+  static std::function<void(const Tensor&)>& leaf_ready_hook() {
+    static thread_local std::function<void(const Tensor&)> hook;
+    return hook;
+  }
+
   void backward() const {
     if (!requires_grad()) return;
     if (size() == 1) {
@@ -253,7 +261,12 @@ class Tensor {
       const Tensor<B>& node = *it;
       if (!visited.insert(node.id()).second) continue;
       std::shared_ptr<Op<B>> op = node.inner->op;
-      if (!op || !node.inner->grad) continue;
+      if (!op) {
+        // every consumer of this leaf has been processed: its gradient is final
+        if (node.inner->grad && node.requires_grad() && leaf_ready_hook()) leaf_ready_hook()(node);
+        continue;
+      }
+      if (!node.inner->grad) continue;
       Storage out_grad = *node.inner->grad;  // value copy, as the reference clones
       std::vector<Storage> grads = op->backward_fn(*op, out_grad);
       if (grads.size() != op->inputs.size())

@@ -53,7 +53,14 @@ rt_status rt_ctx_create(int device, rt_ctx** out) {
 rt_status rt_ctx_destroy(rt_ctx* ctx) {
   RT_CHECK_CTX(ctx);
   cudaSetDevice(ctx->device);
+  if (ctx->on_side) ctx->stream = ctx->main_stream;
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->side_stream) {
+    cudaStreamSynchronize(ctx->side_stream);
+    cudaStreamDestroy(ctx->side_stream);
+    cudaEventDestroy(ctx->fork_ev);
+    cudaEventDestroy(ctx->join_ev);
+  }
   rt_dp_finalize(ctx);
   for (auto& kv : ctx->free_blocks) cudaFree(kv.second);
   for (auto& kv : ctx->capture_free) cudaFree(kv.second);
@@ -78,6 +85,7 @@ static size_t round_size(size_t bytes) {
 rt_status rt_malloc(rt_ctx* ctx, size_t bytes, void** out) {
   RT_CHECK_CTX(ctx);
   RT_CHECK_PTR(ctx, out);
+  if (ctx->on_side) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_malloc inside a side-stream section");
   size_t sz = round_size(bytes);
   if (ctx->capturing) {
     auto cit = ctx->capture_free.lower_bound(sz);
@@ -290,6 +298,42 @@ rt_status rt_upload_submit(rt_ctx* ctx, rt_upload* up, void* dst) {
   RT_CUDA(ctx, cudaEventRecord(up->consumed[k], ctx->stream));
   up->used[k] = true;
   up->next = k ^ 1;
+  return RT_OK;
+}
+
+// ---- side stream --------------------------------------------------------------------------------
+rt_status rt_side_stream_begin(rt_ctx* ctx) {
+  RT_CHECK_CTX(ctx);
+  if (ctx->on_side) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_side_stream_begin: a side section is already open");
+  if (ctx->side_pending) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_side_stream_begin: join the previous side section first");
+  if (!ctx->side_stream) {
+    RT_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
+    RT_CUDA(ctx, cudaEventCreateWithFlags(&ctx->fork_ev, cudaEventDisableTiming));
+    RT_CUDA(ctx, cudaEventCreateWithFlags(&ctx->join_ev, cudaEventDisableTiming));
+  }
+  RT_CUDA(ctx, cudaEventRecord(ctx->fork_ev, ctx->stream));
+  RT_CUDA(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->fork_ev, 0));
+  ctx->main_stream = ctx->stream;
+  ctx->stream = ctx->side_stream;
+  ctx->on_side = true;
+  return RT_OK;
+}
+rt_status rt_side_stream_end(rt_ctx* ctx) {
+  RT_CHECK_CTX(ctx);
+  if (!ctx->on_side) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_side_stream_end: no side section is open");
+  cudaError_t e = cudaEventRecord(ctx->join_ev, ctx->side_stream);
+  ctx->stream = ctx->main_stream;
+  ctx->on_side = false;
+  ctx->side_pending = true;
+  RT_CUDA(ctx, e);
+  return RT_OK;
+}
+rt_status rt_side_stream_join(rt_ctx* ctx) {
+  RT_CHECK_CTX(ctx);
+  if (ctx->on_side) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_side_stream_join: end the side section first");
+  if (!ctx->side_pending) return RT_OK;
+  ctx->side_pending = false;
+  RT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->join_ev, 0));
   return RT_OK;
 }
 

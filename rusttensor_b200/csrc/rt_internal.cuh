@@ -33,6 +33,10 @@ struct rt_ctx {
   bool capturing = false;
   std::multimap<size_t, void*> capture_free;  // released during capture: reusable only inside it
   cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+  // side stream (rt_side_stream_*): `stream` points at it between begin and end
+  cudaStream_t side_stream = nullptr, main_stream = nullptr;
+  cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
+  bool on_side = false, side_pending = false;
   // Error word written by kernels whose bounded waits expire (0 = none); see rt_device_status.
   int* device_status = nullptr;
   // Route large contractions to the tcgen05 3xTF32 kernels (k_gemm_tc.cu).
