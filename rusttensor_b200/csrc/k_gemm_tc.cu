@@ -429,6 +429,23 @@ struct ImageOut {  // out[b, n, p] for row m = (b,p), optional per-channel bias
       if (n0 + j < C) q[(int64_t)j * HW] = bias ? v[j] + __ldg(bias + n0 + j) : v[j];
   }
 };
+struct PhaseOut {  // out[b, n, j*sy + oy, i*sx + ox] for row m = (b, j, i) of one stride phase, optional per-channel bias
+  float* out;
+  const float* bias;
+  int C, Hfull, Wfull, sy, sx, oy, ox, M;
+  FastDiv d_HjWj, d_Wj;
+  __device__ __forceinline__ void store32(int m, int n0, const float (&v)[32], int) const {
+    if (m >= M) return;
+    uint32_t b, r, j, i;
+    d_HjWj.divmod(m, b, r);
+    d_Wj.divmod(r, j, i);
+    const int64_t hw = (int64_t)Hfull * Wfull;
+    float* q = out + ((int64_t)b * C + n0) * hw + (int64_t)((int)j * sy + oy) * Wfull + (int)i * sx + ox;
+#pragma unroll
+    for (int jn = 0; jn < 32; ++jn)
+      if (n0 + jn < C) q[(int64_t)jn * hw] = bias ? v[jn] + __ldg(bias + n0 + jn) : v[jn];
+  }
+};
 struct TransposedOut {  // c[z * split_stride + n * ld + m]: the tile is written transposed
   float* c;
   int64_t ld, split_stride;
@@ -880,6 +897,36 @@ rt_status rt_conv_gather_tc_internal(rt_ctx* ctx, const float* y, const float* w
     TapWeights lb = tap_weights(w, cm, g.kh, g.kw, g.kh * g.kw, cm * g.kh * g.kw, -g.kw, -1, g.kh * g.kw - 1);
     const int Kp = g.Cy * g.kh * la.kwq * 4;
     return dispatch_bn(ctx, la, lb, epi, (int)M, (int)N, Kp, 1, (Kp + BK - 1) / BK * BK);
+  }
+  if ((g.sh > 1 || g.sw > 1) && g.kw <= 32 * g.sw) {
+    // Strided gather (transposed-convolution forward, input gradient of a strided convolution): the outputs of one
+    // stride phase (iy % sh, ix % sw) only meet the kernel taps ky = ky0 + sh*a, kx = kx0 + sw*b, and with those taps
+    // the phase is a unit-stride convolution of y that writes every sh-th / sw-th output.  sh*sw launches without the
+    // structural zeros replace one launch whose reduction is sh*sw times longer.
+    bool ok = true;
+    for (int ry = 0; ry < g.sh && ok; ++ry) ok = (ry + g.ph) % g.sh < g.kh || (g.Hx - ry + g.sh - 1) / g.sh <= 0;
+    for (int rx = 0; rx < g.sw && ok; ++rx) ok = (rx + g.pw) % g.sw < g.kw || (g.Wx - rx + g.sw - 1) / g.sw <= 0;
+    if (ok) {  // every non-empty phase has at least one tap (otherwise its outputs are the bias alone: generic path)
+      for (int ry = 0; ry < g.sh; ++ry)
+        for (int rx = 0; rx < g.sw; ++rx) {
+          const int Hj = (g.Hx - ry + g.sh - 1) / g.sh, Wj = (g.Wx - rx + g.sw - 1) / g.sw;
+          if (Hj <= 0 || Wj <= 0) continue;
+          const int ky0 = (ry + g.ph) % g.sh, kx0 = (rx + g.pw) % g.sw;
+          const int nay = (g.kh - ky0 + g.sh - 1) / g.sh, nax = (g.kw - kx0 + g.sw - 1) / g.sw;
+          const int pt = (nay - 1) - (ry + g.ph - ky0) / g.sh, pl = (nax - 1) - (rx + g.pw - kx0) / g.sw;
+          const int64_t Mp = (int64_t)g.Nb * Hj * Wj;
+          PixelTapRows la = pixel_rows(y, g.Cy, g.Hy, g.Wy, Hj, Wj, nay, nax, 1, 1, pt, pl, (int)Mp);
+          TapWeights lb = tap_weights(w, cm, nay, nax, g.kh * g.kw, cm * g.kh * g.kw, -g.sh * g.kw, -g.sw,
+                                      (ky0 + g.sh * (nay - 1)) * g.kw + kx0 + g.sw * (nax - 1));
+          PhaseOut pe{out, bias, cm, g.Hx, g.Wx, g.sh, g.sw, ry, rx, (int)Mp, {}, {}};
+          pe.d_HjWj.init(Hj * Wj);
+          pe.d_Wj.init(Wj);
+          const int Kp = g.Cy * nay * la.kwq * 4;
+          rt_status st = dispatch_bn(ctx, la, lb, pe, (int)Mp, (int)N, Kp, 1, (Kp + BK - 1) / BK * BK);
+          if (st != RT_OK) return st;
+        }
+      return RT_OK;
+    }
   }
   GatherRows la{y, g, (int)M};
   WeightSecondRows lb{w, g, cm};

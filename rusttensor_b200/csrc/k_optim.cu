@@ -18,7 +18,16 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kMaxTensors = 48;
-constexpr int kChunk = kThreads * 16;  // elements per block
+constexpr int kChunkLarge = kThreads * 16;  // elements per block for large models
+constexpr int kChunkSmall = kThreads * 4;   // ... and when the whole model would not fill the machine otherwise
+
+// Elements per block: one 128-bit access per thread while the model is small (every load of the step in flight at
+// once: a 0.4 M-parameter model is latency-bound, not bandwidth-bound), sixteen elements per thread beyond that.
+inline int chunk_for(rt_ctx* ctx, const int64_t* sizes, int n_tensors) {
+  int64_t total = 0;
+  for (int i = 0; i < n_tensors; ++i) total += sizes[i] > 0 ? sizes[i] : 0;
+  return total <= (int64_t)ctx->sm_count * 8 * kChunkLarge ? kChunkSmall : kChunkLarge;
+}
 
 struct OptArgs {
   float* p[kMaxTensors];
@@ -28,6 +37,7 @@ struct OptArgs {
   int64_t n[kMaxTensors];
   int block_start[kMaxTensors + 1];  // first block of each tensor
   int count;
+  int chunk;  // elements per block
   float lr, beta1, beta2, eps, momentum, bc1, bc2, grad_scale, clip_lo, clip_hi;
   int clip;
 };
@@ -57,9 +67,9 @@ __global__ void __launch_bounds__(kThreads) optimizer_kernel(const __grid_consta
   // locate the tensor this block works on
   int ti = 0;
   while (ti + 1 < a.count && (int)blockIdx.x >= a.block_start[ti + 1]) ++ti;
-  int64_t base = (int64_t)(blockIdx.x - a.block_start[ti]) * kChunk;
+  int64_t base = (int64_t)(blockIdx.x - a.block_start[ti]) * a.chunk;
   int64_t n = a.n[ti];
-  int64_t end = base + kChunk < n ? base + kChunk : n;
+  int64_t end = base + a.chunk < n ? base + a.chunk : n;
   float* p = a.p[ti];
   const float* g = a.g[ti];
   float* s1 = a.s1[ti];
@@ -98,6 +108,7 @@ struct PackArgs {
   int64_t dst_off[kMaxTensors];
   int block_start[kMaxTensors + 1];
   int count;
+  int chunk;  // elements per block
   float clip_lo, clip_hi;
   int clip;
 };
@@ -105,11 +116,23 @@ struct PackArgs {
 __global__ void __launch_bounds__(kThreads) pack_kernel(const __grid_constant__ PackArgs a, float* __restrict__ flat) {
   int ti = 0;
   while (ti + 1 < a.count && (int)blockIdx.x >= a.block_start[ti + 1]) ++ti;
-  int64_t base = (int64_t)(blockIdx.x - a.block_start[ti]) * kChunk;
+  int64_t base = (int64_t)(blockIdx.x - a.block_start[ti]) * a.chunk;
   int64_t n = a.n[ti];
-  int64_t end = base + kChunk < n ? base + kChunk : n;
+  int64_t end = base + a.chunk < n ? base + a.chunk : n;
   const float* s = a.src[ti];
   float* d = flat + a.dst_off[ti];
+  if (rt_aligned16(s) && rt_aligned16(d)) {  // chunk and dst_off are multiples of 4 elements
+    int64_t end4 = base + ((end - base) & ~int64_t(3));
+    for (int64_t i = base + threadIdx.x * 4; i < end4; i += kThreads * 4) {
+      float4 v = __ldg(reinterpret_cast<const float4*>(s + i));
+      if (a.clip) {
+        v.x = fminf(fmaxf(v.x, a.clip_lo), a.clip_hi); v.y = fminf(fmaxf(v.y, a.clip_lo), a.clip_hi);
+        v.z = fminf(fmaxf(v.z, a.clip_lo), a.clip_hi); v.w = fminf(fmaxf(v.w, a.clip_lo), a.clip_hi);
+      }
+      *reinterpret_cast<float4*>(d + i) = v;
+    }
+    base = end4;
+  }
   for (int64_t i = base + threadIdx.x; i < end; i += kThreads) {
     float v = s[i];
     if (a.clip) v = fminf(fmaxf(v, a.clip_lo), a.clip_hi);
@@ -135,9 +158,11 @@ rt_status launch_multi(rt_ctx* ctx, int kind, int n_tensors, float* const* param
                        float eps, float momentum, int64_t t, float grad_scale, int clip, float clip_lo, float clip_hi) {
   if (kind < 0 || kind > 3) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "optimizer kind %d", kind);
   if (kind == 1 && t <= 0) RT_FAIL(ctx, RT_ERR_INTERNAL, "Adam step called with t=0");
+  const int chunk = chunk_for(ctx, sizes, n_tensors);
   for (int first = 0; first < n_tensors; first += kMaxTensors) {
     OptArgs a;
     a.count = 0;
+    a.chunk = chunk;
     int blocks = 0;
     for (int i = first; i < n_tensors && a.count < kMaxTensors; ++i) {
       if (sizes[i] <= 0) continue;
@@ -150,7 +175,7 @@ rt_status launch_multi(rt_ctx* ctx, int kind, int n_tensors, float* const* param
       a.s2[c] = kind == 1 ? s2[i] : nullptr;
       a.n[c] = sizes[i];
       a.block_start[c] = blocks;
-      blocks += (int)((sizes[i] + kChunk - 1) / kChunk);
+      blocks += (int)((sizes[i] + chunk - 1) / chunk);
     }
     if (a.count == 0) continue;
     a.block_start[a.count] = blocks;
@@ -219,9 +244,11 @@ rt_status rt_pack_flat(rt_ctx* ctx, int n_tensors, const float* const* srcs, con
   RT_CHECK_PTR(ctx, sizes);
   RT_CHECK_PTR(ctx, flat);
   int64_t off = 0;
+  const int chunk = chunk_for(ctx, sizes, n_tensors);
   for (int first = 0; first < n_tensors; first += kMaxTensors) {
     PackArgs a;
     a.count = 0;
+    a.chunk = chunk;
     int blocks = 0;
     for (int i = first; i < n_tensors && i < first + kMaxTensors; ++i) {
       int64_t padded = (sizes[i] + 3) & ~int64_t(3);  // every tensor starts on a 16-byte boundary
@@ -232,7 +259,7 @@ rt_status rt_pack_flat(rt_ctx* ctx, int n_tensors, const float* const* srcs, con
         a.n[c] = sizes[i];
         a.dst_off[c] = off;
         a.block_start[c] = blocks;
-        blocks += (int)((sizes[i] + kChunk - 1) / kChunk);
+        blocks += (int)((sizes[i] + chunk - 1) / chunk);
       }
       off += padded;
     }
