@@ -1,6 +1,6 @@
-"""Two-GPU data parallelism on real devices: two ranks, each on its own shard, with the overlapped NCCL all-reduce
-(ready gradients leave on a side stream during the backward pass) must end with the parameters one GPU reaches on the
-concatenated batch.  Skipped on machines with a single GPU."""
+"""Two-GPU data parallelism on real devices: two ranks, each on its own shard, with one NCCL all-reduce after the backward
+pass or with the overlapped exchange (ready gradients leave on a side stream during the backward pass), must end with the
+parameters one GPU reaches on the concatenated batch.  Skipped on machines with a single GPU."""
 import os
 import subprocess
 import sys
@@ -21,14 +21,15 @@ def _gpu_count():
     return torch.cuda.device_count()
 
 
+@pytest.mark.parametrize("overlap", ["0", "1"])
 @pytest.mark.parametrize("mode", ["graph", "eager"])
-def test_two_ranks_match_one_gpu_on_the_joint_batch(gpu_engine, tmp_path, mode):
+def test_two_ranks_match_one_gpu_on_the_joint_batch(gpu_engine, tmp_path, mode, overlap):
     if _gpu_count() < 2:
         pytest.skip("needs two GPUs")
     out = str(tmp_path / "dp2.npz")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", "29533", os.path.join(HERE, "dp_worker.py"), out, mode]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", RT_B200_DP_OVERLAP=overlap)
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     got = np.load(out)
