@@ -57,17 +57,6 @@ __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
   asm volatile(
@@ -109,11 +98,9 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo, uint
   d |= (uint64_t)1 << 46;
   return d;
 }
-// The three MMAs of one 3xTF32 K-step in a single asm block (one predicate set-up, no per-MMA
-// wrapper overhead): cross terms lo*hi and hi*lo into accumulator `d_cross`, hi*hi into `d_main`.
-// Descriptors are passed as (low word, high word); only the low word (start address) changes
-// from step to step.
-// Same, for a warp that runs the issue loop with all lanes (so that the operands stay warp-uniform):
+// The three MMAs of one 3xTF32 K-step in a single asm block: cross terms lo*hi and hi*lo into accumulator
+// `d_cross`, hi*hi into `d_main`.  Descriptors are passed as (low word, high word); only the low word (start address)
+// changes from step to step.  Called by every lane of a converged warp (so that the operands stay warp-uniform);
 // one elected lane issues.
 __device__ __forceinline__ void umma_tf32_step_elect(uint32_t d_cross, uint32_t d_main, uint32_t a_hi_lo32, uint32_t a_lo_lo32,
                                                      uint32_t a_hi32, uint32_t b_hi_lo32, uint32_t b_lo_lo32, uint32_t b_hi32,
@@ -162,26 +149,6 @@ __device__ __forceinline__ void umma_commit_elect(uint32_t bar) {
       "{\n\t.reg .pred pe;\n\t"
       "elect.sync _|pe, 0xffffffff;\n\t"
       "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void umma_tf32_step(uint32_t d_cross, uint32_t d_main, uint32_t a_hi_lo32, uint32_t a_lo_lo32,
-                                               uint32_t a_hi32, uint32_t b_hi_lo32, uint32_t b_lo_lo32, uint32_t b_hi32,
-                                               uint32_t idesc, uint32_t acc_cross, uint32_t acc_main) {
-  asm volatile(
-      "{\n\t.reg .pred pc, pm, pt;\n\t"
-      ".reg .b64 dah, dal, dbh, dbl;\n\t"
-      "setp.ne.b32 pc, %9, 0;\n\t"
-      "setp.ne.b32 pm, %10, 0;\n\t"
-      "setp.eq.b32 pt, 0, 0;\n\t"
-      "mov.b64 dah, {%2, %4};\n\t"
-      "mov.b64 dal, {%3, %4};\n\t"
-      "mov.b64 dbh, {%5, %7};\n\t"
-      "mov.b64 dbl, {%6, %7};\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], dal, dbh, %8, pc;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], dah, dbl, %8, pt;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%1], dah, dbh, %8, pm;\n\t}"
-      ::"r"(d_cross), "r"(d_main), "r"(a_hi_lo32), "r"(a_lo_lo32), "r"(a_hi32), "r"(b_hi_lo32), "r"(b_lo_lo32), "r"(b_hi32),
-        "r"(idesc), "r"(acc_cross), "r"(acc_main)
       : "memory");
 }
 // Low / high words of the shared-memory matrix descriptor of make_desc.

@@ -148,3 +148,57 @@ def test_argument_validation(capi):
     # empty tensors are no-ops
     capi.call("unary", C.c_int(0), None, None, C.c_int64(0), C.c_float(0), C.c_float(0))
     capi.call("reduce", C.c_int(0), None, C.c_int64(0), C.c_int64(5), C.c_int64(3), None)
+
+
+def test_upload_pipeline_and_events(capi):
+    """rt_upload_*: two pinned / staging buffer pairs alternate; data arrives in submit order; rt_event_* waits."""
+    n = 1 << 16
+    up = C.c_void_p()
+    capi.call("upload_create", C.c_size_t(4 * n), C.byref(up))
+    ev = C.c_void_p()
+    capi.call("event_create", C.byref(ev))
+    dst = capi.empty((n,))
+    acc = capi.to_device(np.zeros(n, np.float32))
+    sh = capi.i64([n])
+    seen = []
+    for step in range(5):
+        p = C.c_void_p()
+        capi.call("upload_host_buffer", up, C.byref(p))
+        seen.append(p.value)
+        host = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n,))
+        host[...] = np.arange(n, dtype=np.float32) + 1000.0 * step
+        capi.call("upload_submit", up, dst.ptr)
+        # consume on the context's stream: acc += dst
+        capi.call("binary", C.c_int(BINARY["add"]), acc.ptr, sh, C.c_int(1), dst.ptr, sh, C.c_int(1), acc.ptr)
+        capi.call("event_record", ev)
+    capi.call("event_synchronize", ev)
+    assert seen[0] != seen[1] and seen[0] == seen[2] == seen[4] and seen[1] == seen[3]
+    want = 5 * np.arange(n, dtype=np.float64) + 1000.0 * (0 + 1 + 2 + 3 + 4)
+    assert np.array_equal(acc.numpy(), want.astype(np.float32))
+    capi.call("event_destroy", ev)
+    capi.call("upload_destroy", up)
+
+
+def test_side_stream_sections(capi):
+    """Work issued between rt_side_stream_begin and _end runs after what was queued before and is waited for by _join;
+    nesting, joining inside a section and allocating inside a section are refused."""
+    n = 1 << 20
+    a = capi.to_device(np.full(n, 2.0, np.float32))
+    b, c = capi.empty((n,)), capi.empty((n,))
+    capi.call("unary", C.c_int(UNARY["square"]), a.ptr, b.ptr, C.c_int64(n), C.c_float(0), C.c_float(0))   # main: b = 4
+    capi.call("side_stream_begin")
+    capi.call("unary", C.c_int(UNARY["exp"]), b.ptr, c.ptr, C.c_int64(n), C.c_float(0), C.c_float(0))      # side: c = e^4
+    with pytest.raises(RtError):
+        capi.call("side_stream_begin")
+    with pytest.raises(RtError):
+        capi.call("side_stream_join")
+    with pytest.raises(RtError):
+        capi.empty((16,))
+    capi.call("side_stream_end")
+    capi.call("unary", C.c_int(UNARY["square"]), b.ptr, a.ptr, C.c_int64(n), C.c_float(0), C.c_float(0))   # main: a = 16
+    capi.call("side_stream_join")
+    capi.call("binary", C.c_int(BINARY["add"]), a.ptr, capi.i64([n]), C.c_int(1), c.ptr, capi.i64([n]), C.c_int(1), b.ptr)
+    assert_close(b.numpy(), np.full(n, 16.0 + np.exp(4.0)), 1e-6, "side stream result joined into the main stream")
+    capi.call("side_stream_join")  # nothing pending: a no-op
+    with pytest.raises(RtError):
+        capi.call("side_stream_end")
