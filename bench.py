@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the hot path: forward + backward + optimizer step, samples/s.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c1|c4|c5] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c1|c2|c4|c5] [--impl ours|reference]
 
 N > 1 is launched by `python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...`
 (one rank per GPU; RANK / LOCAL_RANK / WORLD_SIZE from the environment).  Rank 0 prints ONE JSON
@@ -34,6 +34,7 @@ WORKLOADS = {
     # name: (config id, dims, samples per step per GPU, description)
     "c3": (3, [256, 28, 32, 64, 128, 10], 256, "C3 CNN train step, 256x1x28x28 per GPU, Adam"),
     "c1": (1, [64, 784, 128, 10], 64, "C1 MLP train step, batch 64, Adam"),
+    "c2": (2, [4096, 4096], 4096, "C2 elementwise/reduction forward+backward on X [4096,4096], b [4096] (no optimizer; a sample is a row)"),
     "c4": (4, [128, 64, 56, 128], 128, "C4 conv/conv-transpose train step, 128x64x56x56, MomentumSGD"),
     "c5": (5, [65, 512, 128, 64], 64, "C5 char-LSTM train step, T=128, batch 64 per GPU, Adam"),
 }
