@@ -333,7 +333,10 @@ rt_status reduce_float(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, 
   const int tile_cols = wide ? 512 : (vec ? 128 : 32);
   int64_t tiles = (inner + tile_cols - 1) / tile_cols;
   int64_t splits = 1;
-  if (tiles * outer < target_blocks) {
+  // Short reductions (split-K partial sums, bias gradients of a batch) go in one launch: a second pass would cost
+  // more than the idle SMs of the first.
+  const bool short_reduction = len <= 256 || len * inner <= 65536;
+  if (!short_reduction && tiles * outer < target_blocks) {
     splits = (target_blocks + tiles * outer - 1) / (tiles * outer);
     const int min_rows = 64;  // rows per split
     int64_t max_splits = (len + min_rows - 1) / min_rows;
