@@ -299,6 +299,16 @@ def main():
 
     tr = rt.DataParallelTrainer(config, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
     capi = rt.CApi(ctx=rt.context_handle())
+    exchange = "one NCCL all-reduce of the flat gradients (N>1)"
+    if world > 1 and os.environ.get("RT_B200_DP_FUSED", "1") != "0":
+        # gradients are read from the peers' buffers inside the optimizer kernel; every rank must agree on the mode, so a
+        # set-up failure on any rank sends all of them back to the NCCL all-reduce
+        if tr.connect_peers(dist):
+            exchange = "gradient exchange over peer memory fused into the optimizer kernel (N>1)"
+        else:
+            print(f"[rank {rank}] peer-memory exchange unavailable ({getattr(tr, 'peer_error', 'another rank failed')}); using NCCL",
+                  file=sys.stderr)
+            tr = rt.DataParallelTrainer(config, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
     params, inputs = workload_data(config, dims, seed=0, rank=rank)  # same weights on every rank, different data
     for t, p in zip(tr.params, params):
         t.update_from_host(p)
@@ -369,6 +379,8 @@ def main():
 
     ms_e2e = timed(lambda: e2e_all(args.steps), 1)
     loss = losses[-1]
+    code = C.c_int(0)
+    capi.call("device_status", C.byref(code))  # raises if a bounded device-side wait (MMA pipeline, peer flags) expired
 
     if rank == 0:
         pk = peaks()
@@ -389,7 +401,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": desc, "per_gpu_batch": per_gpu, "global_batch": total, "parallelism": f"dp{world}",
                        "l2": f"no explicit flush: device memory in use by one step is {in_use.value / 1e6:.0f} MB (L2 is 126 MB); steps run back to back",
-                       "step": "CUDA-graph replay of forward+backward, one NCCL all-reduce of the flat gradients (N>1), one fused optimizer launch"},
+                       "step": f"CUDA-graph replay of forward+backward, {exchange}, one fused optimizer launch"},
             "e2e": {"value": total * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(gpu_launches), "final_loss": loss, "clocks": clocks,

@@ -268,6 +268,32 @@ rt_status rt_dp_init(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID
 rt_status rt_dp_allreduce_sum(rt_ctx* ctx, float* buf, int64_t n);    /* in place, on the context's stream */
 rt_status rt_dp_finalize(rt_ctx* ctx);
 
+/* ---- gradient exchange fused into the optimizer step over peer memory (new) ----------------------------------
+ * Instead of all-reducing the flat gradient buffer and then running the optimizer, every rank reads the other ranks'
+ * flat buffers directly over NVLink (plain peer loads) inside the optimizer kernel, adds them in rank order (the same
+ * order on every rank, so all ranks compute bit-identical sums) and applies the update: one kernel does the exchange
+ * and the step.  Set-up: each rank exports its buffers with rt_ipc_export, the 64-byte handles travel between the
+ * processes by any means, and each rank opens the others' with rt_ipc_open.
+ * Per step: pack the gradients into flat[step & 1], rt_dp_signal_peers (writes `step` into slot `rank` of every peer's
+ * flag array once the pack has finished), rt_optimizer_step_multi_peers.  The optimizer kernel waits, with a bounded
+ * number of polls, until every peer has signalled `step`; on expiry it leaves the parameters untouched and records a
+ * code in the context's status word (rt_device_status).  Two flat buffers alternate: a rank can only overwrite
+ * flat[s & 1] at step s+2, after every peer has signalled step s+1 and has therefore finished reading it. */
+#define RT_IPC_HANDLE_BYTES 64
+#define RT_DP_MAX_PEERS 8
+rt_status rt_ipc_export(rt_ctx* ctx, void* device_ptr, uint8_t handle[RT_IPC_HANDLE_BYTES]); /* ptr: start of an rt_malloc block */
+rt_status rt_ipc_open(rt_ctx* ctx, const uint8_t handle[RT_IPC_HANDLE_BYTES], void** peer_ptr);
+rt_status rt_ipc_close(rt_ctx* ctx, void* peer_ptr);
+/* peer_flags[r] = rank r's flag array (world ints) as opened on this rank; the entry of this rank is ignored. */
+rt_status rt_dp_signal_peers(rt_ctx* ctx, int* const* peer_flags, int rank, int world, int step);
+/* Like rt_optimizer_step_multi, with grads[i] pointing into THIS rank's flat buffer `flats[rank]`; the same offsets are
+ * read from every flats[r].  local_flags = this rank's flag array.  grad_scale is normally 1/world. */
+rt_status rt_optimizer_step_multi_peers(rt_ctx* ctx, int kind, int n_tensors, float* const* params,
+                                        const float* const* grads, float* const* state1, float* const* state2,
+                                        const int64_t* sizes, float lr, float beta1, float beta2, float epsilon,
+                                        float momentum, int64_t t, float grad_scale, const float* const* flats, int rank,
+                                        int world, const int* local_flags, int step);
+
 #ifdef __cplusplus
 }
 #endif

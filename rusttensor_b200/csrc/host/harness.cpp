@@ -9,6 +9,8 @@
 //    replayed from a CUDA graph.
 //
 // No CPU fallback: every entry point fails with CudaError when no context exists.
+#include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <unordered_map>
@@ -45,6 +47,14 @@ struct DpTrainer {
   rt_graph* graph_b = nullptr;  // rest of the backward pass, when the capture was split there
   int early_lo = 0, early_hi = 0;  // parameters [early_lo, early_hi) are exchanged while graph_b runs
   bool have_loss = false;
+  // exchange fused into the optimizer step over peer memory (rt_optimizer_step_multi_peers): two flat buffers that
+  // alternate per step, a flag array written by the peers, and the peers' buffers as opened on this rank
+  bool fused = false;
+  Storage flat2[2], flag_store;
+  std::vector<const float*> peer_flat[2];
+  std::vector<int*> peer_flags;
+  std::vector<void*> opened;
+  int64_t fused_step = 0;
   // pipelined steps: double-buffered uploads, two loss slots with completion events
   std::vector<rt_upload*> uploads;
   float* pipe_loss[2] = {nullptr, nullptr};
@@ -58,6 +68,7 @@ struct DpTrainer {
   ~DpTrainer() {
     rt_ctx* c = B200Backend::ctx_slot();
     if (!c) return;
+    for (void* p : opened) rt_ipc_close(c, p);
     for (rt_upload* u : uploads) rt_upload_destroy(c, u);
     for (int i = 0; i < 2; ++i) {
       if (pipe_loss[i]) rt_host_free(c, pipe_loss[i]);
@@ -107,9 +118,10 @@ struct DpTrainer {
     }
     rt_ctx* c = B200Backend::ctx();
     const int64_t begin = offsets[lo], end = hi < (int)offsets.size() ? offsets[hi] : flat_len;
-    B200Backend::check(rt_pack_flat(c, hi - lo, srcs.data(), sizes.data() + lo, flat.ptr() + begin, w.clip_grads ? 1 : 0,
-                                    w.clip_lo, w.clip_hi));
-    B200Backend::check(rt_dp_allreduce_sum(c, flat.ptr() + begin, end - begin));
+    float* dst = fused ? flat2[fused_step & 1].ptr() : flat.ptr();
+    B200Backend::check(rt_pack_flat(c, hi - lo, srcs.data(), sizes.data() + lo, dst + begin, w.clip_grads ? 1 : 0, w.clip_lo,
+                                    w.clip_hi));
+    if (!fused) B200Backend::check(rt_dp_allreduce_sum(c, dst + begin, end - begin));
   }
 
   // forward + backward (+ gradient exchange when world > 1); everything asynchronous.
@@ -145,7 +157,7 @@ struct DpTrainer {
       if (it == index.end() || ready[it->second]) return;
       ready[it->second] = 1;
       ready_elems += sizes[it->second];
-      if (fired || ready_elems * 2 < total || ready_elems == total || !overlap_exchange) return;
+      if (fired || ready_elems * 2 < total || ready_elems == total || !overlap_exchange || fused) return;
       int64_t best = 0;
       for (int i = 0; i < n;) {  // largest contiguous run of ready parameters
         if (!ready[i]) { ++i; continue; }
@@ -182,9 +194,57 @@ struct DpTrainer {
   }
   void exchange_rest() {
     if (world == 1) return;
+    if (fused) {  // pack into this step's buffer, then tell the peers it is complete; the optimizer kernel does the rest
+      fused_step += 1;
+      pack_and_reduce(0, (int)tr->w.params.size());
+      B200Backend::check(rt_dp_signal_peers(B200Backend::ctx(), peer_flags.data(), rank, world, (int)fused_step));
+      return;
+    }
     pack_and_reduce(0, early_lo);
     pack_and_reduce(early_hi, (int)tr->w.params.size());
     B200Backend::check(rt_side_stream_join(B200Backend::ctx()));
+  }
+
+  // Peer-memory exchange, set-up part 1: allocate the buffers the peers will read / write and export their handles
+  // (3 x RT_IPC_HANDLE_BYTES: flat buffer 0, flat buffer 1, flag array).
+  void fused_export(uint8_t* out) {
+    if (world == 1) throw Error::invalid_op("fused exchange needs more than one rank");
+    if (graph) throw Error::invalid_op("set up the fused exchange before the first captured step");
+    rt_ctx* c = B200Backend::ctx();
+    // Exported blocks are at least 2 MiB: the driver may carve smaller cudaMalloc requests out of a shared block, and an
+    // IPC handle always maps the whole underlying block from its start.
+    const size_t min_elems = (size_t)1 << 19;
+    for (int i = 0; i < 2; ++i) {
+      flat2[i] = B200Backend::zeros(rt::Shape{std::max((size_t)flat_len, min_elems)});
+      B200Backend::check(rt_ipc_export(c, flat2[i].ptr(), out + i * RT_IPC_HANDLE_BYTES));
+    }
+    flag_store = B200Backend::zeros(rt::Shape{min_elems});  // all-zero bits = step 0; slot r is written by rank r
+    B200Backend::check(rt_ipc_export(c, flag_store.ptr(), out + 2 * RT_IPC_HANDLE_BYTES));
+    B200Backend::check(rt_sync(c));
+  }
+  // Part 2: `all` holds every rank's three handles in rank order.
+  void fused_connect(const uint8_t* all) {
+    if (!flat2[0].buf) throw Error::invalid_op("fused_export must run first");
+    rt_ctx* c = B200Backend::ctx();
+    for (int i = 0; i < 2; ++i) peer_flat[i].assign(world, nullptr);
+    peer_flags.assign(world, nullptr);
+    for (int r = 0; r < world; ++r) {
+      if (r == rank) {
+        peer_flat[0][r] = flat2[0].ptr();
+        peer_flat[1][r] = flat2[1].ptr();
+        peer_flags[r] = reinterpret_cast<int*>(flag_store.ptr());
+        continue;
+      }
+      void* p[3] = {nullptr, nullptr, nullptr};
+      for (int i = 0; i < 3; ++i) {
+        B200Backend::check(rt_ipc_open(c, all + ((size_t)r * 3 + i) * RT_IPC_HANDLE_BYTES, &p[i]));
+        opened.push_back(p[i]);
+      }
+      peer_flat[0][r] = static_cast<const float*>(p[0]);
+      peer_flat[1][r] = static_cast<const float*>(p[1]);
+      peer_flags[r] = static_cast<int*>(p[2]);
+    }
+    fused = true;
   }
 
   void exchange_and_update() {
@@ -202,11 +262,18 @@ struct DpTrainer {
       ps.push_back(p.data().ptr());
       s1.push_back(state1[i].ptr());
       s2.push_back(w.optimizer == 1 ? state2[i].ptr() : nullptr);
-      if (world > 1) gs.push_back(flat.ptr() + offsets[i]);
+      if (world > 1) gs.push_back((fused ? flat2[fused_step & 1].ptr() : flat.ptr()) + offsets[i]);
       else {
         if (!p.grad()) throw Error(ErrorKind::NoGradientError, "parameter received no gradient");
         gs.push_back(p.grad()->ptr());
       }
+    }
+    if (fused) {  // the gradients of all ranks are read and added inside the optimizer kernel
+      B200Backend::check(rt_optimizer_step_multi_peers(c, w.optimizer == 1 ? 1 : 2, (int)ps.size(), ps.data(), gs.data(), s1.data(),
+                                                       s2.data(), sizes.data(), w.lr, w.beta1, w.beta2, w.eps, w.momentum, t,
+                                                       1.0f / (float)world, peer_flat[fused_step & 1].data(), rank, world,
+                                                       reinterpret_cast<const int*>(flag_store.ptr()), (int)fused_step));
+      return;
     }
     // single GPU: clip fused here; multi GPU: the clip already happened while packing
     int clip = (world == 1 && w.clip_grads) ? 1 : 0;
@@ -471,6 +538,15 @@ int rth_dp_step_pipelined(int64_t h, float* prev_loss, int* has_prev) {
 // Waits for the last pipelined step and returns its loss.
 int rth_dp_pipeline_flush(int64_t h, float* loss) {
   return rt::capi::guarded<B200Backend>([&](auto&) { *loss = dp_get(h).pipe_flush(); });
+}
+// Peer-memory gradient exchange fused into the optimizer step (optional, world > 1, before the first step):
+// every rank calls rth_dp_fused_export (192 bytes out), the handles of all ranks are gathered in rank order by the
+// caller (any transport) and handed to rth_dp_fused_connect on every rank.
+int rth_dp_fused_export(int64_t h, uint8_t* handles) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { dp_get(h).fused_export(handles); });
+}
+int rth_dp_fused_connect(int64_t h, const uint8_t* all_handles) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { dp_get(h).fused_connect(all_handles); });
 }
 int rth_dp_loss_tensor(int64_t h, int64_t* out) {
   return rt::capi::guarded<B200Backend>([&](auto& r) {

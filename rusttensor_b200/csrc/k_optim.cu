@@ -102,6 +102,108 @@ __global__ void __launch_bounds__(kThreads) optimizer_kernel(const __grid_consta
   }
 }
 
+// ---- optimizer step with the gradient exchange fused in (peer memory) -----------------------------------------------
+constexpr int kMaxPeers = RT_DP_MAX_PEERS;
+constexpr uint32_t kPeerSpinLimit = 1u << 22;
+struct PeerArgs {
+  const float* flat[kMaxPeers];  // flat[r] = rank r's packed gradients (this rank's own buffer at [rank])
+  const int* flags;              // this rank's flag array: flags[r] = last step rank r has signalled
+  int world, rank, step;
+  int* status;
+};
+
+__device__ __forceinline__ float4 ld_peer4(const float* p) {  // system-scope load: never served from a stale L1 line
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_peer1(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Same work split as optimizer_kernel.  The block first waits (bounded) until every peer has signalled this step.
+template <int KIND>
+__global__ void __launch_bounds__(kThreads) optimizer_peer_kernel(const __grid_constant__ OptArgs a, const __grid_constant__ PeerArgs pa) {
+  __shared__ int ready;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int r = 0; r < pa.world && ok; ++r) {
+      if (r == pa.rank) continue;
+      const volatile int* f = pa.flags + r;
+      uint32_t spins = 0;
+      while (*f < pa.step) {
+        if (++spins > kPeerSpinLimit) {
+          ok = 0;
+          atomicCAS(pa.status, 0, 16 + r);
+          break;
+        }
+        if (spins > 32) __nanosleep(100);
+      }
+    }
+    __threadfence_system();
+    ready = ok;
+  }
+  __syncthreads();
+  if (!ready) return;
+  int ti = 0;
+  while (ti + 1 < a.count && (int)blockIdx.x >= a.block_start[ti + 1]) ++ti;
+  int64_t base = (int64_t)(blockIdx.x - a.block_start[ti]) * a.chunk;
+  const int64_t n = a.n[ti];
+  const int64_t end = base + a.chunk < n ? base + a.chunk : n;
+  float* p = a.p[ti];
+  float* s1 = a.s1[ti];
+  float* s2 = a.s2[ti];
+  const int64_t goff = a.g[ti] - pa.flat[pa.rank];  // offset of this tensor inside every flat buffer
+  const bool vec = rt_aligned16(p) && ((goff & 3) == 0) && (KIND == 0 || rt_aligned16(s1)) && (KIND != 1 || rt_aligned16(s2));
+  if (vec) {
+    const int64_t end4 = base + ((end - base) & ~int64_t(3));
+    for (int64_t i = base + threadIdx.x * 4; i < end4; i += kThreads * 4) {
+      float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < pa.world; ++r) {  // rank order: the same sum on every rank
+        const float4 t = ld_peer4(pa.flat[r] + goff + i);
+        gv.x += t.x; gv.y += t.y; gv.z += t.z; gv.w += t.w;
+      }
+      float4 pv = *reinterpret_cast<float4*>(p + i);
+      float4 m = make_float4(0, 0, 0, 0), v = make_float4(0, 0, 0, 0);
+      if (KIND != 0) m = *reinterpret_cast<float4*>(s1 + i);
+      if (KIND == 1) v = *reinterpret_cast<float4*>(s2 + i);
+      update<KIND>(pv.x, gv.x, m.x, v.x, a);
+      update<KIND>(pv.y, gv.y, m.y, v.y, a);
+      update<KIND>(pv.z, gv.z, m.z, v.z, a);
+      update<KIND>(pv.w, gv.w, m.w, v.w, a);
+      *reinterpret_cast<float4*>(p + i) = pv;
+      if (KIND != 0) *reinterpret_cast<float4*>(s1 + i) = m;
+      if (KIND == 1) *reinterpret_cast<float4*>(s2 + i) = v;
+    }
+    base = end4;
+  }
+  for (int64_t i = base + threadIdx.x; i < end; i += kThreads) {
+    float g = 0.f;
+    for (int r = 0; r < pa.world; ++r) g += ld_peer1(pa.flat[r] + goff + i);
+    float pv = p[i], m = KIND != 0 ? s1[i] : 0.f, v = KIND == 1 ? s2[i] : 0.f;
+    update<KIND>(pv, g, m, v, a);
+    p[i] = pv;
+    if (KIND != 0) s1[i] = m;
+    if (KIND == 1) s2[i] = v;
+  }
+}
+
+struct SignalArgs {
+  int* flags[kMaxPeers];
+  int world, rank, step;
+};
+// Runs after the pack kernel on the same stream: the packed gradients are complete in this GPU's memory when the
+// peers see the flag.
+__global__ void dp_signal_kernel(const SignalArgs sa) {
+  const int r = threadIdx.x;
+  if (r < sa.world && r != sa.rank) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(sa.flags[r] + sa.rank), "r"(sa.step) : "memory");
+  }
+}
+
 struct PackArgs {
   const float* src[kMaxTensors];
   int64_t n[kMaxTensors];
@@ -269,6 +371,79 @@ rt_status rt_pack_flat(rt_ctx* ctx, int n_tensors, const float* const* srcs, con
     pack_kernel<<<blocks, kThreads, 0, ctx->stream>>>(a, flat);
     RT_LAUNCHED(ctx);
   }
+  return RT_OK;
+}
+
+rt_status rt_dp_signal_peers(rt_ctx* ctx, int* const* peer_flags, int rank, int world, int step) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, peer_flags);
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_dp_signal_peers: rank %d of %d (at most %d peers)", rank, world, kMaxPeers);
+  SignalArgs sa;
+  for (int r = 0; r < kMaxPeers; ++r) sa.flags[r] = r < world ? peer_flags[r] : nullptr;
+  for (int r = 0; r < world; ++r)
+    if (r != rank && !sa.flags[r]) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_dp_signal_peers: no flag array for rank %d", r);
+  sa.world = world; sa.rank = rank; sa.step = step;
+  dp_signal_kernel<<<1, 32, 0, ctx->stream>>>(sa);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+rt_status rt_optimizer_step_multi_peers(rt_ctx* ctx, int kind, int n_tensors, float* const* params, const float* const* grads,
+                                        float* const* state1, float* const* state2, const int64_t* sizes, float lr, float beta1,
+                                        float beta2, float epsilon, float momentum, int64_t t, float grad_scale,
+                                        const float* const* flats, int rank, int world, const int* local_flags, int step) {
+  RT_CHECK_CTX(ctx);
+  if (n_tensors <= 0) return RT_OK;
+  RT_CHECK_PTR(ctx, params);
+  RT_CHECK_PTR(ctx, grads);
+  RT_CHECK_PTR(ctx, sizes);
+  RT_CHECK_PTR(ctx, flats);
+  RT_CHECK_PTR(ctx, local_flags);
+  if (kind < 0 || kind > 3) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "optimizer kind %d", kind);
+  if (kind == 1 && t <= 0) RT_FAIL(ctx, RT_ERR_INTERNAL, "Adam step called with t=0");
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_optimizer_step_multi_peers: rank %d of %d (at most %d peers)", rank, world, kMaxPeers);
+  if (n_tensors > kMaxTensors) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_optimizer_step_multi_peers: at most %d tensors", kMaxTensors);
+  PeerArgs pa;
+  for (int r = 0; r < kMaxPeers; ++r) pa.flat[r] = r < world ? flats[r] : nullptr;
+  for (int r = 0; r < world; ++r)
+    if (!pa.flat[r]) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_optimizer_step_multi_peers: no flat buffer for rank %d", r);
+  pa.flags = local_flags; pa.world = world; pa.rank = rank; pa.step = step; pa.status = ctx->device_status;
+  const int chunk = chunk_for(ctx, sizes, n_tensors);
+  OptArgs a;
+  a.count = 0;
+  a.chunk = chunk;
+  int blocks = 0;
+  for (int i = 0; i < n_tensors; ++i) {
+    if (sizes[i] <= 0) continue;
+    if (!params[i] || !grads[i] || (kind != 0 && !state1[i]) || (kind == 1 && !state2[i]))
+      RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "optimizer step: null pointer for tensor %d", i);
+    int c = a.count++;
+    a.p[c] = params[i];
+    a.g[c] = grads[i];
+    a.s1[c] = kind != 0 ? state1[i] : nullptr;
+    a.s2[c] = kind == 1 ? state2[i] : nullptr;
+    a.n[c] = sizes[i];
+    a.block_start[c] = blocks;
+    blocks += (int)((sizes[i] + chunk - 1) / chunk);
+  }
+  if (a.count == 0) return RT_OK;
+  a.block_start[a.count] = blocks;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = epsilon; a.momentum = momentum;
+  a.grad_scale = grad_scale; a.clip = 0; a.clip_lo = 0.f; a.clip_hi = 0.f;
+  a.bc1 = a.bc2 = 1.f;
+  if (kind == 1) {
+    a.bc1 = 1.0f - powi_f32(beta1, (int)t);
+    a.bc2 = 1.0f - powi_f32(beta2, (int)t);
+  }
+  switch (kind) {
+    case 0: optimizer_peer_kernel<0><<<blocks, kThreads, 0, ctx->stream>>>(a, pa); break;
+    case 1: optimizer_peer_kernel<1><<<blocks, kThreads, 0, ctx->stream>>>(a, pa); break;
+    case 2: optimizer_peer_kernel<2><<<blocks, kThreads, 0, ctx->stream>>>(a, pa); break;
+    default: optimizer_peer_kernel<3><<<blocks, kThreads, 0, ctx->stream>>>(a, pa); break;
+  }
+  RT_LAUNCHED(ctx);
   return RT_OK;
 }
 

@@ -515,6 +515,7 @@ rt_status rt_dp_init(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID
   ctx->dp_rank = rank;
   ctx->dp_world = world;
   if (world == 1) return RT_OK;
+  if (ctx->nccl_comm) return RT_OK;  // already joined (a second trainer on the same context reuses the communicator)
   RT_CHECK_PTR(ctx, id);
   NcclApi& n = nccl();
   if (!n.ok) RT_FAIL(ctx, RT_ERR_NCCL, "libnccl.so.2 could not be loaded");
@@ -535,6 +536,31 @@ rt_status rt_dp_allreduce_sum(rt_ctx* ctx, float* buf, int64_t count) {
   const int nccl_float32 = 7, nccl_sum = 0;
   int rc = n.AllReduce(buf, buf, (size_t)count, nccl_float32, nccl_sum, ctx->nccl_comm, ctx->stream);
   if (rc != 0) RT_FAIL(ctx, RT_ERR_NCCL, "ncclAllReduce failed: %s", n.GetErrorString ? n.GetErrorString(rc) : "?");
+  return RT_OK;
+}
+
+rt_status rt_ipc_export(rt_ctx* ctx, void* device_ptr, uint8_t handle[RT_IPC_HANDLE_BYTES]) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, device_ptr);
+  RT_CHECK_PTR(ctx, handle);
+  static_assert(sizeof(cudaIpcMemHandle_t) == RT_IPC_HANDLE_BYTES, "handle size");
+  cudaIpcMemHandle_t h;
+  RT_CUDA(ctx, cudaIpcGetMemHandle(&h, device_ptr));
+  memcpy(handle, &h, sizeof(h));
+  return RT_OK;
+}
+rt_status rt_ipc_open(rt_ctx* ctx, const uint8_t handle[RT_IPC_HANDLE_BYTES], void** peer_ptr) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, handle);
+  RT_CHECK_PTR(ctx, peer_ptr);
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  RT_CUDA(ctx, cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return RT_OK;
+}
+rt_status rt_ipc_close(rt_ctx* ctx, void* peer_ptr) {
+  RT_CHECK_CTX(ctx);
+  if (peer_ptr) RT_CUDA(ctx, cudaIpcCloseMemHandle(peer_ptr));
   return RT_OK;
 }
 

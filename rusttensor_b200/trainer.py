@@ -109,6 +109,45 @@ class DataParallelTrainer:
         self._call("dp_last_loss", C.c_int64(self.handle), C.byref(loss))
         return loss.value
 
+    # ---- gradient exchange fused into the optimizer step over peer memory (world > 1) ----
+    def fused_export(self):
+        """192 bytes: the IPC handles of this rank's two flat gradient buffers and of its flag array."""
+        buf = (C.c_uint8 * 192)()
+        self._call("dp_fused_export", C.c_int64(self.handle), buf)
+        return bytes(buf)
+
+    def fused_connect(self, all_handles):
+        """``all_handles``: the 192-byte blobs of every rank, concatenated in rank order."""
+        data = bytes(all_handles)
+        assert len(data) == 192 * self.world
+        buf = (C.c_uint8 * len(data)).from_buffer_copy(data)
+        self._call("dp_fused_connect", C.c_int64(self.handle), buf)
+
+    def connect_peers(self, dist):
+        """Sets the fused exchange up through a ``torch.distributed`` process group.  Every rank calls it and every rank
+        gets the same answer: True when all ranks are connected; False when any rank failed (the trainer must then be
+        discarded and a new one used with the NCCL exchange).  All collectives run on every rank whatever fails."""
+        import torch
+
+        ok, blob = 1, bytes(192)
+        try:
+            blob = self.fused_export()
+        except Exception as e:  # noqa: BLE001
+            ok, self.peer_error = 0, str(e)
+        mine = torch.tensor(list(blob) + [ok], dtype=torch.uint8, device="cuda")
+        parts = [torch.zeros_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine)
+        rows = [bytes(p.cpu().tolist()) for p in parts]
+        ok = min(r[192] for r in rows)
+        if ok:
+            try:
+                self.fused_connect(b"".join(r[:192] for r in rows))
+            except Exception as e:  # noqa: BLE001
+                ok, self.peer_error = 0, str(e)
+        flag = torch.tensor([ok], dtype=torch.int32, device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return bool(flag.item())
+
     # ---- pipelined steps: the upload of step i+1 overlaps the device work of step i ----
     def pipeline_buffer(self, i):
         """numpy view of the pinned host buffer to fill with input ``i`` of the NEXT pipelined step

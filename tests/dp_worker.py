@@ -26,6 +26,8 @@ def main():
     dist.broadcast(idt, 0)
     dims = [4, 8, 4, 6, 16, 5]
     tr = rt.DataParallelTrainer(3, dims, rank=rank, world=world, nccl_id=idt.cpu().tolist(), device=local)
+    if os.environ.get("RT_B200_DP_FUSED", "0") == "1":
+        assert tr.connect_peers(dist), getattr(tr, "peer_error", "peer set-up failed on another rank")
     params, _ = workload_data(3, dims, seed=0)
     for t, p in zip(tr.params, params):
         t.update_from_host(p)

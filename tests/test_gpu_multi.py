@@ -21,15 +21,16 @@ def _gpu_count():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("overlap", ["0", "1"])
+@pytest.mark.parametrize("exchange", ["nccl", "nccl-overlap", "peer-fused"])
 @pytest.mark.parametrize("mode", ["graph", "eager"])
-def test_two_ranks_match_one_gpu_on_the_joint_batch(gpu_engine, tmp_path, mode, overlap):
+def test_two_ranks_match_one_gpu_on_the_joint_batch(gpu_engine, tmp_path, mode, exchange):
     if _gpu_count() < 2:
         pytest.skip("needs two GPUs")
     out = str(tmp_path / "dp2.npz")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", "29533", os.path.join(HERE, "dp_worker.py"), out, mode]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", RT_B200_DP_OVERLAP=overlap)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", RT_B200_DP_OVERLAP="1" if exchange == "nccl-overlap" else "0",
+               RT_B200_DP_FUSED="1" if exchange == "peer-fused" else "0")
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     got = np.load(out)
