@@ -169,8 +169,9 @@ def measure_dominant_kernel(rt, capi, config, dims, pk):
     t = float(np.mean(times)) * 1e-3
     peak = pk["bf16"] / 6.0  # 3xTF32: TF32 runs at half the bf16 rate, three MMAs per product
     achieved = flops / t / 1e12
-    # DRAM bytes (read + write) of the two kernels of this call from the ncu capture summarised in
-    # profiles/conv_kernels_c3_ncu_full.md: 13.07 MB (input gradient) + 19.34 MB (weight gradient); the outputs stay in L2.
+    # DRAM bytes (read + write) of the two kernels of this call from an `ncu --set full` capture of this workload
+    # (its summary is committed with the other profile summaries): 13.07 MB (input gradient) + 19.34 MB (weight
+    # gradient); the outputs stay in L2.
     traffic = 32.41e6 if (n, hw, c1, c2) == (256, 14, 32, 64) else None
     return {"bound": "tensor", "kernel": name, "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
             "traffic": traffic, "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, ncu)",
