@@ -46,6 +46,7 @@ struct DpTrainer {
   rt_graph* graph = nullptr;    // forward + backward (up to the point where the early gradient slice is final)
   rt_graph* graph_b = nullptr;  // rest of the backward pass, when the capture was split there
   int early_lo = 0, early_hi = 0;  // parameters [early_lo, early_hi) are exchanged while graph_b runs
+  bool packed_in_graph = false;    // the captured graph ends with the pack kernel
   bool have_loss = false;
   // exchange fused into the optimizer step over peer memory (rt_optimizer_step_multi_peers): two flat buffers that
   // alternate per step, a flag array written by the peers, and the peers' buffers as opened on this rank
@@ -107,7 +108,7 @@ struct DpTrainer {
   }
 
   // Packs the gradients of parameters [lo, hi) into their slice of the flat buffer and all-reduces that slice.
-  void pack_and_reduce(int lo, int hi) {
+  void pack_and_reduce(int lo, int hi, bool do_pack = true, bool do_reduce = true) {
     if (lo >= hi) return;
     auto& w = tr->w;
     std::vector<const float*> srcs;
@@ -119,9 +120,10 @@ struct DpTrainer {
     rt_ctx* c = B200Backend::ctx();
     const int64_t begin = offsets[lo], end = hi < (int)offsets.size() ? offsets[hi] : flat_len;
     float* dst = fused ? flat2[fused_step & 1].ptr() : flat.ptr();
-    B200Backend::check(rt_pack_flat(c, hi - lo, srcs.data(), sizes.data() + lo, dst + begin, w.clip_grads ? 1 : 0, w.clip_lo,
-                                    w.clip_hi));
-    if (!fused) B200Backend::check(rt_dp_allreduce_sum(c, dst + begin, end - begin));
+    if (do_pack)
+      B200Backend::check(rt_pack_flat(c, hi - lo, srcs.data(), sizes.data() + lo, dst + begin, w.clip_grads ? 1 : 0, w.clip_lo,
+                                      w.clip_hi));
+    if (do_reduce && !fused) B200Backend::check(rt_dp_allreduce_sum(c, dst + begin, end - begin));
   }
 
   // forward + backward (+ gradient exchange when world > 1); everything asynchronous.
@@ -178,6 +180,10 @@ struct DpTrainer {
     loss.backward();
     Tensor::leaf_ready_hook() = nullptr;
     if (!capturing) exchange_rest();
+    else if (!fused && !fired) {  // single exchange: the pack kernel is recorded with the backward pass
+      pack_and_reduce(0, n, true, false);
+      packed_in_graph = true;
+    }
     return loss;
   }
   void exchange_early() {
@@ -198,6 +204,10 @@ struct DpTrainer {
       fused_step += 1;
       pack_and_reduce(0, (int)tr->w.params.size());
       B200Backend::check(rt_dp_signal_peers(B200Backend::ctx(), peer_flags.data(), rank, world, (int)fused_step));
+      return;
+    }
+    if (packed_in_graph && graph) {  // replaying: the graph has already packed
+      pack_and_reduce(0, (int)tr->w.params.size(), false, true);
       return;
     }
     pack_and_reduce(0, early_lo);
