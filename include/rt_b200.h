@@ -192,6 +192,15 @@ rt_status rt_log_softmax(rt_ctx* ctx, const float* x, int64_t outer, int64_t len
 rt_status rt_log_softmax_backward(rt_ctx* ctx, const float* x, const float* g, int64_t outer, int64_t len,
                                   int64_t inner, float* dx);
 
+/* Fused classification loss (no counterpart in the reference, whose examples spell the chain out:
+ * examples/train_mnist_cpu.rs:63-97): loss[0] = -(1/rows) * sum over rows and classes of targets * log_softmax(logits).
+ * Backward: dlogits = -(g/rows) * (targets - softmax(logits) * sum_k targets), dtargets = -(g/rows) * log_softmax(logits);
+ * g is the one-element upstream gradient on the device; either output may be NULL. */
+rt_status rt_softmax_cross_entropy(rt_ctx* ctx, const float* logits, const float* targets, int64_t rows, int64_t classes,
+                                   float* loss);
+rt_status rt_softmax_cross_entropy_backward(rt_ctx* ctx, const float* logits, const float* targets, const float* g,
+                                            int64_t rows, int64_t classes, float* dlogits, float* dtargets);
+
 /* out[outer, inner] = sum over the middle axis of x[outer, len, inner], like rt_reduce(RT_RED_SUM), but the
  * call allocates nothing: the partial sums of a split reduction go to a fixed 1 MiB array in device memory
  * (one per device) instead of a block from the context's allocator.  No counterpart in the reference; it
@@ -211,6 +220,13 @@ rt_status rt_max_pool2d(rt_ctx* ctx, const float* x, int64_t n, int64_t c, int64
                         int sh, int sw, int ph, int pw, float* y, float* idx);
 rt_status rt_max_pool2d_backward(rt_ctx* ctx, const float* g, const float* idx, int64_t n, int64_t c, int64_t h,
                                  int64_t w, int kh, int kw, int sh, int sw, int ph, int pw, float* dx);
+/* Fused relu + max_pool2d (no counterpart in the reference, whose models call relu and max_pool2d one after the other,
+ * e.g. examples/train_mnist_cnn_cpu.rs): y, idx = max_pool2d(relu(x)) without materialising relu(x); the backward routes g
+ * through idx and masks it with x > 0 in the same pass.  Values and indices are bit-identical to the two separate ops. */
+rt_status rt_relu_max_pool2d(rt_ctx* ctx, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, int kh, int kw,
+                             int sh, int sw, int ph, int pw, float* y, float* idx);
+rt_status rt_relu_max_pool2d_backward(rt_ctx* ctx, const float* x, const float* g, const float* idx, int64_t n, int64_t c,
+                                      int64_t h, int64_t w, int kh, int kw, int sh, int sw, int ph, int pw, float* dx);
 
 /* ---- dense contractions ---------------------------------------------------------------------- */
 /* C[M,N] = op(A) * op(B) (+ C when accumulate != 0); row-major with leading dimensions.

@@ -26,6 +26,7 @@
 #include <tuple>
 #include <unordered_set>
 #include <utility>
+#include <type_traits>
 #include <vector>
 
 namespace rt {
@@ -97,7 +98,8 @@ struct OpType {
     Matmul, Mul, Add, Mean, Relu, LogSoftmax, Sum, Sub, Div, Exp, Ln, Broadcast, View, Abs,
     Sigmoid, Sqrt, Tanh, Softplus, Max, Min, Prod, LogSumExp, ArgMax, ArgMin, Powf, Square,
     Maximum, Minimum, Elu, Transpose, Sin, Cos, Tan, Conv2d, MaxPool2D, Conv2DTranspose, Slice,
-    Concat, ExpandDims, Squeeze, Clip, DivScalar, MulScalar
+    Concat, ExpandDims, Squeeze, Clip, DivScalar, MulScalar,
+    FusedReluMaxPool2D, FusedSoftmaxNll  // fused forward ops added beside the reference's (ops::fused_*)
   } kind;
   std::optional<size_t> axis;          // Mean/Sum/Max/Min/Prod/LogSumExp(Option), LogSoftmax/ArgMax/...
   float scalar = 0.f;                  // Elu(alpha), MulScalar, DivScalar
@@ -117,7 +119,7 @@ struct OpType {
       "Div", "Exp", "Ln", "Broadcast", "View", "Abs", "Sigmoid", "Sqrt", "Tanh", "Softplus", "Max",
       "Min", "Prod", "LogSumExp", "ArgMax", "ArgMin", "Powf", "Square", "Maximum", "Minimum", "Elu",
       "Transpose", "Sin", "Cos", "Tan", "Conv2d", "MaxPool2D", "Conv2DTranspose", "Slice", "Concat",
-      "ExpandDims", "Squeeze", "Clip", "DivScalar", "MulScalar"};
+      "ExpandDims", "Squeeze", "Clip", "DivScalar", "MulScalar", "FusedReluMaxPool2D", "FusedSoftmaxNll"};
     return n[(int)kind];
   }
 };
@@ -787,6 +789,64 @@ Tensor<B> softmax_cross_entropy(const Tensor<B>& logits, const Tensor<B>& target
   Tensor<B> minus_one = Tensor<B>::from_vec({-1.0f}, Shape{}, false);
   Tensor<B> per_sample = mul(s, minus_one);
   return apply_reduction(per_sample, r);
+}
+
+// ---- fused forward ops (not in the reference) -----------------------------------------------------------------------
+// They sit beside the unchanged ops and compute exactly what the corresponding chain of reference ops computes.  A
+// backend that has no fused kernels (the CPU restatement used by the tests) gets the chain itself.
+template <class B, class = void>
+struct HasFusedForward : std::false_type {};
+template <class B>
+struct HasFusedForward<B, std::void_t<decltype(&B::relu_max_pool2d)>> : std::true_type {};
+
+// max_pool2d(relu(x)): one kernel forward (relu(x) is never materialised), one backward.
+template <class B>
+Tensor<B> fused_relu_max_pool2d(const Tensor<B>& input, Pair kernel, Pair stride, Pair padding) {
+  if constexpr (!HasFusedForward<B>::value) {
+    return max_pool2d(relu(input), kernel, stride, padding);
+  } else {
+    auto r = B::relu_max_pool2d(input.data(), kernel, stride, padding);
+    bool rg = input.requires_grad();
+    Tensor<B> t(std::move(r.first), rg);
+    if (rg) {
+      Tensor<B> idx(std::move(r.second), false);
+      OpType ot(OpType::FusedReluMaxPool2D);
+      ot.kernel_size = kernel;
+      ot.stride = stride;
+      ot.padding = padding;
+      t.set_op(Op<B>(ot, {input, idx}, [](const Op<B>& op, const St<B>& g) {
+        St<B> gi = B::relu_max_pool2d_backward(op, g);
+        return Grads<B>{std::move(gi), B::unused_grad(B::shape(op.inputs[1].data()))};
+      }));
+    }
+    return t;
+  }
+}
+
+// -mean over the rows of sum_k targets * log_softmax(logits, 1): the loss of the reference's classification examples
+// (examples/train_mnist_cpu.rs:63-97: log_softmax -> mul -> sum(axis 1) -> mean -> mul(-1)), 2-D logits.
+template <class B>
+Tensor<B> fused_softmax_nll(const Tensor<B>& logits, const Tensor<B>& targets) {
+  if (logits.shape() != targets.shape()) throw Error::incompatible("fused_softmax_nll", logits.shape(), targets.shape());
+  if (logits.shape().size() != 2) throw Error::invalid_op("fused_softmax_nll expects [rows, classes] logits");
+  if constexpr (!HasFusedForward<B>::value) {
+    Tensor<B> e = mul(log_softmax(logits, 1), targets);
+    Tensor<B> per = sum(e, 1);
+    Tensor<B> m = mean(per, std::nullopt);
+    Tensor<B> minus_one = Tensor<B>::from_vec({-1.0f}, Shape{}, false);
+    return mul(m, minus_one);
+  } else {
+    St<B> out = B::softmax_nll(logits.data(), targets.data());
+    bool rg = logits.requires_grad() || targets.requires_grad();
+    Tensor<B> t(std::move(out), rg);
+    if (rg) {
+      t.set_op(Op<B>(OpType(OpType::FusedSoftmaxNll), {logits, targets}, [](const Op<B>& op, const St<B>& g) {
+        auto p = B::softmax_nll_backward(op, g);
+        return Grads<B>{std::move(p.first), std::move(p.second)};
+      }));
+    }
+    return t;
+  }
 }
 
 }  // namespace ops

@@ -568,6 +568,48 @@ struct B200Backend {
     return dx;
   }
 
+  // ---- fused forward ops (no counterpart in the reference; ops::fused_* in autograd.hpp) -------------------------
+  static std::pair<Storage, Storage> relu_max_pool2d(const Storage& x, Pair k, Pair s, Pair p) {
+    if (x.shape.size() != 4) throw Error::invalid_op("relu_max_pool2d expects 4D input (NCHW)");
+    size_t ho = (x.shape[2] + 2 * p.first - k.first) / s.first + 1, wo = (x.shape[3] + 2 * p.second - k.second) / s.second + 1;
+    Shape os{x.shape[0], x.shape[1], ho, wo};
+    Storage y = alloc(os), idx = alloc(os);
+    check(rt_relu_max_pool2d(ctx(), x.ptr(), (int64_t)x.shape[0], (int64_t)x.shape[1], (int64_t)x.shape[2], (int64_t)x.shape[3],
+                             (int)k.first, (int)k.second, (int)s.first, (int)s.second, (int)p.first, (int)p.second, y.ptr(),
+                             idx.ptr()));
+    return {std::move(y), std::move(idx)};
+  }
+  static Storage relu_max_pool2d_backward(const OpB& o, const Storage& g) {
+    if (o.inputs.size() < 2) throw Error::invalid_op("relu_max_pool2d_backward requires the input and the indices");
+    const Storage& x = o.inputs[0].data();
+    const Storage& idx = o.inputs[1].data();
+    if (g.numel() != idx.numel()) throw Error::shape_mismatch(idx.shape, g.shape);
+    Shape is = x.shape;
+    Pair k = o.op_type.kernel_size, s = o.op_type.stride, p = o.op_type.padding;
+    Storage dx = alloc(is);
+    check(rt_relu_max_pool2d_backward(ctx(), x.ptr(), g.ptr(), idx.ptr(), (int64_t)is[0], (int64_t)is[1], (int64_t)is[2],
+                                      (int64_t)is[3], (int)k.first, (int)k.second, (int)s.first, (int)s.second, (int)p.first,
+                                      (int)p.second, dx.ptr()));
+    return dx;
+  }
+  static Storage softmax_nll(const Storage& logits, const Storage& targets) {
+    Storage loss = alloc(Shape{});
+    check(rt_softmax_cross_entropy(ctx(), logits.ptr(), targets.ptr(), (int64_t)logits.shape[0], (int64_t)logits.shape[1],
+                                   loss.ptr()));
+    return loss;
+  }
+  static std::pair<Storage, Storage> softmax_nll_backward(const OpB& o, const Storage& g) {
+    const Storage& logits = o.inputs[0].data();
+    const Storage& targets = o.inputs[1].data();
+    if (g.numel() != 1) throw Error::shape_mismatch(Shape{}, g.shape);
+    const bool need_l = o.inputs[0].requires_grad(), need_t = o.inputs[1].requires_grad();
+    Storage dl = need_l ? alloc(logits.shape) : unused_grad(logits.shape);
+    Storage dt = need_t ? alloc(targets.shape) : unused_grad(targets.shape);
+    check(rt_softmax_cross_entropy_backward(ctx(), logits.ptr(), targets.ptr(), g.ptr(), (int64_t)logits.shape[0],
+                                            (int64_t)logits.shape[1], need_l ? dl.ptr() : nullptr, need_t ? dt.ptr() : nullptr));
+    return {std::move(dl), std::move(dt)};
+  }
+
   // ---- optimizer steps (mod.rs:18-36, 256-272) ---------------------------------------------------
   static void sgd_step(Storage& w, const Storage& dw, float lr) {
     if (w.shape != dw.shape) throw Error::shape_mismatch(w.shape, dw.shape);

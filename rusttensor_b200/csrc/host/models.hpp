@@ -31,6 +31,8 @@ struct Workload {
   float lr = 1e-3f, beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, momentum = 0.9f;
   bool clip_grads = false;
   float clip_lo = -5.f, clip_hi = 5.f;
+  // true: relu + max_pool2d and the classification loss go through the fused ops (ops::fused_*); same mathematics
+  bool fused_forward = false;
 
   void add_param(const std::string& n, const Shape& s) {
     params.push_back(Tensor<B>::zeros(s, true));
@@ -47,6 +49,10 @@ struct Workload {
 template <class B>
 Workload<B> make_workload(int config, const std::vector<size_t>& d) {
   Workload<B> w;
+  if (config >= 100) {  // 100 + c: configuration c built from the fused forward ops
+    config -= 100;
+    w.fused_forward = true;
+  }
   w.config = config;
   w.dims = d;
   auto need = [&](size_t n) {
@@ -133,10 +139,15 @@ template <class B>
 Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
   const auto& p = w.params;
   const auto& d = w.dims;
+  const Pair two{2, 2}, zero{0, 0};
+  auto relu_pool = [&](const Tensor<B>& x) {
+    return w.fused_forward ? ops::fused_relu_max_pool2d(x, two, two, zero) : ops::max_pool2d(ops::relu(x), two, two, zero);
+  };
   switch (w.config) {
     case C1_MLP: {
       Tensor<B> h = ops::relu(linear(in.at(0), p[0], p[1]));
       Tensor<B> logits = linear(h, p[2], p[3]);
+      if (w.fused_forward) return ops::fused_softmax_nll(logits, in.at(1));
       return nll_loss(ops::log_softmax(logits, 1), in.at(1));
     }
     case C2_ELEMENTWISE: {
@@ -157,17 +168,18 @@ Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
     case C3_CNN: {
       size_t n = in.at(0).shape()[0];
       Tensor<B> c1 = ops::conv2d(in[0], p[0], &p[1], {1, 1}, {1, 1});
-      Tensor<B> p1 = ops::max_pool2d(ops::relu(c1), {2, 2}, {2, 2}, {0, 0});
+      Tensor<B> p1 = relu_pool(c1);
       Tensor<B> c2 = ops::conv2d(p1, p[2], &p[3], {1, 1}, {1, 1});
-      Tensor<B> p2 = ops::max_pool2d(ops::relu(c2), {2, 2}, {2, 2}, {0, 0});
+      Tensor<B> p2 = relu_pool(c2);
       Tensor<B> flat = p2.view({n, p[4].shape()[0]});
       Tensor<B> f1 = ops::relu(linear(flat, p[4], p[5]));
       Tensor<B> logits = linear(f1, p[6], p[7]);
+      if (w.fused_forward) return ops::fused_softmax_nll(logits, in.at(1));
       return ops::softmax_cross_entropy(logits, in.at(1), 1, Reduction::Mean);
     }
     case C4_CONV_CONVT: {
       Tensor<B> c = ops::conv2d(in.at(0), p[0], &p[1], {1, 1}, {1, 1});
-      Tensor<B> pl = ops::max_pool2d(ops::relu(c), {2, 2}, {2, 2}, {0, 0});
+      Tensor<B> pl = relu_pool(c);
       Tensor<B> up = ops::conv2d_transpose(pl, p[2], &p[3], {2, 2}, {1, 1});
       return ops::mse_loss(up, in.at(1), Reduction::Mean);
     }
@@ -187,7 +199,7 @@ Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
         c = ops::add(ops::mul(fg, c), ops::mul(ig, gg));
         h = ops::mul(og, ops::tanh(c));
         Tensor<B> logits = linear(h, p[2], p[3]);
-        Tensor<B> l = ops::softmax_cross_entropy(logits, y_t, 1, Reduction::Mean);
+        Tensor<B> l = w.fused_forward ? ops::fused_softmax_nll(logits, y_t) : ops::softmax_cross_entropy(logits, y_t, 1, Reduction::Mean);
         total = t == 0 ? l : ops::add(total, l);
       }
       return total;

@@ -19,6 +19,7 @@ namespace {
 
 constexpr int kThreads = 256;
 
+template <bool RELU>  // RELU: the pooled tensor is relu(x), computed on the fly (fused relu + max_pool2d)
 __global__ void __launch_bounds__(kThreads) pool_fwd_general(const float* __restrict__ x, float* __restrict__ y,
                                                               float* __restrict__ idx, int64_t total, int h, int w, int ho,
                                                               int wo, int kh, int kw, int sh, int sw, int ph, int pw) {
@@ -35,7 +36,11 @@ __global__ void __launch_bounds__(kThreads) pool_fwd_general(const float* __rest
       int iy = yo * sh + ky - ph;
       for (int kx = 0; kx < kw; ++kx, ++iw) {
         int ix = xo * sw + kx - pw;
-        float v = (iy >= 0 && iy < h && ix >= 0 && ix < w) ? __ldg(p + (int64_t)iy * w + ix) : -INFINITY;
+        float v = -INFINITY;
+        if (iy >= 0 && iy < h && ix >= 0 && ix < w) {
+          v = __ldg(p + (int64_t)iy * w + ix);
+          if (RELU) v = fmaxf(v, 0.f);
+        }
         if (v > mv) {
           mv = v;
           mi = iw;
@@ -48,6 +53,7 @@ __global__ void __launch_bounds__(kThreads) pool_fwd_general(const float* __rest
 }
 
 // 2x2 window, stride 2, no padding, even H and W: one thread per output, two 8-byte loads.
+template <bool RELU>
 __global__ void __launch_bounds__(kThreads) pool_fwd_2x2(const float* __restrict__ x, float* __restrict__ y,
                                                           float* __restrict__ idx, int64_t total, int w, int ho, int wo) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -56,6 +62,10 @@ __global__ void __launch_bounds__(kThreads) pool_fwd_2x2(const float* __restrict
     int64_t row = o / wo;  // = bc * ho + yo ; the input row pair starts at 2 * row (H = 2 * ho)
     const float2* p = reinterpret_cast<const float2*>(x + (row * 2) * w) + xo;
     float2 a = __ldg(p), b = __ldg(p + (w >> 1));
+    if (RELU) {
+      a.x = fmaxf(a.x, 0.f); a.y = fmaxf(a.y, 0.f);
+      b.x = fmaxf(b.x, 0.f); b.y = fmaxf(b.y, 0.f);
+    }
     float mv = -INFINITY;
     int mi = 0;
     if (a.x > mv) { mv = a.x; mi = 0; }
@@ -67,8 +77,10 @@ __global__ void __launch_bounds__(kThreads) pool_fwd_2x2(const float* __restrict
   }
 }
 
+template <bool RELU>  // RELU: dx is also masked with x > 0 (backward of the fused relu + max_pool2d)
 __global__ void __launch_bounds__(kThreads) pool_bwd_2x2(const float* __restrict__ g, const float* __restrict__ idx,
-                                                          float* __restrict__ dx, int64_t total, int w, int ho, int wo) {
+                                                          const float* __restrict__ x, float* __restrict__ dx, int64_t total,
+                                                          int w, int ho, int wo) {
   int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += stride) {
     int xo = (int)(o % wo);
@@ -77,6 +89,12 @@ __global__ void __launch_bounds__(kThreads) pool_bwd_2x2(const float* __restrict
     int mi = (int)lrintf(__ldg(idx + o));
     float2 a = make_float2(mi == 0 ? gv : 0.f, mi == 1 ? gv : 0.f);
     float2 b = make_float2(mi == 2 ? gv : 0.f, mi == 3 ? gv : 0.f);
+    if (RELU) {
+      const float2* q = reinterpret_cast<const float2*>(x + (row * 2) * w) + xo;
+      const float2 xa = __ldg(q), xb = __ldg(q + (w >> 1));
+      a.x = xa.x > 0.f ? a.x : 0.f; a.y = xa.y > 0.f ? a.y : 0.f;
+      b.x = xb.x > 0.f ? b.x : 0.f; b.y = xb.y > 0.f ? b.y : 0.f;
+    }
     float2* p = reinterpret_cast<float2*>(dx + (row * 2) * w) + xo;
     p[0] = a;
     p[w >> 1] = b;
@@ -120,8 +138,8 @@ static rt_status pool_dims(rt_ctx* ctx, int64_t h, int64_t w, int kh, int kw, in
   return RT_OK;
 }
 
-rt_status rt_max_pool2d(rt_ctx* ctx, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, int kh, int kw, int sh,
-                        int sw, int ph, int pw, float* y, float* idx) {
+static rt_status pool_forward(rt_ctx* ctx, bool relu, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, int kh, int kw,
+                              int sh, int sw, int ph, int pw, float* y, float* idx) {
   RT_CHECK_CTX(ctx);
   int64_t ho, wo;
   rt_status st = pool_dims(ctx, h, w, kh, kw, sh, sw, ph, pw, &ho, &wo);
@@ -134,14 +152,30 @@ rt_status rt_max_pool2d(rt_ctx* ctx, const float* x, int64_t n, int64_t c, int64
   int grid = rt_grid_for(ctx, total, kThreads * 2);
   bool fast = kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && (h % 2 == 0) && (w % 2 == 0) &&
               (reinterpret_cast<uintptr_t>(x) % 8 == 0);
-  if (fast) pool_fwd_2x2<<<grid, kThreads, 0, ctx->stream>>>(x, y, idx, total, (int)w, (int)ho, (int)wo);
-  else pool_fwd_general<<<grid, kThreads, 0, ctx->stream>>>(x, y, idx, total, (int)h, (int)w, (int)ho, (int)wo, kh, kw, sh, sw, ph, pw);
+  if (fast) {
+    if (relu) pool_fwd_2x2<true><<<grid, kThreads, 0, ctx->stream>>>(x, y, idx, total, (int)w, (int)ho, (int)wo);
+    else pool_fwd_2x2<false><<<grid, kThreads, 0, ctx->stream>>>(x, y, idx, total, (int)w, (int)ho, (int)wo);
+  } else {
+    if (relu) pool_fwd_general<true><<<grid, kThreads, 0, ctx->stream>>>(x, y, idx, total, (int)h, (int)w, (int)ho, (int)wo, kh, kw, sh, sw, ph, pw);
+    else pool_fwd_general<false><<<grid, kThreads, 0, ctx->stream>>>(x, y, idx, total, (int)h, (int)w, (int)ho, (int)wo, kh, kw, sh, sw, ph, pw);
+  }
   RT_LAUNCHED(ctx);
   return RT_OK;
 }
 
-rt_status rt_max_pool2d_backward(rt_ctx* ctx, const float* g, const float* idx, int64_t n, int64_t c, int64_t h, int64_t w,
-                                 int kh, int kw, int sh, int sw, int ph, int pw, float* dx) {
+rt_status rt_max_pool2d(rt_ctx* ctx, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, int kh, int kw, int sh,
+                        int sw, int ph, int pw, float* y, float* idx) {
+  return pool_forward(ctx, false, x, n, c, h, w, kh, kw, sh, sw, ph, pw, y, idx);
+}
+
+rt_status rt_relu_max_pool2d(rt_ctx* ctx, const float* x, int64_t n, int64_t c, int64_t h, int64_t w, int kh, int kw, int sh,
+                             int sw, int ph, int pw, float* y, float* idx) {
+  return pool_forward(ctx, true, x, n, c, h, w, kh, kw, sh, sw, ph, pw, y, idx);
+}
+
+// x != nullptr: backward of the fused relu + max_pool2d (dx masked with x > 0)
+static rt_status pool_backward(rt_ctx* ctx, const float* x, const float* g, const float* idx, int64_t n, int64_t c, int64_t h,
+                               int64_t w, int kh, int kw, int sh, int sw, int ph, int pw, float* dx) {
   RT_CHECK_CTX(ctx);
   int64_t ho, wo;
   rt_status st = pool_dims(ctx, h, w, kh, kw, sh, sw, ph, pw, &ho, &wo);
@@ -155,9 +189,15 @@ rt_status rt_max_pool2d_backward(rt_ctx* ctx, const float* g, const float* idx, 
     if (total == 0) return RT_OK;
     RT_CHECK_PTR(ctx, g);
     RT_CHECK_PTR(ctx, idx);
-    pool_bwd_2x2<<<rt_grid_for(ctx, total, kThreads * 2), kThreads, 0, ctx->stream>>>(g, idx, dx, total, (int)w, (int)ho, (int)wo);
+    const int grid2 = rt_grid_for(ctx, total, kThreads * 2);
+    if (x && reinterpret_cast<uintptr_t>(x) % 8 == 0) {
+      pool_bwd_2x2<true><<<grid2, kThreads, 0, ctx->stream>>>(g, idx, x, dx, total, (int)w, (int)ho, (int)wo);
+      RT_LAUNCHED(ctx);
+      return RT_OK;
+    }
+    pool_bwd_2x2<false><<<grid2, kThreads, 0, ctx->stream>>>(g, idx, nullptr, dx, total, (int)w, (int)ho, (int)wo);
     RT_LAUNCHED(ctx);
-    return RT_OK;
+    return x ? rt_unary_backward(ctx, RT_RELU, x, dx, dx, in_total, 0.f, 0.f) : RT_OK;
   }
   st = rt_fill(ctx, dx, 0.f, in_total);
   if (st != RT_OK || total == 0) return st;
@@ -168,7 +208,19 @@ rt_status rt_max_pool2d_backward(rt_ctx* ctx, const float* g, const float* idx, 
   if (overlap) pool_bwd_general<true><<<grid, kThreads, 0, ctx->stream>>>(g, idx, dx, total, (int)h, (int)w, (int)ho, (int)wo, kw, sh, sw, ph, pw);
   else pool_bwd_general<false><<<grid, kThreads, 0, ctx->stream>>>(g, idx, dx, total, (int)h, (int)w, (int)ho, (int)wo, kw, sh, sw, ph, pw);
   RT_LAUNCHED(ctx);
-  return RT_OK;
+  return x ? rt_unary_backward(ctx, RT_RELU, x, dx, dx, in_total, 0.f, 0.f) : RT_OK;  // element-wise, safe in place
+}
+
+rt_status rt_max_pool2d_backward(rt_ctx* ctx, const float* g, const float* idx, int64_t n, int64_t c, int64_t h, int64_t w,
+                                 int kh, int kw, int sh, int sw, int ph, int pw, float* dx) {
+  return pool_backward(ctx, nullptr, g, idx, n, c, h, w, kh, kw, sh, sw, ph, pw, dx);
+}
+
+rt_status rt_relu_max_pool2d_backward(rt_ctx* ctx, const float* x, const float* g, const float* idx, int64_t n, int64_t c,
+                                      int64_t h, int64_t w, int kh, int kw, int sh, int sw, int ph, int pw, float* dx) {
+  RT_CHECK_CTX(ctx);
+  if (n * c * h * w > 0) RT_CHECK_PTR(ctx, x);
+  return pool_backward(ctx, x, g, idx, n, c, h, w, kh, kw, sh, sw, ph, pw, dx);
 }
 
 }  // extern "C"

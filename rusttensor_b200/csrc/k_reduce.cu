@@ -899,3 +899,86 @@ extern "C" rt_status rt_reduce_sum_static_scratch(rt_ctx* ctx, const float* x, i
   }
   return RT_OK;
 }
+
+// ---- fused classification loss ---------------------------------------------------------------------------------------
+// loss = -(1/rows) * sum_b sum_k targets[b,k] * log_softmax(logits)[b,k]: the chain log_softmax -> mul -> sum(axis 1) ->
+// mean -> mul(-1) of the reference's training examples (examples/train_mnist_cpu.rs:63-97) in one kernel forward and
+// one backward.  No counterpart in the reference.  One thread per row (classification heads have tens of classes);
+// the row losses are added by one block in a fixed order.
+namespace {
+
+__device__ __forceinline__ void row_max_lse(const float* __restrict__ x, int classes, float& m, float& lse) {
+  m = -INFINITY;
+  for (int k = 0; k < classes; ++k) m = fmaxf(m, __ldg(x + k));
+  float s = 0.f;
+  for (int k = 0; k < classes; ++k) s += expf(__ldg(x + k) - m);
+  lse = logf(s);
+}
+
+__global__ void __launch_bounds__(kThreads) sce_forward_kernel(const float* __restrict__ logits, const float* __restrict__ targets,
+                                                               float* __restrict__ loss, int64_t rows, int classes) {
+  __shared__ float smem[kThreads / 32];
+  float acc = 0.f;
+  for (int64_t r = threadIdx.x; r < rows; r += kThreads) {
+    const float* x = logits + r * classes;
+    const float* t = targets + r * classes;
+    float m, lse;
+    row_max_lse(x, classes, m, lse);
+    float e = 0.f;
+    for (int k = 0; k < classes; ++k) e += ((__ldg(x + k) - m) - lse) * __ldg(t + k);
+    acc += e;
+  }
+  acc = block_reduce<RT_RED_SUM>(acc, smem);
+  if (threadIdx.x == 0) loss[0] = (acc / (float)rows) * -1.0f;
+}
+
+// dlogits = -(g/rows) * (t - softmax * sum_k t);  dtargets (optional) = -(g/rows) * log_softmax
+__global__ void __launch_bounds__(kThreads) sce_backward_kernel(const float* __restrict__ logits, const float* __restrict__ targets,
+                                                                const float* __restrict__ g, float* __restrict__ dlogits,
+                                                                float* __restrict__ dtargets, int64_t rows, int classes) {
+  const float scale = -__ldg(g) / (float)rows;
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += (int64_t)gridDim.x * blockDim.x) {
+    const float* x = logits + r * classes;
+    const float* t = targets + r * classes;
+    float m, lse;
+    row_max_lse(x, classes, m, lse);
+    float st = 0.f;
+    for (int k = 0; k < classes; ++k) st += __ldg(t + k) * scale;  // sum of the upstream gradient of log_softmax
+    for (int k = 0; k < classes; ++k) {
+      const float ls = (__ldg(x + k) - m) - lse;
+      if (dlogits) dlogits[r * classes + k] = __ldg(t + k) * scale - expf(ls) * st;
+      if (dtargets) dtargets[r * classes + k] = ls * scale;
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" rt_status rt_softmax_cross_entropy(rt_ctx* ctx, const float* logits, const float* targets, int64_t rows, int64_t classes,
+                                              float* loss) {
+  RT_CHECK_CTX(ctx);
+  if (rows <= 0 || classes <= 0) RT_FAIL(ctx, RT_ERR_EMPTY_TENSOR, "rt_softmax_cross_entropy: empty input");
+  if (classes > 4096 || rows > (int64_t(1) << 24))
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_softmax_cross_entropy: at most 4096 classes and 2^24 rows");
+  RT_CHECK_PTR(ctx, logits);
+  RT_CHECK_PTR(ctx, targets);
+  RT_CHECK_PTR(ctx, loss);
+  sce_forward_kernel<<<1, kThreads, 0, ctx->stream>>>(logits, targets, loss, rows, (int)classes);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+extern "C" rt_status rt_softmax_cross_entropy_backward(rt_ctx* ctx, const float* logits, const float* targets, const float* g,
+                                                       int64_t rows, int64_t classes, float* dlogits, float* dtargets) {
+  RT_CHECK_CTX(ctx);
+  if (rows <= 0 || classes <= 0) return RT_OK;
+  if (classes > 4096) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_softmax_cross_entropy_backward: at most 4096 classes");
+  RT_CHECK_PTR(ctx, logits);
+  RT_CHECK_PTR(ctx, targets);
+  RT_CHECK_PTR(ctx, g);
+  if (!dlogits && !dtargets) return RT_OK;
+  sce_backward_kernel<<<rt_grid_for(ctx, rows, kThreads), kThreads, 0, ctx->stream>>>(logits, targets, g, dlogits, dtargets, rows,
+                                                                                     (int)classes);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}

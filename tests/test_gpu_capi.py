@@ -202,3 +202,51 @@ def test_side_stream_sections(capi):
     capi.call("side_stream_join")  # nothing pending: a no-op
     with pytest.raises(RtError):
         capi.call("side_stream_end")
+
+
+def test_fused_relu_max_pool_is_bit_identical_to_the_two_ops(capi):
+    r = rng(71)
+    i64, i32 = C.c_int64, C.c_int
+    for (n, c, h, w, k, st, pd) in ((3, 5, 8, 12, 2, 2, 0), (2, 3, 9, 7, 3, 2, 1), (2, 2, 6, 6, 2, 1, 0), (4, 32, 28, 28, 2, 2, 0)):
+        x = r.standard_normal((n, c, h, w)).astype(np.float32)
+        x[r.random(x.shape) < 0.1] = 0.0   # exact zeros and all-negative windows exercise the first-maximum rule
+        ho, wo = (h + 2 * pd - k) // st + 1, (w + 2 * pd - k) // st + 1
+        g = r.standard_normal((n, c, ho, wo)).astype(np.float32)
+        dx_, dg = capi.to_device(x), capi.to_device(g)
+        args = (i64(n), i64(c), i64(h), i64(w), i32(k), i32(k), i32(st), i32(st), i32(pd), i32(pd))
+        # two ops
+        rl, y0, i0 = capi.empty(x.shape), capi.empty(g.shape), capi.empty(g.shape)
+        capi.call("unary", i32(UNARY["relu"]), dx_.ptr, rl.ptr, i64(x.size), C.c_float(0), C.c_float(0))
+        capi.call("max_pool2d", rl.ptr, *args, y0.ptr, i0.ptr)
+        dp, d0 = capi.empty(x.shape), capi.empty(x.shape)
+        capi.call("max_pool2d_backward", dg.ptr, i0.ptr, *args, dp.ptr)
+        capi.call("unary_backward", i32(UNARY["relu"]), dx_.ptr, dp.ptr, d0.ptr, i64(x.size), C.c_float(0), C.c_float(0))
+        # fused
+        y1, i1, d1 = capi.empty(g.shape), capi.empty(g.shape), capi.empty(x.shape)
+        capi.call("relu_max_pool2d", dx_.ptr, *args, y1.ptr, i1.ptr)
+        capi.call("relu_max_pool2d_backward", dx_.ptr, dg.ptr, i1.ptr, *args, d1.ptr)
+        assert np.array_equal(y1.numpy(), y0.numpy()) and np.array_equal(i1.numpy(), i0.numpy())
+        assert np.array_equal(d1.numpy(), d0.numpy())
+
+
+def test_fused_softmax_cross_entropy(capi):
+    r = rng(72)
+    for rows, classes in ((1, 1), (7, 10), (256, 10), (64, 65), (1000, 33)):
+        x = (3 * r.standard_normal((rows, classes))).astype(np.float32)
+        t = np.eye(classes, dtype=np.float32)[r.integers(0, classes, rows)]
+        t[0] = r.random(classes).astype(np.float32)   # a soft target row
+        gup = np.array([1.7], np.float32)
+        dx_, dt, dgu = capi.to_device(x), capi.to_device(t), capi.to_device(gup)
+        loss, dl, dtt = capi.empty((1,)), capi.empty(x.shape), capi.empty(x.shape)
+        capi.call("softmax_cross_entropy", dx_.ptr, dt.ptr, C.c_int64(rows), C.c_int64(classes), loss.ptr)
+        capi.call("softmax_cross_entropy_backward", dx_.ptr, dt.ptr, dgu.ptr, C.c_int64(rows), C.c_int64(classes), dl.ptr, dtt.ptr)
+        x64, t64 = x.astype(np.float64), t.astype(np.float64)
+        ls = x64 - x64.max(1, keepdims=True)
+        ls = ls - np.log(np.exp(ls).sum(1, keepdims=True))
+        assert_close(loss.numpy(), np.array([-(ls * t64).sum() / rows]), 1e-5, f"loss [{rows},{classes}]")
+        sc = -1.7 / rows
+        assert_close(dl.numpy(), sc * (t64 - np.exp(ls) * t64.sum(1, keepdims=True)), 1e-4, "dlogits", abs_floor=1e-7)
+        assert_close(dtt.numpy(), sc * ls, 1e-5, "dtargets")
+        capi.call("softmax_cross_entropy_backward", dx_.ptr, dt.ptr, dgu.ptr, C.c_int64(rows), C.c_int64(classes), dl.ptr, None)
+    with pytest.raises(RtError):
+        capi.call("softmax_cross_entropy", dx_.ptr, dt.ptr, C.c_int64(0), C.c_int64(5), loss.ptr)

@@ -21,8 +21,9 @@ SMALL = {
 FULL = {1: [64, 784, 128, 10], 3: [256, 28, 32, 64, 128, 10]}
 
 
-def run_reference_step(engine, config, dims, params, inputs, steps=1, conv_dx_correct=False):
-    tr = setup_trainer(engine, config, dims, params)
+def run_reference_step(engine, config, dims, params, inputs, steps=1, conv_dx_correct=False, variant=0):
+    # variant 100: the same network built from the fused forward ops (ops::fused_*)
+    tr = setup_trainer(engine, config + variant, dims, params)
     ins = [engine.tensor(a, requires_grad=(config == 4 and i == 0)) for i, a in enumerate(inputs)]
     losses = []
     if conv_dx_correct:
@@ -190,3 +191,26 @@ def test_pipelined_steps_equal_plain_steps(gpu_engine):
     assert got == ref
     for a, b in zip(plain.params, piped.params):
         assert np.array_equal(a.numpy(), b.numpy())
+
+
+@pytest.mark.parametrize("config", [1, 3, 4, 5])
+def test_fused_forward_ops_match_the_reference_chain(oracle_engine, gpu_engine, config):
+    """Configuration 100 + c builds network c from the fused forward ops (relu + max_pool2d in one kernel, the
+    classification loss in one kernel).  It must match the oracle running the reference's own chain of ops, to the
+    same tolerance as the unfused CUDA path, and max-pool routing must stay identical."""
+    dims = SMALL[config]
+    params, inputs = workload_data(config, dims, seed=9)
+    cpu = run_reference_step(oracle_engine, config, dims, params, inputs, steps=2, conv_dx_correct=config in (3, 4))
+    gpu = run_reference_step(gpu_engine, config, dims, params, inputs, steps=2, variant=100)
+    compare_runs(cpu, gpu, f"C{config} fused forward", lr=LR[config])
+
+
+def test_fused_forward_full_size_cnn(oracle_engine, gpu_engine):
+    dims = FULL[3]
+    params, inputs = workload_data(3, dims, seed=2)
+    cpu = run_reference_step(oracle_engine, 3, dims, params, inputs, steps=1, conv_dx_correct=True)
+    gpu = run_reference_step(gpu_engine, 3, dims, params, inputs, steps=1, variant=100)
+    assert_close(np.array(gpu["loss"]), np.array(cpu["loss"]), TOL, "loss")
+    for k in ("grads", "states"):
+        for i, (a, b) in enumerate(zip(cpu[k], gpu[k])):
+            assert_close(b, a, TOL, f"C3 fused full {k}[{i}]")
