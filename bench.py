@@ -258,6 +258,9 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fused-forward", action="store_true",
+                    help="build the network from the fused forward ops (relu + max_pool2d in one kernel, the classification loss "
+                         "in one kernel) instead of the reference's op sequence; same mathematics")
     ap.add_argument("--kernels-size", type=int, default=4096, help="rows = cols of the matrices of --kernels")
     ap.add_argument("--kernels", action="store_true",
                     help="print the bandwidth table of the HBM-bound kernels (one GPU) instead of the training-step line")
@@ -298,7 +301,10 @@ def main():
         dist.broadcast(idt, 0)
         nccl_id = idt.cpu().tolist()
 
-    tr = rt.DataParallelTrainer(config, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
+    trainer_config = config + (100 if args.fused_forward else 0)
+    if args.fused_forward:
+        desc += " [fused forward ops]"
+    tr = rt.DataParallelTrainer(trainer_config, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
     capi = rt.CApi(ctx=rt.context_handle())
     exchange = "one NCCL all-reduce of the flat gradients (N>1)"
     if world > 1 and os.environ.get("RT_B200_DP_FUSED", "0") == "1":
@@ -310,7 +316,7 @@ def main():
         else:
             print(f"[rank {rank}] peer-memory exchange unavailable ({getattr(tr, 'peer_error', 'another rank failed')}); using NCCL",
                   file=sys.stderr)
-            tr = rt.DataParallelTrainer(config, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
+            tr = rt.DataParallelTrainer(trainer_config, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
     params, inputs = workload_data(config, dims, seed=0, rank=rank)  # same weights on every rank, different data
     for t, p in zip(tr.params, params):
         t.update_from_host(p)
@@ -384,6 +390,26 @@ def main():
     code = C.c_int(0)
     capi.call("device_status", C.byref(code))  # raises if a bounded device-side wait (MMA pipeline, peer flags) expired
 
+    # The same network built from the fused forward ops (relu + max_pool2d and the classification loss as single
+    # kernels), timed the same way on device-resident inputs; reported beside the headline, which keeps the reference's
+    # own op sequence.
+    fused_line = None
+    if not args.fused_forward and config in (1, 3, 4, 5) and os.environ.get("RT_BENCH_SKIP_FUSED") != "1":
+        try:
+            tr2 = rt.DataParallelTrainer(config + 100, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
+            for t, p in zip(tr2.params, params):
+                t.update_from_host(p)
+            tr2.step(inputs)
+            tr2.last_loss()
+            for _ in range(args.warmup):
+                tr2.step(None)
+            ms2 = timed(lambda: tr2.step(None), args.steps)
+            fused_line = {"value": per_gpu * world * args.steps / (ms2 * 1e-3), "unit": "samples/s", "ms_per_step": ms2 / args.steps,
+                          "note": "same network from the fused forward ops (ops::fused_relu_max_pool2d, ops::fused_softmax_nll)"}
+            del tr2
+        except Exception as e:  # noqa: BLE001  (the headline above does not depend on this extra measurement)
+            fused_line = {"unavailable": str(e)}
+
     if rank == 0:
         pk = peaks()
         res, in_use, nalloc = C.c_int64(0), C.c_int64(0), C.c_int64(0)
@@ -408,6 +434,8 @@ def main():
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(gpu_launches), "final_loss": loss, "clocks": clocks,
         }
+        if fused_line:
+            line["fused_forward"] = fused_line
         if roof:
             line["roofline"] = roof
         if cpu:
