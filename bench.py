@@ -259,7 +259,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--fused-forward", action="store_true",
-                    help="build the network from the fused forward ops (relu + max_pool2d in one kernel, the classification loss "
+                    help="build the network from the fused forward ops (relu + max_pool2d in one kernel, the LSTM cell in two, the classification loss "
                          "in one kernel) instead of the reference's op sequence; same mathematics")
     ap.add_argument("--kernels-size", type=int, default=4096, help="rows = cols of the matrices of --kernels")
     ap.add_argument("--kernels", action="store_true",
@@ -405,7 +405,7 @@ def main():
                 tr2.step(None)
             ms2 = timed(lambda: tr2.step(None), args.steps)
             fused_line = {"value": per_gpu * world * args.steps / (ms2 * 1e-3), "unit": "samples/s", "ms_per_step": ms2 / args.steps,
-                          "note": "same network from the fused forward ops (ops::fused_relu_max_pool2d, ops::fused_softmax_nll)"}
+                          "note": "same network from the fused forward ops (ops::fused_relu_max_pool2d, ops::fused_softmax_nll, ops::fused_lstm_cell_c/_h)"}
             del tr2
         except Exception as e:  # noqa: BLE001  (the headline above does not depend on this extra measurement)
             fused_line = {"unavailable": str(e)}

@@ -192,6 +192,17 @@ rt_status rt_log_softmax(rt_ctx* ctx, const float* x, int64_t outer, int64_t len
 rt_status rt_log_softmax_backward(rt_ctx* ctx, const float* x, const float* g, int64_t outer, int64_t len,
                                   int64_t inner, float* dx);
 
+/* Fused LSTM cell update (no counterpart in the reference, whose char-LSTM example builds the cell from slice, sigmoid, tanh,
+ * mul and add ops: examples/lstm_char_rnn_cpu.rs).  gates is [batch, 4*hidden] with column blocks (input, forget, candidate,
+ * output); c = sigmoid(f)*c_prev + sigmoid(i)*tanh(g); h = sigmoid(o)*tanh(c).  Each backward writes a full [batch, 4*hidden]
+ * gradient for gates (zeros in the blocks it does not touch); gradient outputs may be NULL. */
+rt_status rt_lstm_cell_c(rt_ctx* ctx, const float* gates, const float* c_prev, int64_t batch, int64_t hidden, float* c);
+rt_status rt_lstm_cell_c_backward(rt_ctx* ctx, const float* gates, const float* c_prev, const float* dc, int64_t batch,
+                                  int64_t hidden, float* dgates, float* dc_prev);
+rt_status rt_lstm_cell_h(rt_ctx* ctx, const float* gates, const float* c, int64_t batch, int64_t hidden, float* h);
+rt_status rt_lstm_cell_h_backward(rt_ctx* ctx, const float* gates, const float* c, const float* dh, int64_t batch,
+                                  int64_t hidden, float* dgates, float* dc);
+
 /* Fused classification loss (no counterpart in the reference, whose examples spell the chain out:
  * examples/train_mnist_cpu.rs:63-97): loss[0] = -(1/rows) * sum over rows and classes of targets * log_softmax(logits).
  * Backward: dlogits = -(g/rows) * (targets - softmax(logits) * sum_k targets), dtargets = -(g/rows) * log_softmax(logits);

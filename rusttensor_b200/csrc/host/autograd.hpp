@@ -99,7 +99,7 @@ struct OpType {
     Sigmoid, Sqrt, Tanh, Softplus, Max, Min, Prod, LogSumExp, ArgMax, ArgMin, Powf, Square,
     Maximum, Minimum, Elu, Transpose, Sin, Cos, Tan, Conv2d, MaxPool2D, Conv2DTranspose, Slice,
     Concat, ExpandDims, Squeeze, Clip, DivScalar, MulScalar,
-    FusedReluMaxPool2D, FusedSoftmaxNll  // fused forward ops added beside the reference's (ops::fused_*)
+    FusedReluMaxPool2D, FusedSoftmaxNll, FusedLstmCellC, FusedLstmCellH  // fused forward ops added beside the reference's (ops::fused_*)
   } kind;
   std::optional<size_t> axis;          // Mean/Sum/Max/Min/Prod/LogSumExp(Option), LogSoftmax/ArgMax/...
   float scalar = 0.f;                  // Elu(alpha), MulScalar, DivScalar
@@ -119,7 +119,7 @@ struct OpType {
       "Div", "Exp", "Ln", "Broadcast", "View", "Abs", "Sigmoid", "Sqrt", "Tanh", "Softplus", "Max",
       "Min", "Prod", "LogSumExp", "ArgMax", "ArgMin", "Powf", "Square", "Maximum", "Minimum", "Elu",
       "Transpose", "Sin", "Cos", "Tan", "Conv2d", "MaxPool2D", "Conv2DTranspose", "Slice", "Concat",
-      "ExpandDims", "Squeeze", "Clip", "DivScalar", "MulScalar", "FusedReluMaxPool2D", "FusedSoftmaxNll"};
+      "ExpandDims", "Squeeze", "Clip", "DivScalar", "MulScalar", "FusedReluMaxPool2D", "FusedSoftmaxNll", "FusedLstmCellC", "FusedLstmCellH"};
     return n[(int)kind];
   }
 };
@@ -842,6 +842,58 @@ Tensor<B> fused_softmax_nll(const Tensor<B>& logits, const Tensor<B>& targets) {
     if (rg) {
       t.set_op(Op<B>(OpType(OpType::FusedSoftmaxNll), {logits, targets}, [](const Op<B>& op, const St<B>& g) {
         auto p = B::softmax_nll_backward(op, g);
+        return Grads<B>{std::move(p.first), std::move(p.second)};
+      }));
+    }
+    return t;
+  }
+}
+
+// LSTM cell update from the pre-activation gates [B, 4H] (column blocks: input, forget, candidate, output), as the
+// reference's char-LSTM example spells it with slices (examples/lstm_char_rnn_cpu.rs):
+//   c = sigmoid(f) * c_prev + sigmoid(i) * tanh(g)
+template <class B>
+Tensor<B> fused_lstm_cell_c(const Tensor<B>& gates, const Tensor<B>& c_prev) {
+  const Shape& gs = gates.shape();
+  if (gs.size() != 2 || c_prev.shape().size() != 2 || gs[0] != c_prev.shape()[0] || gs[1] != 4 * c_prev.shape()[1])
+    throw Error::incompatible("fused_lstm_cell_c", gs, c_prev.shape());
+  const size_t Bn = gs[0], H = c_prev.shape()[1];
+  if constexpr (!HasFusedForward<B>::value) {
+    Tensor<B> ig = sigmoid(slice(gates, {{0, Bn}, {0, H}}));
+    Tensor<B> fg = sigmoid(slice(gates, {{0, Bn}, {H, 2 * H}}));
+    Tensor<B> gg = tanh(slice(gates, {{0, Bn}, {2 * H, 3 * H}}));
+    return add(mul(fg, c_prev), mul(ig, gg));
+  } else {
+    St<B> out = B::lstm_cell_c(gates.data(), c_prev.data());
+    bool rg = gates.requires_grad() || c_prev.requires_grad();
+    Tensor<B> t(std::move(out), rg);
+    if (rg) {
+      t.set_op(Op<B>(OpType(OpType::FusedLstmCellC), {gates, c_prev}, [](const Op<B>& op, const St<B>& g) {
+        auto p = B::lstm_cell_c_backward(op, g);
+        return Grads<B>{std::move(p.first), std::move(p.second)};
+      }));
+    }
+    return t;
+  }
+}
+
+//   h = sigmoid(o) * tanh(c)
+template <class B>
+Tensor<B> fused_lstm_cell_h(const Tensor<B>& gates, const Tensor<B>& c) {
+  const Shape& gs = gates.shape();
+  if (gs.size() != 2 || c.shape().size() != 2 || gs[0] != c.shape()[0] || gs[1] != 4 * c.shape()[1])
+    throw Error::incompatible("fused_lstm_cell_h", gs, c.shape());
+  const size_t Bn = gs[0], H = c.shape()[1];
+  if constexpr (!HasFusedForward<B>::value) {
+    Tensor<B> og = sigmoid(slice(gates, {{0, Bn}, {3 * H, 4 * H}}));
+    return mul(og, tanh(c));
+  } else {
+    St<B> out = B::lstm_cell_h(gates.data(), c.data());
+    bool rg = gates.requires_grad() || c.requires_grad();
+    Tensor<B> t(std::move(out), rg);
+    if (rg) {
+      t.set_op(Op<B>(OpType(OpType::FusedLstmCellH), {gates, c}, [](const Op<B>& op, const St<B>& g) {
+        auto p = B::lstm_cell_h_backward(op, g);
         return Grads<B>{std::move(p.first), std::move(p.second)};
       }));
     }

@@ -610,6 +610,39 @@ struct B200Backend {
     return {std::move(dl), std::move(dt)};
   }
 
+  static Storage lstm_cell_c(const Storage& gates, const Storage& c_prev) {
+    Storage c = alloc(c_prev.shape);
+    check(rt_lstm_cell_c(ctx(), gates.ptr(), c_prev.ptr(), (int64_t)c_prev.shape[0], (int64_t)c_prev.shape[1], c.ptr()));
+    return c;
+  }
+  static std::pair<Storage, Storage> lstm_cell_c_backward(const OpB& o, const Storage& g) {
+    const Storage& gates = o.inputs[0].data();
+    const Storage& c_prev = o.inputs[1].data();
+    if (g.shape != c_prev.shape) throw Error::shape_mismatch(c_prev.shape, g.shape);
+    const bool ng = o.inputs[0].requires_grad(), nc = o.inputs[1].requires_grad();
+    Storage dg = ng ? alloc(gates.shape) : unused_grad(gates.shape);
+    Storage dc = nc ? alloc(c_prev.shape) : unused_grad(c_prev.shape);
+    check(rt_lstm_cell_c_backward(ctx(), gates.ptr(), c_prev.ptr(), g.ptr(), (int64_t)c_prev.shape[0], (int64_t)c_prev.shape[1],
+                                  ng ? dg.ptr() : nullptr, nc ? dc.ptr() : nullptr));
+    return {std::move(dg), std::move(dc)};
+  }
+  static Storage lstm_cell_h(const Storage& gates, const Storage& c) {
+    Storage h = alloc(c.shape);
+    check(rt_lstm_cell_h(ctx(), gates.ptr(), c.ptr(), (int64_t)c.shape[0], (int64_t)c.shape[1], h.ptr()));
+    return h;
+  }
+  static std::pair<Storage, Storage> lstm_cell_h_backward(const OpB& o, const Storage& g) {
+    const Storage& gates = o.inputs[0].data();
+    const Storage& c = o.inputs[1].data();
+    if (g.shape != c.shape) throw Error::shape_mismatch(c.shape, g.shape);
+    const bool ng = o.inputs[0].requires_grad(), nc = o.inputs[1].requires_grad();
+    Storage dg = ng ? alloc(gates.shape) : unused_grad(gates.shape);
+    Storage dc = nc ? alloc(c.shape) : unused_grad(c.shape);
+    check(rt_lstm_cell_h_backward(ctx(), gates.ptr(), c.ptr(), g.ptr(), (int64_t)c.shape[0], (int64_t)c.shape[1],
+                                  ng ? dg.ptr() : nullptr, nc ? dc.ptr() : nullptr));
+    return {std::move(dg), std::move(dc)};
+  }
+
   // ---- optimizer steps (mod.rs:18-36, 256-272) ---------------------------------------------------
   static void sgd_step(Storage& w, const Storage& dw, float lr) {
     if (w.shape != dw.shape) throw Error::shape_mismatch(w.shape, dw.shape);

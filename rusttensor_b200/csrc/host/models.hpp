@@ -192,12 +192,17 @@ Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
         Tensor<B> y_t = ops::slice(in.at(1), {{t * Bn, (t + 1) * Bn}, {0, V}});
         Tensor<B> xh = ops::concat<B>({x_t, h}, 1);
         Tensor<B> gates = linear(xh, p[0], p[1]);
-        Tensor<B> ig = ops::sigmoid(ops::slice(gates, {{0, Bn}, {0, H}}));
-        Tensor<B> fg = ops::sigmoid(ops::slice(gates, {{0, Bn}, {H, 2 * H}}));
-        Tensor<B> gg = ops::tanh(ops::slice(gates, {{0, Bn}, {2 * H, 3 * H}}));
-        Tensor<B> og = ops::sigmoid(ops::slice(gates, {{0, Bn}, {3 * H, 4 * H}}));
-        c = ops::add(ops::mul(fg, c), ops::mul(ig, gg));
-        h = ops::mul(og, ops::tanh(c));
+        if (w.fused_forward) {
+          c = ops::fused_lstm_cell_c(gates, c);
+          h = ops::fused_lstm_cell_h(gates, c);
+        } else {
+          Tensor<B> ig = ops::sigmoid(ops::slice(gates, {{0, Bn}, {0, H}}));
+          Tensor<B> fg = ops::sigmoid(ops::slice(gates, {{0, Bn}, {H, 2 * H}}));
+          Tensor<B> gg = ops::tanh(ops::slice(gates, {{0, Bn}, {2 * H, 3 * H}}));
+          Tensor<B> og = ops::sigmoid(ops::slice(gates, {{0, Bn}, {3 * H, 4 * H}}));
+          c = ops::add(ops::mul(fg, c), ops::mul(ig, gg));
+          h = ops::mul(og, ops::tanh(c));
+        }
         Tensor<B> logits = linear(h, p[2], p[3]);
         Tensor<B> l = w.fused_forward ? ops::fused_softmax_nll(logits, y_t) : ops::softmax_cross_entropy(logits, y_t, 1, Reduction::Mean);
         total = t == 0 ? l : ops::add(total, l);

@@ -250,3 +250,40 @@ def test_fused_softmax_cross_entropy(capi):
         capi.call("softmax_cross_entropy_backward", dx_.ptr, dt.ptr, dgu.ptr, C.c_int64(rows), C.c_int64(classes), dl.ptr, None)
     with pytest.raises(RtError):
         capi.call("softmax_cross_entropy", dx_.ptr, dt.ptr, C.c_int64(0), C.c_int64(5), loss.ptr)
+
+
+def test_fused_lstm_cell(capi):
+    r = rng(73)
+    sig = lambda v: 1.0 / (1.0 + np.exp(-v))
+    for batch, hidden in ((1, 1), (3, 5), (64, 128), (7, 33)):
+        gates = (2 * r.standard_normal((batch, 4 * hidden))).astype(np.float32)
+        cp = r.standard_normal((batch, hidden)).astype(np.float32)
+        up = r.standard_normal((batch, hidden)).astype(np.float32)
+        dg_, dcp, dup = capi.to_device(gates), capi.to_device(cp), capi.to_device(up)
+        dims = (C.c_int64(batch), C.c_int64(hidden))
+        g64 = gates.astype(np.float64)
+        i, f, g, o = (g64[:, k * hidden:(k + 1) * hidden] for k in range(4))
+        si, sf, tg, so = sig(i), sig(f), np.tanh(g), sig(o)
+        # c = sigmoid(f) * c_prev + sigmoid(i) * tanh(g)
+        c, dgates, dprev = capi.empty(cp.shape), capi.empty(gates.shape), capi.empty(cp.shape)
+        capi.call("lstm_cell_c", dg_.ptr, dcp.ptr, *dims, c.ptr)
+        capi.call("lstm_cell_c_backward", dg_.ptr, dcp.ptr, dup.ptr, *dims, dgates.ptr, dprev.ptr)
+        c64 = sf * cp + si * tg
+        assert_close(c.numpy(), c64, 1e-5, f"c [{batch},{hidden}]", abs_floor=1e-6)
+        want = np.concatenate([up * tg * si * (1 - si), up * cp * sf * (1 - sf), up * si * (1 - tg * tg), np.zeros_like(c64)], axis=1)
+        assert_close(dgates.numpy(), want, 1e-4, "c: dgates", abs_floor=1e-6)
+        assert_close(dprev.numpy(), up * sf, 1e-5, "c: dc_prev", abs_floor=1e-6)
+        capi.call("lstm_cell_c_backward", dg_.ptr, dcp.ptr, dup.ptr, *dims, None, dprev.ptr)
+        capi.call("lstm_cell_c_backward", dg_.ptr, dcp.ptr, dup.ptr, *dims, dgates.ptr, None)
+        # h = sigmoid(o) * tanh(c)
+        h, dgates2, dc = capi.empty(cp.shape), capi.empty(gates.shape), capi.empty(cp.shape)
+        capi.call("lstm_cell_h", dg_.ptr, c.ptr, *dims, h.ptr)
+        capi.call("lstm_cell_h_backward", dg_.ptr, c.ptr, dup.ptr, *dims, dgates2.ptr, dc.ptr)
+        tc = np.tanh(c.numpy().astype(np.float64))
+        assert_close(h.numpy(), so * tc, 1e-5, "h", abs_floor=1e-6)
+        want = np.concatenate([np.zeros((batch, 3 * hidden)), up * tc * so * (1 - so)], axis=1)
+        assert_close(dgates2.numpy(), want, 1e-4, "h: dgates", abs_floor=1e-6)
+        assert_close(dc.numpy(), up * so * (1 - tc * tc), 1e-4, "h: dc", abs_floor=1e-6)
+    capi.call("lstm_cell_c", dg_.ptr, dcp.ptr, C.c_int64(0), C.c_int64(4), c.ptr)   # empty batch: nothing to do
+    with pytest.raises(RtError):
+        capi.call("lstm_cell_h", dg_.ptr, dcp.ptr, C.c_int64(-1), C.c_int64(4), h.ptr)
