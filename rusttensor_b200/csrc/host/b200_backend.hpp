@@ -171,10 +171,23 @@ struct B200Backend {
   static Storage greater_equal(const Storage& a, const Storage& b) { return binary(RT_GREATER_EQUAL, a, b, "greater_equal"); }
   static Storage less(const Storage& a, const Storage& b) { return binary(RT_LESS, a, b, "less"); }
   static Storage less_equal(const Storage& a, const Storage& b) { return binary(RT_LESS_EQUAL, a, b, "less_equal"); }
+  // true when `small` (rank <= rank of `full`, no empty axis) broadcasts onto `full` by stretching 1s only
+  static bool stretches_onto(const Shape& small, const Shape& full) {
+    if (small.size() > full.size()) return false;
+    const size_t off = full.size() - small.size();
+    for (size_t i = 0; i < small.size(); ++i)
+      if (small[i] != full[i + off] && small[i] != 1) return false;
+    return true;
+  }
   static std::pair<Storage, Storage> mul_backward(const OpB& o, const Storage& g) { return binary_bwd(RT_MUL, o, g, "mul"); }
   static std::pair<Storage, Storage> add_backward(const OpB& o, const Storage& g) {
     // same-shape add: both gradients are the upstream gradient itself (no copy)
     if (o.inputs.size() == 2 && o.inputs[0].data().shape == g.shape && o.inputs[1].data().shape == g.shape) return {g, g};
+    // full-shape a + broadcast b (a bias): da is the upstream gradient itself, db its sum over the stretched axes
+    if (o.inputs.size() == 2 && o.inputs[0].data().shape == g.shape && g.numel() > 0 && stretches_onto(o.inputs[1].data().shape, g.shape)) {
+      const Shape& bs = o.inputs[1].data().shape;
+      return {g, o.inputs[1].requires_grad() ? unbroadcast(g, bs) : unused_grad(bs)};
+    }
     return binary_bwd(RT_ADD, o, g, "add");
   }
   static std::pair<Storage, Storage> sub_backward(const OpB& o, const Storage& g) { return binary_bwd(RT_SUB, o, g, "sub"); }

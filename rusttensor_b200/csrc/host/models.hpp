@@ -126,9 +126,12 @@ Tensor<B> nll_loss(const Tensor<B>& log_probs, const Tensor<B>& y) {
   return ops::mul(m, minus_one);
 }
 
+// x·w + b as the examples write it: the bias is broadcast to [batch, out] by its own op and then added.  With
+// `direct_bias` the add broadcasts the bias itself (operator broadcasting, src/ops/mod.rs add), one kernel fewer.
 template <class B>
-Tensor<B> linear(const Tensor<B>& x, const Tensor<B>& w, const Tensor<B>& b) {
+Tensor<B> linear(const Tensor<B>& x, const Tensor<B>& w, const Tensor<B>& b, bool direct_bias = false) {
   Tensor<B> h = ops::matmul(x, w);
+  if (direct_bias) return ops::add(h, b);
   return ops::add(h, b.broadcast_to({x.shape()[0], w.shape()[1]}));
 }
 
@@ -145,8 +148,8 @@ Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
   };
   switch (w.config) {
     case C1_MLP: {
-      Tensor<B> h = ops::relu(linear(in.at(0), p[0], p[1]));
-      Tensor<B> logits = linear(h, p[2], p[3]);
+      Tensor<B> h = ops::relu(linear(in.at(0), p[0], p[1], w.fused_forward));
+      Tensor<B> logits = linear(h, p[2], p[3], w.fused_forward);
       if (w.fused_forward) return ops::fused_softmax_nll(logits, in.at(1));
       return nll_loss(ops::log_softmax(logits, 1), in.at(1));
     }
@@ -172,8 +175,8 @@ Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
       Tensor<B> c2 = ops::conv2d(p1, p[2], &p[3], {1, 1}, {1, 1});
       Tensor<B> p2 = relu_pool(c2);
       Tensor<B> flat = p2.view({n, p[4].shape()[0]});
-      Tensor<B> f1 = ops::relu(linear(flat, p[4], p[5]));
-      Tensor<B> logits = linear(f1, p[6], p[7]);
+      Tensor<B> f1 = ops::relu(linear(flat, p[4], p[5], w.fused_forward));
+      Tensor<B> logits = linear(f1, p[6], p[7], w.fused_forward);
       if (w.fused_forward) return ops::fused_softmax_nll(logits, in.at(1));
       return ops::softmax_cross_entropy(logits, in.at(1), 1, Reduction::Mean);
     }
@@ -191,7 +194,7 @@ Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
         Tensor<B> x_t = ops::slice(in.at(0), {{t * Bn, (t + 1) * Bn}, {0, V}});
         Tensor<B> y_t = ops::slice(in.at(1), {{t * Bn, (t + 1) * Bn}, {0, V}});
         Tensor<B> xh = ops::concat<B>({x_t, h}, 1);
-        Tensor<B> gates = linear(xh, p[0], p[1]);
+        Tensor<B> gates = linear(xh, p[0], p[1], w.fused_forward);
         if (w.fused_forward) {
           c = ops::fused_lstm_cell_c(gates, c);
           h = ops::fused_lstm_cell_h(gates, c);
@@ -203,7 +206,7 @@ Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
           c = ops::add(ops::mul(fg, c), ops::mul(ig, gg));
           h = ops::mul(og, ops::tanh(c));
         }
-        Tensor<B> logits = linear(h, p[2], p[3]);
+        Tensor<B> logits = linear(h, p[2], p[3], w.fused_forward);
         Tensor<B> l = w.fused_forward ? ops::fused_softmax_nll(logits, y_t) : ops::softmax_cross_entropy(logits, y_t, 1, Reduction::Mean);
         total = t == 0 ? l : ops::add(total, l);
       }

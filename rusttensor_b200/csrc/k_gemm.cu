@@ -342,6 +342,123 @@ rt_status gemm_plain(rt_ctx* ctx, const LA& la, const LB& lb, float* c, int64_t 
   return rt_sum_axis_internal(ctx, ws.as<float>(), 1, splits, M * N, c, 1.f);
 }
 
+// ---- narrow products -------------------------------------------------------------------------------------------
+// A classifier head (N <= 16 output columns) or its input gradient (K <= 16) gives a tile kernel one or two CTAs that
+// walk K serially; these two kernels spread the same arithmetic over the block instead.
+constexpr int kSkinnyN = 16, kSkinnyRows = 32, kSkinnyKC = 128, kSkinnySlices = 8;
+
+// C[M, N<=16] = A x B.  A block owns 32 rows of C: A and B chunks of 128 k are staged in shared memory with coalesced
+// loads whatever the storage order, thread (row, slice) accumulates every 8th k, the 8 slices are added in a fixed order.
+template <bool TA, bool TB>
+__global__ void __launch_bounds__(kSkinnyRows * kSkinnySlices)
+gemm_skinny_n_kernel(const float* __restrict__ a, int64_t lda, const float* __restrict__ b, int64_t ldb, float* __restrict__ c,
+                     int64_t ldc, int M, int N, int K, int accumulate) {
+  constexpr int T = kSkinnyRows * kSkinnySlices;
+  __shared__ float As[kSkinnyRows][kSkinnyKC + 1];
+  __shared__ __align__(16) float Bs[kSkinnyKC][kSkinnyN];
+  __shared__ float red[kSkinnySlices][kSkinnyRows][kSkinnyN + 1];
+  const int tid = threadIdx.x, ml = tid & 31, ks = tid >> 5;
+  const int m0 = blockIdx.x * kSkinnyRows;
+  float acc[kSkinnyN];
+#pragma unroll
+  for (int j = 0; j < kSkinnyN; ++j) acc[j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += kSkinnyKC) {
+#pragma unroll 4
+    for (int i = tid; i < kSkinnyRows * kSkinnyKC; i += T) {
+      int mm, kk;
+      if (TA) { mm = i % kSkinnyRows; kk = i / kSkinnyRows; } else { kk = i % kSkinnyKC; mm = i / kSkinnyKC; }
+      const bool in = m0 + mm < M && k0 + kk < K;
+      const int64_t off = TA ? (int64_t)(k0 + kk) * lda + m0 + mm : (int64_t)(m0 + mm) * lda + k0 + kk;
+      As[mm][kk] = in ? __ldg(a + off) : 0.f;
+    }
+#pragma unroll 4
+    for (int i = tid; i < kSkinnyKC * kSkinnyN; i += T) {
+      int j, kk;
+      if (TB) { kk = i % kSkinnyKC; j = i / kSkinnyKC; } else { j = i % kSkinnyN; kk = i / kSkinnyN; }
+      const bool in = j < N && k0 + kk < K;
+      const int64_t off = TB ? (int64_t)j * ldb + k0 + kk : (int64_t)(k0 + kk) * ldb + j;
+      Bs[kk][j] = in ? __ldg(b + off) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int kk = ks; kk < kSkinnyKC; kk += kSkinnySlices) {
+      const float av = As[ml][kk];
+      const float4* br = reinterpret_cast<const float4*>(&Bs[kk][0]);
+#pragma unroll
+      for (int q = 0; q < kSkinnyN / 4; ++q) {
+        const float4 bv = br[q];
+        acc[q * 4 + 0] = fmaf(av, bv.x, acc[q * 4 + 0]);
+        acc[q * 4 + 1] = fmaf(av, bv.y, acc[q * 4 + 1]);
+        acc[q * 4 + 2] = fmaf(av, bv.z, acc[q * 4 + 2]);
+        acc[q * 4 + 3] = fmaf(av, bv.w, acc[q * 4 + 3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int j = 0; j < kSkinnyN; ++j) red[ks][ml][j] = acc[j];
+  __syncthreads();
+  for (int o = tid; o < kSkinnyRows * kSkinnyN; o += T) {
+    const int mm = o / kSkinnyN, j = o % kSkinnyN;
+    if (m0 + mm >= M || j >= N) continue;
+    float v = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < kSkinnySlices; ++s2) v += red[s2][mm][j];
+    float* dst = c + (int64_t)(m0 + mm) * ldc + j;
+    *dst = accumulate ? *dst + v : v;
+  }
+}
+
+// C[M, N] = A x B for K <= 16: one thread per output element, B (K x N, a few KB) read through the cache.
+template <bool TA, bool TB>
+__global__ void __launch_bounds__(256) gemm_small_k_kernel(const float* __restrict__ a, int64_t lda, const float* __restrict__ b,
+                                                           int64_t ldb, float* __restrict__ c, int64_t ldc, int64_t MN, int N, int K,
+                                                           int accumulate) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < MN; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i = e / N;
+    const int j = (int)(e - i * N);
+    float av[16], bv[16];
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      av[kk] = kk < K ? __ldg(a + (TA ? (int64_t)kk * lda + i : i * lda + kk)) : 0.f;
+      bv[kk] = kk < K ? __ldg(b + (TB ? (int64_t)j * ldb + kk : (int64_t)kk * ldb + j)) : 0.f;
+    }
+    float v = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) v = fmaf(av[kk], bv[kk], v);
+    float* dst = c + i * ldc + j;
+    *dst = accumulate ? *dst + v : v;
+  }
+}
+
+template <bool TA, bool TB>
+rt_status gemm_narrow_launch(rt_ctx* ctx, int64_t m, int64_t n, int64_t k, const float* a, int64_t lda, const float* b,
+                             int64_t ldb, float* c, int64_t ldc, int accumulate) {
+  if (k <= 16) {
+    gemm_small_k_kernel<TA, TB><<<rt_grid_for(ctx, m * n, 256), 256, 0, ctx->stream>>>(a, lda, b, ldb, c, ldc, m * n, (int)n,
+                                                                                      (int)k, accumulate);
+  } else {
+    const int grid = (int)((m + kSkinnyRows - 1) / kSkinnyRows);
+    gemm_skinny_n_kernel<TA, TB><<<grid, kSkinnyRows * kSkinnySlices, 0, ctx->stream>>>(a, lda, b, ldb, c, ldc, (int)m, (int)n,
+                                                                                        (int)k, accumulate);
+  }
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+// Narrow products (K <= 16, or N <= 16 with a K one block can walk); RT_ERR_UNIMPLEMENTED for everything else.
+rt_status gemm_narrow(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, int64_t n, int64_t k, const float* a, int64_t lda,
+                      const float* b, int64_t ldb, float* c, int64_t ldc, int accumulate) {
+  if (k < 1 || m >= (1ll << 31) || n >= (1ll << 31) || m * n >= (1ll << 40)) return RT_ERR_UNIMPLEMENTED;
+  const bool small_k = k <= 16;
+  const bool skinny_n = n <= kSkinnyN && (k <= 4096 || m >= 4096) && k < (1ll << 30) && m < (1ll << 30);
+  if (!small_k && !skinny_n) return RT_ERR_UNIMPLEMENTED;
+  if (!trans_a && !trans_b) return gemm_narrow_launch<false, false>(ctx, m, n, k, a, lda, b, ldb, c, ldc, accumulate);
+  if (!trans_a && trans_b) return gemm_narrow_launch<false, true>(ctx, m, n, k, a, lda, b, ldb, c, ldc, accumulate);
+  if (trans_a && !trans_b) return gemm_narrow_launch<true, false>(ctx, m, n, k, a, lda, b, ldb, c, ldc, accumulate);
+  return gemm_narrow_launch<true, true>(ctx, m, n, k, a, lda, b, ldb, c, ldc, accumulate);
+}
+
 rt_status check_conv_args(rt_ctx* ctx, int64_t n, int64_t cin, int64_t h, int64_t w, int64_t cout, int kh, int kw, int sh,
                           int sw, int ph, int pw) {
   if (n < 0 || cin < 0 || h < 0 || w < 0 || cout < 0) RT_FAIL(ctx, RT_ERR_INVALID_INDEX, "conv: negative extent");
@@ -441,6 +558,10 @@ rt_status rt_gemm(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, int64_t n, i
   if (lda < (trans_a ? m : k) || ldb < (trans_b ? k : n) || ldc < n)
     RT_FAIL(ctx, RT_ERR_SHAPE_MISMATCH, "rt_gemm: leading dimension smaller than the row length");
   bool acc = accumulate != 0;
+  if (ctx->use_tensor_cores) {  // narrow products: dedicated FP32 kernels
+    rt_status st = gemm_narrow(ctx, trans_a, trans_b, m, n, k, a, lda, b, ldb, c, ldc, accumulate);
+    if (st != RT_ERR_UNIMPLEMENTED) return st;
+  }
   if (ctx->use_tensor_cores && k >= 32 && m >= 32 && n >= 16 && m * n * k >= (1ll << 20)) {
     rt_status st = rt_gemm_tc_internal(ctx, trans_a, trans_b, m, n, k, a, lda, b, ldb, c, ldc, accumulate);
     if (st != RT_ERR_UNIMPLEMENTED) return st;

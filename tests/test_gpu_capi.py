@@ -110,6 +110,32 @@ def test_gemm_transposes_ld_and_accumulate(capi):
     assert_close(out.numpy(), a.astype(np.float64).T @ g.astype(np.float64), 1e-4, "split-K gemm")
 
 
+def test_gemm_narrow_products(capi):
+    """Classifier-head shapes (N <= 16) and their input gradients (K <= 16) take dedicated kernels: every storage
+    order, padded leading dimensions, accumulate, ragged extents around the 32-row / 128-k tiles."""
+    r = rng(74)
+    shapes = [(256, 10, 128), (128, 10, 256), (256, 128, 10), (1, 1, 1), (33, 16, 129), (31, 3, 4097), (5000, 7, 40),
+              (65, 200, 16), (3, 2, 5)]
+    for (m, n, k) in shapes:
+        for ta in (0, 1):
+            for tb in (0, 1):
+                for acc in (0, 1):
+                    pad_a, pad_b, pad_c = 3, 2, 5
+                    a = r.standard_normal((k, m + pad_a) if ta else (m, k + pad_a)).astype(np.float32)
+                    b = r.standard_normal((n, k + pad_b) if tb else (k, n + pad_b)).astype(np.float32)
+                    c0 = r.standard_normal((m, n + pad_c)).astype(np.float32)
+                    dc = capi.to_device(c0)
+                    capi.call("gemm", C.c_int(ta), C.c_int(tb), C.c_int64(m), C.c_int64(n), C.c_int64(k), capi.to_device(a).ptr,
+                              C.c_int64(a.shape[1]), capi.to_device(b).ptr, C.c_int64(b.shape[1]), dc.ptr, C.c_int64(n + pad_c),
+                              C.c_int(acc))
+                    A = (a[:, :m].T if ta else a[:, :k]).astype(np.float64)
+                    B = (b[:, :k].T if tb else b[:, :n]).astype(np.float64)
+                    want = c0.astype(np.float64)
+                    want[:, :n] = (want[:, :n] if acc else 0.0) + A @ B
+                    assert_close(dc.numpy(), want, 1e-4, f"narrow gemm {m}x{n}x{k} ta={ta} tb={tb} acc={acc}")
+                    assert np.array_equal(dc.numpy()[:, n:], c0[:, n:]), "padding columns of C were written"
+
+
 def test_optimizer_multi_matches_per_tensor(capi):
     r = rng(67)
     sizes = [1, 7, 4096, 5000, 33]
