@@ -363,21 +363,36 @@ gemm_skinny_n_kernel(const float* __restrict__ a, int64_t lda, const float* __re
 #pragma unroll
   for (int j = 0; j < kSkinnyN; ++j) acc[j] = 0.f;
   for (int k0 = 0; k0 < K; k0 += kSkinnyKC) {
-#pragma unroll 4
-    for (int i = tid; i < kSkinnyRows * kSkinnyKC; i += T) {
+    // all loads of the chunk are issued before the first store, so the chunk costs one memory round trip
+    constexpr int kALoads = kSkinnyRows * kSkinnyKC / T, kBLoads = kSkinnyKC * kSkinnyN / T;
+    float ar[kALoads], br_[kBLoads];
+#pragma unroll
+    for (int u = 0; u < kALoads; ++u) {
+      const int i = tid + u * T;
       int mm, kk;
       if (TA) { mm = i % kSkinnyRows; kk = i / kSkinnyRows; } else { kk = i % kSkinnyKC; mm = i / kSkinnyKC; }
       const bool in = m0 + mm < M && k0 + kk < K;
       const int64_t off = TA ? (int64_t)(k0 + kk) * lda + m0 + mm : (int64_t)(m0 + mm) * lda + k0 + kk;
-      As[mm][kk] = in ? __ldg(a + off) : 0.f;
+      ar[u] = in ? __ldg(a + off) : 0.f;
     }
-#pragma unroll 4
-    for (int i = tid; i < kSkinnyKC * kSkinnyN; i += T) {
+#pragma unroll
+    for (int u = 0; u < kBLoads; ++u) {
+      const int i = tid + u * T;
       int j, kk;
       if (TB) { kk = i % kSkinnyKC; j = i / kSkinnyKC; } else { j = i % kSkinnyN; kk = i / kSkinnyN; }
       const bool in = j < N && k0 + kk < K;
       const int64_t off = TB ? (int64_t)j * ldb + k0 + kk : (int64_t)(k0 + kk) * ldb + j;
-      Bs[kk][j] = in ? __ldg(b + off) : 0.f;
+      br_[u] = in ? __ldg(b + off) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < kALoads; ++u) {
+      const int i = tid + u * T;
+      if (TA) As[i % kSkinnyRows][i / kSkinnyRows] = ar[u]; else As[i / kSkinnyKC][i % kSkinnyKC] = ar[u];
+    }
+#pragma unroll
+    for (int u = 0; u < kBLoads; ++u) {
+      const int i = tid + u * T;
+      if (TB) Bs[i % kSkinnyKC][i / kSkinnyKC] = br_[u]; else Bs[i / kSkinnyN][i % kSkinnyN] = br_[u];
     }
     __syncthreads();
 #pragma unroll 4
