@@ -10,7 +10,7 @@
 // every input element belongs to at most one window, so the scatter has no write
 // conflicts and runs without atomics; the common 2x2 / stride 2 / no-padding case is
 // written as a gather that produces each 2x2 block of dx with two 8-byte stores and needs
-// no zero-fill.  Overlapping windows fall back to atomicAdd into a zero-filled dx.
+// no zero-fill.  Overlapping windows are gathered per input element in the reference's order of additions.
 #include <cmath>
 
 #include "rt_internal.cuh"
@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(kThreads) pool_bwd_2x2(const float* __restrict
   }
 }
 
-template <bool ATOMIC>
+// Disjoint windows: every input element is the target of at most one window, plain read-modify-write into a zero-filled dx.
 __global__ void __launch_bounds__(kThreads) pool_bwd_general(const float* __restrict__ g, const float* __restrict__ idx,
                                                               float* __restrict__ dx, int64_t total, int h, int w, int ho,
                                                               int wo, int kw, int sh, int sw, int ph, int pw) {
@@ -115,11 +115,37 @@ __global__ void __launch_bounds__(kThreads) pool_bwd_general(const float* __rest
     if (flat < 0) flat = 0;
     int ky = (int)(flat / kw), kx = (int)(flat % kw);
     int iy = yo * sh + ky - ph, ix = xo * sw + kx - pw;
-    if (iy >= 0 && iy < h && ix >= 0 && ix < w) {
-      float* q = dx + (bc * h + iy) * w + ix;
-      if (ATOMIC) atomicAdd(q, __ldg(g + o));
-      else *q += __ldg(g + o);
+    if (iy >= 0 && iy < h && ix >= 0 && ix < w) dx[(bc * h + iy) * w + ix] += __ldg(g + o);
+  }
+}
+
+// Overlapping windows (stride < kernel): a thread per INPUT element visits the windows that cover it in ascending
+// (yo, xo) order and adds the gradients of those whose saved index points at it.  No atomics and no zero-fill, and the
+// order of the additions is the one of the reference's sequential scatter, so the result is reproducible bit for bit.
+__global__ void __launch_bounds__(kThreads) pool_bwd_gather(const float* __restrict__ g, const float* __restrict__ idx,
+                                                             float* __restrict__ dx, int64_t in_total, int h, int w, int ho,
+                                                             int wo, int kh, int kw, int sh, int sw, int ph, int pw) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < in_total; e += stride) {
+    const int ix = (int)(e % w);
+    const int64_t r = e / w;
+    const int iy = (int)(r % h);
+    const int64_t bc = r / h;
+    const int ny = iy + ph - kh + 1, nx = ix + pw - kw + 1;
+    const int y_lo = ny > 0 ? (ny + sh - 1) / sh : 0, x_lo = nx > 0 ? (nx + sw - 1) / sw : 0;
+    const int y_hi = min((iy + ph) / sh, ho - 1), x_hi = min((ix + pw) / sw, wo - 1);
+    float acc = 0.f;
+    for (int yo = y_lo; yo <= y_hi; ++yo) {
+      const int ky = iy + ph - yo * sh;
+      for (int xo = x_lo; xo <= x_hi; ++xo) {
+        const int kx = ix + pw - xo * sw;
+        const int64_t o = (bc * ho + yo) * wo + xo;
+        long flat = lrintf(__ldg(idx + o));
+        if (flat < 0) flat = 0;
+        if (flat == (long)ky * kw + kx) acc += __ldg(g + o);
+      }
     }
+    dx[e] = acc;
   }
 }
 
@@ -199,15 +225,22 @@ static rt_status pool_backward(rt_ctx* ctx, const float* x, const float* g, cons
     RT_LAUNCHED(ctx);
     return x ? rt_unary_backward(ctx, RT_RELU, x, dx, dx, in_total, 0.f, 0.f) : RT_OK;
   }
-  st = rt_fill(ctx, dx, 0.f, in_total);
-  if (st != RT_OK || total == 0) return st;
-  RT_CHECK_PTR(ctx, g);
-  RT_CHECK_PTR(ctx, idx);
-  int grid = rt_grid_for(ctx, total, kThreads * 2);
-  bool overlap = sh < kh || sw < kw;
-  if (overlap) pool_bwd_general<true><<<grid, kThreads, 0, ctx->stream>>>(g, idx, dx, total, (int)h, (int)w, (int)ho, (int)wo, kw, sh, sw, ph, pw);
-  else pool_bwd_general<false><<<grid, kThreads, 0, ctx->stream>>>(g, idx, dx, total, (int)h, (int)w, (int)ho, (int)wo, kw, sh, sw, ph, pw);
-  RT_LAUNCHED(ctx);
+  const bool overlap = sh < kh || sw < kw;
+  if (overlap && total > 0) {
+    RT_CHECK_PTR(ctx, g);
+    RT_CHECK_PTR(ctx, idx);
+    pool_bwd_gather<<<rt_grid_for(ctx, in_total, kThreads * 2), kThreads, 0, ctx->stream>>>(g, idx, dx, in_total, (int)h, (int)w, (int)ho,
+                                                                                          (int)wo, kh, kw, sh, sw, ph, pw);
+    RT_LAUNCHED(ctx);
+  } else {
+    st = rt_fill(ctx, dx, 0.f, in_total);
+    if (st != RT_OK || total == 0) return st;
+    RT_CHECK_PTR(ctx, g);
+    RT_CHECK_PTR(ctx, idx);
+    pool_bwd_general<<<rt_grid_for(ctx, total, kThreads * 2), kThreads, 0, ctx->stream>>>(g, idx, dx, total, (int)h, (int)w, (int)ho, (int)wo,
+                                                                                        kw, sh, sw, ph, pw);
+    RT_LAUNCHED(ctx);
+  }
   return x ? rt_unary_backward(ctx, RT_RELU, x, dx, dx, in_total, 0.f, 0.f) : RT_OK;  // element-wise, safe in place
 }
 

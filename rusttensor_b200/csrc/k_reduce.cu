@@ -952,6 +952,82 @@ __global__ void __launch_bounds__(kThreads) sce_backward_kernel(const float* __r
   }
 }
 
+// ---- the same two kernels with a warp per row (lanes over the classes, coalesced), used for more than 16 classes ----
+__device__ __forceinline__ float warp_sum_all(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max_all(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ void row_max_lse_warp(const float* x, int classes, int lane, float& m, float& lse) {
+  float mm = -INFINITY;
+  for (int k = lane; k < classes; k += 32) mm = fmaxf(mm, __ldg(x + k));
+  m = warp_max_all(mm);
+  float ss = 0.f;
+  for (int k = lane; k < classes; k += 32) ss += expf(__ldg(x + k) - m);
+  lse = logf(warp_sum_all(ss));
+}
+
+constexpr int kSceWarpBlock = 1024;
+// part[block] = sum over the block's rows of sum_k log_softmax * t; with `final` the single block writes the loss itself.
+__global__ void __launch_bounds__(kSceWarpBlock) sce_forward_warp_kernel(const float* __restrict__ logits,
+                                                                         const float* __restrict__ targets, float* __restrict__ out,
+                                                                         int64_t rows, int classes, int final) {
+  __shared__ float smem[kSceWarpBlock / 32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int nw = kSceWarpBlock / 32;
+  float acc = 0.f;
+  for (int64_t r = (int64_t)blockIdx.x * nw + warp; r < rows; r += (int64_t)gridDim.x * nw) {
+    const float* x = logits + r * classes;
+    const float* t = targets + r * classes;
+    float m, lse;
+    row_max_lse_warp(x, classes, lane, m, lse);
+    float e = 0.f;
+    for (int k = lane; k < classes; k += 32) e += ((__ldg(x + k) - m) - lse) * __ldg(t + k);
+    acc += warp_sum_all(e);
+  }
+  if (lane == 0) smem[warp] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int w = 0; w < nw; ++w) total += smem[w];
+    out[blockIdx.x] = final ? (total / (float)rows) * -1.0f : total;
+  }
+}
+
+__global__ void __launch_bounds__(32) sce_finish_kernel(const float* __restrict__ part, int n, float* __restrict__ loss, int64_t rows) {
+  float v = 0.f;
+  for (int i = threadIdx.x; i < n; i += 32) v += part[i];
+  v = warp_sum_all(v);
+  if (threadIdx.x == 0) loss[0] = (v / (float)rows) * -1.0f;
+}
+
+__global__ void __launch_bounds__(kThreads) sce_backward_warp_kernel(const float* __restrict__ logits, const float* __restrict__ targets,
+                                                                     const float* __restrict__ g, float* __restrict__ dlogits,
+                                                                     float* __restrict__ dtargets, int64_t rows, int classes) {
+  const float scale = -__ldg(g) / (float)rows;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int nw = kThreads / 32;
+  for (int64_t r = (int64_t)blockIdx.x * nw + warp; r < rows; r += (int64_t)gridDim.x * nw) {
+    const float* x = logits + r * classes;
+    const float* t = targets + r * classes;
+    float m, lse;
+    row_max_lse_warp(x, classes, lane, m, lse);
+    float st = 0.f;
+    for (int k = lane; k < classes; k += 32) st += __ldg(t + k) * scale;
+    st = warp_sum_all(st);
+    for (int k = lane; k < classes; k += 32) {
+      const float ls = (__ldg(x + k) - m) - lse;
+      if (dlogits) dlogits[r * classes + k] = __ldg(t + k) * scale - expf(ls) * st;
+      if (dtargets) dtargets[r * classes + k] = ls * scale;
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" rt_status rt_softmax_cross_entropy(rt_ctx* ctx, const float* logits, const float* targets, int64_t rows, int64_t classes,
@@ -963,7 +1039,25 @@ extern "C" rt_status rt_softmax_cross_entropy(rt_ctx* ctx, const float* logits, 
   RT_CHECK_PTR(ctx, logits);
   RT_CHECK_PTR(ctx, targets);
   RT_CHECK_PTR(ctx, loss);
-  sce_forward_kernel<<<1, kThreads, 0, ctx->stream>>>(logits, targets, loss, rows, (int)classes);
+  if (classes <= 16) {  // a thread per row
+    sce_forward_kernel<<<1, kThreads, 0, ctx->stream>>>(logits, targets, loss, rows, (int)classes);
+    RT_LAUNCHED(ctx);
+    return RT_OK;
+  }
+  constexpr int rows_per_block = kSceWarpBlock / 32;
+  if (rows <= 8 * rows_per_block) {
+    sce_forward_warp_kernel<<<1, kSceWarpBlock, 0, ctx->stream>>>(logits, targets, loss, rows, (int)classes, 1);
+    RT_LAUNCHED(ctx);
+    return RT_OK;
+  }
+  int64_t want = (rows + 4 * rows_per_block - 1) / (4 * rows_per_block);
+  const int grid = (int)(want < ctx->sm_count ? want : ctx->sm_count);
+  RtScratch part(ctx);
+  rt_status st = part.alloc(sizeof(float) * (size_t)grid);
+  if (st != RT_OK) return st;
+  sce_forward_warp_kernel<<<grid, kSceWarpBlock, 0, ctx->stream>>>(logits, targets, part.as<float>(), rows, (int)classes, 0);
+  RT_LAUNCHED(ctx);
+  sce_finish_kernel<<<1, 32, 0, ctx->stream>>>(part.as<float>(), grid, loss, rows);
   RT_LAUNCHED(ctx);
   return RT_OK;
 }
@@ -977,8 +1071,12 @@ extern "C" rt_status rt_softmax_cross_entropy_backward(rt_ctx* ctx, const float*
   RT_CHECK_PTR(ctx, targets);
   RT_CHECK_PTR(ctx, g);
   if (!dlogits && !dtargets) return RT_OK;
-  sce_backward_kernel<<<rt_grid_for(ctx, rows, kThreads), kThreads, 0, ctx->stream>>>(logits, targets, g, dlogits, dtargets, rows,
-                                                                                     (int)classes);
+  if (classes <= 16)
+    sce_backward_kernel<<<rt_grid_for(ctx, rows, kThreads), kThreads, 0, ctx->stream>>>(logits, targets, g, dlogits, dtargets, rows,
+                                                                                       (int)classes);
+  else
+    sce_backward_warp_kernel<<<rt_grid_for(ctx, rows, kThreads / 32), kThreads, 0, ctx->stream>>>(logits, targets, g, dlogits,
+                                                                                                 dtargets, rows, (int)classes);
   RT_LAUNCHED(ctx);
   return RT_OK;
 }

@@ -255,6 +255,39 @@ def test_fused_relu_max_pool_is_bit_identical_to_the_two_ops(capi):
         assert np.array_equal(d1.numpy(), d0.numpy())
 
 
+def test_max_pool_backward_with_overlapping_windows_is_reproducible(capi):
+    """stride < kernel: several windows can route their gradient to one input element.  The sum is formed in the order
+    of the reference's sequential scatter (ascending output index), so it equals a float32 replay of that loop bit for
+    bit and does not change from run to run."""
+    r = rng(75)
+    i64, i32 = C.c_int64, C.c_int
+    for (n, c, h, w, k, st, pd) in ((2, 3, 9, 7, 3, 2, 1), (2, 2, 6, 6, 2, 1, 0), (1, 1, 5, 5, 3, 1, 1), (3, 4, 12, 12, 4, 2, 0)):
+        x = r.integers(-2, 3, (n, c, h, w)).astype(np.float32)   # many ties: shared maxima between neighbouring windows
+        ho, wo = (h + 2 * pd - k) // st + 1, (w + 2 * pd - k) // st + 1
+        g = r.standard_normal((n, c, ho, wo)).astype(np.float32)
+        dx_, dg = capi.to_device(x), capi.to_device(g)
+        args = (i64(n), i64(c), i64(h), i64(w), i32(k), i32(k), i32(st), i32(st), i32(pd), i32(pd))
+        y, idx = capi.empty(g.shape), capi.empty(g.shape)
+        capi.call("max_pool2d", dx_.ptr, *args, y.ptr, idx.ptr)
+        runs = []
+        for _ in range(4):
+            d = capi.empty(x.shape)
+            capi.call("max_pool2d_backward", dg.ptr, idx.ptr, *args, d.ptr)
+            runs.append(d.numpy())
+        want = np.zeros_like(x)
+        flat = np.rint(idx.numpy()).astype(np.int64)
+        for b in range(n):
+            for ch in range(c):
+                for yo in range(ho):
+                    for xo in range(wo):
+                        ky, kx = divmod(int(flat[b, ch, yo, xo]), k)
+                        iy, ix = yo * st + ky - pd, xo * st + kx - pd
+                        if 0 <= iy < h and 0 <= ix < w:
+                            want[b, ch, iy, ix] = np.float32(want[b, ch, iy, ix] + g[b, ch, yo, xo])
+        for d in runs:
+            assert np.array_equal(d, want)
+
+
 def test_fused_softmax_cross_entropy(capi):
     r = rng(72)
     for rows, classes in ((1, 1), (7, 10), (256, 10), (64, 65), (1000, 33)):
