@@ -590,12 +590,16 @@ rt_status rt_gemm(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, int64_t n, i
 rt_status rt_matmul_backward(rt_ctx* ctx, const float* a, const float* b, const float* g, int64_t m, int64_t k, int64_t n,
                              float* da, float* db) {
   RT_CHECK_CTX(ctx);
-  rt_status st = RT_OK;
-  // da[M,K] = g[M,N] * b[K,N]^T ; db[K,N] = a[M,K]^T * g[M,N]
+  // da[M,K] = g[M,N] * b[K,N]^T ; db[K,N] = a[M,K]^T * g[M,N]: independent, so db goes to the side stream
+  RtFork fork(ctx, da && db);
+  rt_status st = RT_OK, st2 = RT_OK;
+  if (db) st2 = rt_gemm(ctx, 1, 0, k, n, m, a, k, g, n, db, n, 0);
+  rt_status e1 = fork.end();
   if (da) st = rt_gemm(ctx, 0, 1, m, k, n, g, n, b, n, da, k, 0);
+  rt_status e2 = fork.join();
   if (st != RT_OK) return st;
-  if (db) st = rt_gemm(ctx, 1, 0, k, n, m, a, k, g, n, db, n, 0);
-  return st;
+  if (st2 != RT_OK) return st2;
+  return e1 != RT_OK ? e1 : e2;
 }
 
 rt_status rt_conv2d(rt_ctx* ctx, const float* x, const float* w, const float* bias, int64_t n, int64_t cin, int64_t h,
@@ -618,21 +622,22 @@ rt_status rt_conv2d_backward(rt_ctx* ctx, const float* x, const float* w, const 
   if (st != RT_OK) return st;
   if (h + 2 * ph < kh || wd + 2 * pw < kw) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "conv2d_backward: kernel larger than padded input");
   ConvGeom g = make_geom(n, cin, h, wd, cout, kh, kw, sh, sw, ph, pw);
-  if (dw) {
-    st = conv_weight_grad_like(ctx, x, gr, g, dw);
-    if (st != RT_OK) return st;
-  }
-  if (db) {
-    st = channel_sum(ctx, gr, n, cout, (int64_t)g.Hy * g.Wy, db);
-    if (st != RT_OK) return st;
-  }
-  if (dx) {
+  // The three gradients are independent.  The bias gradient (bandwidth-bound, small footprint) goes to the side stream,
+  // where it overlaps the contraction kernels.
+  RtFork fork(ctx, db && (dw || dx));
+  rt_status st_b = RT_OK;
+  if (db) st_b = channel_sum(ctx, gr, n, cout, (int64_t)g.Hy * g.Wy, db);
+  rt_status e1 = fork.end();
+  if (dw) st = conv_weight_grad_like(ctx, x, gr, g, dw);
+  if (st == RT_OK && dx) {
     // positions never touched by a window (possible when stride > kernel) must read as 0:
     // the gather computes every dx element, so no pre-fill is needed.
     st = conv_gather_like(ctx, gr, w, nullptr, g, (int)cin, dx);
-    if (st != RT_OK) return st;
   }
-  return RT_OK;
+  rt_status e2 = fork.join();
+  if (st != RT_OK) return st;
+  if (st_b != RT_OK) return st_b;
+  return e1 != RT_OK ? e1 : e2;
 }
 
 rt_status rt_conv2d_transpose(rt_ctx* ctx, const float* x, const float* w, const float* bias, int64_t n, int64_t cin,

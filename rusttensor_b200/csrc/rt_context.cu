@@ -46,6 +46,8 @@ rt_status rt_ctx_create(int device, rt_ctx** out) {
   }
   const char* no_tc = getenv("RT_B200_DISABLE_TENSOR_CORES");
   if (no_tc && no_tc[0] == '1') ctx->use_tensor_cores = false;
+  const char* serial = getenv("RT_B200_SERIAL_BACKWARD");
+  if (serial && serial[0] == '1') ctx->concurrent_backward = false;
   *out = ctx;
   return RT_OK;
 }
@@ -64,6 +66,7 @@ rt_status rt_ctx_destroy(rt_ctx* ctx) {
   rt_dp_finalize(ctx);
   for (auto& kv : ctx->free_blocks) cudaFree(kv.second);
   for (auto& kv : ctx->capture_free) cudaFree(kv.second);
+  for (auto& kv : ctx->side_deferred) cudaFree(kv.second);
   for (auto& kv : ctx->live_blocks) cudaFree(kv.first);
   if (ctx->device_status) cudaFree(ctx->device_status);
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
@@ -85,7 +88,7 @@ static size_t round_size(size_t bytes) {
 rt_status rt_malloc(rt_ctx* ctx, size_t bytes, void** out) {
   RT_CHECK_CTX(ctx);
   RT_CHECK_PTR(ctx, out);
-  if (ctx->on_side) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_malloc inside a side-stream section");
+  if (ctx->on_side && !ctx->side_internal) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_malloc inside a side-stream section");
   size_t sz = round_size(bytes);
   if (ctx->capturing) {
     auto cit = ctx->capture_free.lower_bound(sz);
@@ -140,7 +143,8 @@ rt_status rt_free(rt_ctx* ctx, void* ptr) {
   auto it = ctx->live_blocks.find(ptr);
   if (it == ctx->live_blocks.end()) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_free: pointer %p is not a live block", ptr);
   ctx->bytes_in_use -= (int64_t)it->second;
-  if (ctx->capturing) ctx->capture_free.emplace(it->second, ptr);
+  if (ctx->on_side && ctx->side_internal) ctx->side_deferred.emplace_back(it->second, ptr);
+  else if (ctx->capturing) ctx->capture_free.emplace(it->second, ptr);
   else ctx->free_blocks.emplace(it->second, ptr);
   ctx->live_blocks.erase(it);
   return RT_OK;
@@ -335,6 +339,32 @@ rt_status rt_side_stream_join(rt_ctx* ctx) {
   ctx->side_pending = false;
   RT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->join_ev, 0));
   return RT_OK;
+}
+
+RtFork::RtFork(rt_ctx* c, bool want) : ctx(c) {
+  if (!want || !c->concurrent_backward || c->on_side || c->side_pending) return;
+  if (rt_side_stream_begin(c) != RT_OK) return;
+  c->side_internal = true;
+  open = true;
+}
+rt_status RtFork::end() {
+  if (!open) return RT_OK;
+  open = false;
+  pending = true;
+  ctx->side_internal = false;
+  return rt_side_stream_end(ctx);
+}
+rt_status RtFork::join() {
+  if (!pending) return RT_OK;
+  pending = false;
+  rt_status st = rt_side_stream_join(ctx);
+  // ordered after the join on the main stream: the parked blocks may be handed out again
+  for (auto& kv : ctx->side_deferred) {
+    if (ctx->capturing) ctx->capture_free.emplace(kv.first, kv.second);
+    else ctx->free_blocks.emplace(kv.first, kv.second);
+  }
+  ctx->side_deferred.clear();
+  return st;
 }
 
 // ---- events on the context's stream -----------------------------------------------------------

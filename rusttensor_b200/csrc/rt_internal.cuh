@@ -37,6 +37,11 @@ struct rt_ctx {
   cudaStream_t side_stream = nullptr, main_stream = nullptr;
   cudaEvent_t fork_ev = nullptr, join_ev = nullptr;
   bool on_side = false, side_pending = false;
+  // Sections opened by the library itself (RtFork) may allocate: what they free is parked until the join, so that
+  // nothing queued on the main stream in between can be handed a block the side stream still uses.
+  bool side_internal = false;
+  std::vector<std::pair<size_t, void*>> side_deferred;
+  bool concurrent_backward = true;  // independent halves of one backward call on two streams (RT_B200_SERIAL_BACKWARD=1: off)
   // Error word written by kernels whose bounded waits expire (0 = none); see rt_device_status.
   int* device_status = nullptr;
   // Route large contractions to the tcgen05 3xTF32 kernels (k_gemm_tc.cu).
@@ -95,6 +100,21 @@ struct RtScratch {
   }
   template <class T>
   T* as() { return static_cast<T*>(ptr); }
+};
+
+// Runs the calls between construction and end() on the context's side stream, when the context allows it and no
+// other section is open; join() (or the destructor) makes the main stream wait for them.  With `want` false, or when a
+// section is already open, everything simply stays on the main stream.
+struct RtFork {
+  rt_ctx* ctx;
+  bool open = false, pending = false;
+  RtFork(rt_ctx* c, bool want);
+  rt_status end();
+  rt_status join();
+  ~RtFork() {
+    end();
+    join();
+  }
 };
 
 static inline int rt_grid_for(rt_ctx* ctx, int64_t work_items, int per_block, int max_waves = 8) {
