@@ -627,6 +627,11 @@ rt_status rt_conv2d_backward(rt_ctx* ctx, const float* x, const float* w, const 
   RtFork fork(ctx, db && (dw || dx));
   rt_status st_b = RT_OK;
   if (db) st_b = channel_sum(ctx, gr, n, cout, (int64_t)g.Hy * g.Wy, db);
+  // with an input gradient to compute, the weight gradient joins the bias gradient on the side stream
+  if (dw && dx && fork.open) {
+    st = conv_weight_grad_like(ctx, x, gr, g, dw);
+    dw = nullptr;
+  }
   rt_status e1 = fork.end();
   if (dw) st = conv_weight_grad_like(ctx, x, gr, g, dw);
   if (st == RT_OK && dx) {
