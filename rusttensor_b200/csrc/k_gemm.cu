@@ -680,19 +680,21 @@ rt_status rt_conv2d_transpose_backward(rt_ctx* ctx, const float* x, const float*
   g.Hy = (int)h;
   g.Wy = (int)wd;
   g.finish();
-  if (dx) {  // dx = conv(grad_output, w viewed as [cin, cout, kh, kw])
-    st = conv_forward_like(ctx, gr, w, nullptr, g, dx);
-    if (st != RT_OK) return st;
+  // as in rt_conv2d_backward: bias gradient (and the weight gradient, when dx is wanted too) on the side stream
+  RtFork fork(ctx, db && (dw || dx));
+  rt_status st_side = RT_OK;
+  if (db) st_side = channel_sum(ctx, gr, n, cout, oh * ow, db);
+  if (st_side == RT_OK && dw && dx && fork.open) {  // dw[cin, cout*kh*kw] = sum x * im2col(grad_output)
+    st_side = conv_weight_grad_like(ctx, gr, x, g, dw);
+    dw = nullptr;
   }
-  if (dw) {  // dw[cin, cout*kh*kw] = sum x * im2col(grad_output)
-    st = conv_weight_grad_like(ctx, gr, x, g, dw);
-    if (st != RT_OK) return st;
-  }
-  if (db) {
-    st = channel_sum(ctx, gr, n, cout, oh * ow, db);
-    if (st != RT_OK) return st;
-  }
-  return RT_OK;
+  rt_status e1 = fork.end();
+  if (dx) st = conv_forward_like(ctx, gr, w, nullptr, g, dx);  // dx = conv(grad_output, w viewed as [cin, cout, kh, kw])
+  if (st == RT_OK && dw) st = conv_weight_grad_like(ctx, gr, x, g, dw);
+  rt_status e2 = fork.join();
+  if (st != RT_OK) return st;
+  if (st_side != RT_OK) return st_side;
+  return e1 != RT_OK ? e1 : e2;
 }
 
 }  // extern "C"
