@@ -79,7 +79,8 @@ rt_status rt_upload_submit(rt_ctx* ctx, rt_upload* up, void* dst);
 /* A side stream for work that may overlap what follows on the context's stream (new; used to all-reduce the
  * gradients that are ready while the rest of the backward pass runs).  Between begin and end every rt_* call of this
  * context is enqueued on the side stream, which first waits for everything queued before `begin`; `join` makes the
- * context's stream wait for the side work.  Calls inside the section must not allocate (rt_malloc fails there);
+ * context's stream wait for the side work.  Calls inside a section opened through this API must not allocate (rt_malloc fails there; the sections the library
+ * opens itself inside a backward call park their frees until the join instead);
  * sections do not nest; a section opened during graph capture must be joined before the capture ends. */
 rt_status rt_side_stream_begin(rt_ctx* ctx);
 rt_status rt_side_stream_end(rt_ctx* ctx);
