@@ -99,6 +99,10 @@ rt_status rt_kernel_launch_count(rt_ctx* ctx, int64_t* launches);               
 rt_status rt_device_status(rt_ctx* ctx, int* code);
 /* 1 (default): large contractions run on the tcgen05 3xTF32 tensor-core kernels; 0: exact FP32 kernels only. */
 rt_status rt_set_tensor_cores(rt_ctx* ctx, int enable);
+/* 1 (default): the independent halves of one backward call (da / db of a matmul; the bias and weight gradients of a
+ * convolution beside its input gradient) are issued on two streams; 0: one after the other on the context's stream.
+ * Results are bit-identical either way.  No counterpart in the reference (a scheduling switch of this backend). */
+rt_status rt_set_concurrent_backward(rt_ctx* ctx, int enable);
 
 /* CUDA-graph capture of a fixed call sequence (one training step). */
 rt_status rt_graph_begin(rt_ctx* ctx);

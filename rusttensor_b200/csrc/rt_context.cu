@@ -422,6 +422,12 @@ rt_status rt_set_tensor_cores(rt_ctx* ctx, int enable) {
   return RT_OK;
 }
 
+rt_status rt_set_concurrent_backward(rt_ctx* ctx, int enable) {
+  RT_CHECK_CTX(ctx);
+  ctx->concurrent_backward = enable != 0;
+  return RT_OK;
+}
+
 // ---- CUDA graphs -----------------------------------------------------------------
 rt_status rt_graph_begin(rt_ctx* ctx) {
   RT_CHECK_CTX(ctx);

@@ -288,6 +288,56 @@ def test_max_pool_backward_with_overlapping_windows_is_reproducible(capi):
             assert np.array_equal(d, want)
 
 
+def test_two_stream_backward_is_bit_identical_to_serial(capi):
+    """matmul / conv / conv-transpose backward issue their independent halves on two streams (scratch allocated on the
+    side stream, frees parked until the join).  Alternating shapes back to back, so that scratch blocks get recycled
+    between the streams, every gradient must equal the single-stream result bit for bit."""
+    r = rng(76)
+    i64, i32 = C.c_int64, C.c_int
+
+    def run_all():
+        outs = []
+        for rep in range(3):
+            for (m, k, n) in ((256, 3136, 128), (64, 577, 2048), (256, 128, 10), (70, 90, 50)):
+                rr = rng(1000 + m + k + n)
+                a = capi.to_device(rr.standard_normal((m, k)).astype(np.float32))
+                b = capi.to_device(rr.standard_normal((k, n)).astype(np.float32))
+                g = capi.to_device(rr.standard_normal((m, n)).astype(np.float32))
+                da, db = capi.empty((m, k)), capi.empty((k, n))
+                capi.call("matmul_backward", a.ptr, b.ptr, g.ptr, i64(m), i64(k), i64(n), da.ptr, db.ptr)
+                outs += [da.numpy(), db.numpy()]
+            for (nb, cin, hw, cout, ks, st, pd) in ((16, 32, 14, 64, 3, 1, 1), (4, 3, 9, 5, 3, 2, 1), (8, 1, 28, 32, 3, 1, 1)):
+                rr = rng(2000 + nb + cin + hw)
+                ho = (hw + 2 * pd - ks) // st + 1
+                x = capi.to_device(rr.standard_normal((nb, cin, hw, hw)).astype(np.float32))
+                w = capi.to_device(rr.standard_normal((cout, cin, ks, ks)).astype(np.float32))
+                g = capi.to_device(rr.standard_normal((nb, cout, ho, ho)).astype(np.float32))
+                dx, dw, db = capi.empty((nb, cin, hw, hw)), capi.empty((cout, cin, ks, ks)), capi.empty((cout,))
+                capi.call("conv2d_backward", x.ptr, w.ptr, g.ptr, i64(nb), i64(cin), i64(hw), i64(hw), i64(cout), i32(ks), i32(ks),
+                          i32(st), i32(st), i32(pd), i32(pd), dx.ptr, dw.ptr, db.ptr)
+                outs += [dx.numpy(), dw.numpy(), db.numpy()]
+                # transposed: x [nb, cout, ho, ho] -> y [nb, cin, hw', hw'], weights [cout, cin, ks, ks]
+                ot = (ho - 1) * st + ks - 2 * pd
+                xt = capi.to_device(rr.standard_normal((nb, cout, ho, ho)).astype(np.float32))
+                gt = capi.to_device(rr.standard_normal((nb, cin, ot, ot)).astype(np.float32))
+                dxt, dwt, dbt = capi.empty((nb, cout, ho, ho)), capi.empty((cout, cin, ks, ks)), capi.empty((cin,))
+                capi.call("conv2d_transpose_backward", xt.ptr, w.ptr, gt.ptr, i64(nb), i64(cout), i64(ho), i64(ho), i64(cin), i32(ks),
+                          i32(ks), i32(st), i32(st), i32(pd), i32(pd), dxt.ptr, dwt.ptr, dbt.ptr)
+                outs += [dxt.numpy(), dwt.numpy(), dbt.numpy()]
+        return outs
+
+    try:
+        capi.call("set_concurrent_backward", i32(0))
+        serial = run_all()
+        capi.call("set_concurrent_backward", i32(1))
+        forked = run_all()
+    finally:
+        capi.call("set_concurrent_backward", i32(1))
+    assert len(serial) == len(forked)
+    for i, (a, b) in enumerate(zip(serial, forked)):
+        assert np.array_equal(a, b), f"output {i} differs between the two-stream and the single-stream backward"
+
+
 def test_fused_softmax_cross_entropy(capi):
     r = rng(72)
     for rows, classes in ((1, 1), (7, 10), (256, 10), (64, 65), (1000, 33)):
