@@ -28,7 +28,6 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 WORKLOADS = {
     # name: (config id, dims, samples per step per GPU, description)
@@ -100,7 +99,7 @@ class ClockSampler:
 def cpu_step_time(config, dims, seed, steps):
     """Times `steps` training steps of the CPU oracle (single thread). Returns seconds per step."""
     import oracle
-    from helpers import setup_trainer, workload_data
+    from rusttensor_b200.workloads import setup_trainer, workload_data
 
     e = oracle.engine()
     params, inputs = workload_data(config, dims, seed)
@@ -114,69 +113,222 @@ def cpu_step_time(config, dims, seed, steps):
     return (time.perf_counter() - t0) / steps
 
 
+def _cpu_worker(a):
+    config, dims, steps = a
+    return cpu_step_time(config, dims, 0, steps)
+
+
+def cpu_all_cores(config, dims, per_gpu, steps):
+    """Throughput of the host with every core busy: one independent single-thread replica of the CPU path per core, each
+    running full-batch steps (the most generous reading of 'all cores': no exchange between the replicas is counted).
+    NOT reference behaviour: the reference's ndarray / matrixmultiply build runs one thread."""
+    import multiprocessing as mp
+
+    procs = max(1, os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    with mp.get_context("fork").Pool(procs) as pool:
+        secs = pool.map(_cpu_worker, [(config, dims, steps)] * procs)
+    wall = time.perf_counter() - t0
+    return {"value": procs * per_gpu / max(secs), "unit": "samples/s", "cores": procs, "kind": "port",
+            "sample": f"{procs} independent single-thread replicas x {steps} full-batch steps, slowest replica {max(secs) * 1e3:.0f} ms per step "
+                      f"(wall {wall:.1f} s incl. start-up); not reference behaviour (the reference runs one thread)"}
+
+
+def workload_config(desc, per_gpu, world, extra=None):
+    cfg = {"workload": desc, "per_gpu_batch": per_gpu, "global_batch": per_gpu * world, "parallelism": f"dp{world}"}
+    cfg.update(extra or {})
+    return cfg
+
+
 def run_reference(args, rank, world):
     """The reference arm: the reference's own CPU algorithm (oracle port) on the host cores."""
     if rank != 0:
         return
     config, dims, per_gpu, desc = WORKLOADS[args.workload]
     n_timed = max(1, min(args.steps, 20 if args.workload in ("c3", "c1") else 1))  # bounded: about 10-15 s of CPU work
-    t = [cpu_step_time(config, dims, 0, n_timed)]
-    sec = float(np.mean(t))
+    sec = cpu_step_time(config, dims, 0, n_timed)
     value = per_gpu / sec
+    cpu = {"value": value, "unit": "samples/s", "cores": 1, "kind": "port",
+           "sample": f"{n_timed} timed full-batch steps ({per_gpu} samples each) of the C++ restatement of the reference "
+                     f"CPU backend; the Rust reference cannot be built here (no cargo/rustc); host has {os.cpu_count()} cores, "
+                     "the reference's ndarray/matrixmultiply build is single-threaded"}
     line = {
         "impl": "reference", "metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": desc, "per_gpu_batch": per_gpu, "note": "CPU path of the reference, single host thread; one rank only"},
-        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": 1, "kind": "port",
-                         "sample": f"{n_timed} timed full-batch steps ({per_gpu} samples each) of the C++ restatement of the reference "
-                                   f"CPU backend; the Rust reference cannot be built here (no cargo/rustc); host has {os.cpu_count()} cores, "
-                                   "the reference's ndarray/matrixmultiply build is single-threaded"},
+        "config": workload_config(desc, per_gpu, max(1, args.gpus)),
+        "note": "CPU path of the reference, single host thread (as the reference is built); one process whatever --gpus says",
+        "cpu_baseline": cpu,
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if args.workload in ("c3", "c1"):
+        line["cpu_all_cores"] = cpu_all_cores(config, dims, per_gpu, max(2, n_timed // 4))
     print(json.dumps(line))
 
 
-def measure_dominant_kernel(rt, capi, config, dims, pk):
-    """Times the dominant kernel of the step in isolation with CUDA events on the library's stream,
-    flushing L2 between launches, and reports it against its roofline."""
-    lib, ctx = capi.lib, capi.ctx
-    if config == 3:
-        n, hw, c1, c2 = dims[0], dims[1] // 2, dims[2], dims[3]
-        # conv2 gradients: x [n,c1,hw,hw], w [c2,c1,3,3], g [n,c2,hw,hw] -> dX and dW implicit GEMMs
-        r = np.random.default_rng(0)
-        x = capi.to_device(r.standard_normal((n, c1, hw, hw)).astype(np.float32))
-        w = capi.to_device(r.standard_normal((c2, c1, 3, 3)).astype(np.float32))
-        g = capi.to_device(r.standard_normal((n, c2, hw, hw)).astype(np.float32))
-        dx, dw, db = capi.empty((n, c1, hw, hw)), capi.empty((c2, c1, 3, 3)), capi.empty((c2,))
-        flops = 2.0 * 2.0 * n * hw * hw * c2 * c1 * 9  # dX + dW, 2*M*N*K each
-        call = lambda: capi.call("conv2d_backward", x.ptr, w.ptr, g.ptr, C.c_int64(n), C.c_int64(c1), C.c_int64(hw), C.c_int64(hw),
-                                 C.c_int64(c2), C.c_int(3), C.c_int(3), C.c_int(1), C.c_int(1), C.c_int(1), C.c_int(1), dx.ptr, dw.ptr, None)
-        name = "conv2 input+weight gradient (implicit GEMM)"
-    else:
+def _recorded_traffic(key):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of a kernel at a given shape, from the ncu
+    captures summarised under profiles/ (profiles/roofline_traffic.json); None when no capture matches."""
+    path = os.path.join(ROOT, "profiles", "roofline_traffic.json")
+    try:
+        return json.load(open(path)).get(key, {}).get("dram_bytes_per_launch")
+    except (OSError, ValueError):
         return None
-    flush = capi.empty((64 * 1024 * 1024,))  # 256 MB > 126 MB L2
+
+
+def _time_call(capi, call, flush, reps=20):
+    """Mean CUDA-event time (seconds) of `call` on the library's stream with a 256 MB L2 flush before every launch."""
     ms = C.c_float(0)
     for _ in range(3):
         call()
     times = []
-    for _ in range(20):
+    for _ in range(reps):
         capi.call("fill", flush.ptr, C.c_float(1.0), C.c_int64(flush.size))
         capi.call("timer_start")
         call()
         capi.call("timer_stop", C.byref(ms))
         times.append(ms.value)
-    t = float(np.mean(times)) * 1e-3
-    peak = pk["bf16"] / 6.0  # 3xTF32: TF32 runs at half the bf16 rate, three MMAs per product
-    achieved = flops / t / 1e12
-    # DRAM bytes (read + write) of the two kernels of this call from an `ncu --set full` capture of this workload
-    # (its summary is committed with the other profile summaries): 13.07 MB (input gradient) + 19.34 MB (weight
-    # gradient); the outputs stay in L2.
-    traffic = 32.41e6 if (n, hw, c1, c2) == (256, 14, 32, 64) else None
-    return {"bound": "tensor", "kernel": name, "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-            "traffic": traffic, "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, ncu)",
-            "algorithmic_bytes": 4.0 * (2 * n * c1 * hw * hw + 2 * n * c2 * hw * hw + 2 * c2 * c1 * 9), "avg_launch_ms": t * 1e3,
-            "peak_source": f"{pk['source']} bf16 burst {pk['bf16']} TFLOP/s / 6 (TF32 = bf16/2, three TF32 MMAs per fp32 product)"}
+    return float(np.mean(times)) * 1e-3
+
+
+def measure_dominant_kernel(rt, capi, config, dims, pk):
+    """Times the convolution-gradient contractions of the step in isolation (CUDA events on the library's stream, L2
+    flushed between launches) and reports each against the 3xTF32 tensor-core roofline: flops = 2*M*N*K of real
+    multiply-adds, peak = measured bf16 burst / 6 (TF32 runs at half the bf16 rate, three MMAs per fp32 product).
+    `roofline` is the dominant one (C3: the conv2 input+weight gradient pair, one rt_conv2d_backward call); `kernels`
+    lists every contraction on its own."""
+    i64, i32 = C.c_int64, C.c_int
+    peak = pk["bf16"] / 6.0
+    src = f"{pk['source']} bf16 burst {pk['bf16']} TFLOP/s / 6 (TF32 = bf16/2, three TF32 MMAs per fp32 product)"
+    r = np.random.default_rng(0)
+    dev = lambda *shape: capi.to_device(r.standard_normal(shape).astype(np.float32))
+    flush = capi.empty((64 * 1024 * 1024,))  # 256 MB > 126 MB L2
+
+    def conv_case(tag, n, cin, hw, cout):
+        x, w, g = dev(n, cin, hw, hw), dev(cout, cin, 3, 3), dev(n, cout, hw, hw)
+        dx, dw = capi.empty((n, cin, hw, hw)), capi.empty((cout, cin, 3, 3))
+        mk = lambda pdx, pdw: (lambda: capi.call("conv2d_backward", x.ptr, w.ptr, g.ptr, i64(n), i64(cin), i64(hw), i64(hw), i64(cout),
+                                                 i32(3), i32(3), i32(1), i32(1), i32(1), i32(1), pdx, pdw, None))
+        fl = 2.0 * n * hw * hw * cout * cin * 9
+        shape = f"n{n}_c{cin}_hw{hw}_k{cout}"
+        byt_dx = 4.0 * (n * cout * hw * hw + cout * cin * 9 + n * cin * hw * hw)
+        byt_dw = 4.0 * (n * cout * hw * hw + n * cin * hw * hw + cout * cin * 9)
+        return [(f"{tag} input gradient", f"conv3x3_dx_{shape}", fl, byt_dx, mk(dx.ptr, None)),
+                (f"{tag} weight gradient", f"conv3x3_dw_{shape}", fl, byt_dw, mk(None, dw.ptr)),
+                (f"{tag} input+weight gradient (one call)", f"conv3x3_dxdw_{shape}", 2 * fl, byt_dx + byt_dw - 4.0 * n * cout * hw * hw,
+                 mk(dx.ptr, dw.ptr))]
+
+    def convt_case(tag, n, cin, hw, cout):  # k4 s2 p1: x [n,cin,hw,hw], w [cin,cout,4,4], g [n,cout,2hw,2hw]
+        x, w, g = dev(n, cin, hw, hw), dev(cin, cout, 4, 4), dev(n, cout, 2 * hw, 2 * hw)
+        dx, dw = capi.empty((n, cin, hw, hw)), capi.empty((cin, cout, 4, 4))
+        mk = lambda pdx, pdw: (lambda: capi.call("conv2d_transpose_backward", x.ptr, w.ptr, g.ptr, i64(n), i64(cin), i64(hw), i64(hw),
+                                                 i64(cout), i32(4), i32(4), i32(2), i32(2), i32(1), i32(1), pdx, pdw, None))
+        fl = 2.0 * n * hw * hw * cin * cout * 16
+        shape = f"n{n}_c{cin}_hw{hw}_k{cout}"
+        byt = 4.0 * (n * cout * 4 * hw * hw + cin * cout * 16 + n * cin * hw * hw)
+        return [(f"{tag} input gradient", f"convT4x4s2_dx_{shape}", fl, byt, mk(dx.ptr, None)),
+                (f"{tag} weight gradient", f"convT4x4s2_dw_{shape}", fl, byt, mk(None, dw.ptr))]
+
+    if config == 3:
+        n, hw, c1, c2 = dims[0], dims[1] // 2, dims[2], dims[3]
+        cases = conv_case("conv2", n, c1, hw, c2)
+        dominant = 2
+    elif config == 4:
+        n, cin, hw, cout = dims
+        cases = conv_case("conv", n, cin, hw, cout)[:2] + convt_case("conv-transpose", n, cout, hw // 2, cin)
+        dominant = None  # the slowest of the four
+    else:
+        return None
+    kernels = []
+    for name, key, flops, nbytes, call in cases:
+        t = _time_call(capi, call, flush)
+        achieved = flops / t / 1e12
+        kernels.append({"bound": "tensor", "kernel": name, "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                        "traffic": _recorded_traffic(key), "traffic_unit": "bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum, ncu)",
+                        "algorithmic_bytes": nbytes, "gflop": flops / 1e9, "avg_launch_ms": t * 1e3, "peak_source": src})
+    if dominant is None:
+        dominant = int(np.argmax([k["avg_launch_ms"] for k in kernels]))
+    roof = dict(kernels[dominant])
+    roof["kernels"] = [k for i, k in enumerate(kernels) if i != dominant]
+    return roof
+
+
+def mma_rate_table(capi, iters=512):
+    """Cycles one tcgen05.mma.kind::tf32 (K = 8) occupies the tensor pipe, by M, N and source of the A operand
+    (shared memory or tensor memory), with the fraction of the full rate (2048 multiply-adds per cycle per SM)."""
+    out = []
+    for m in (128, 64):
+        for a_in_tmem in (0, 1):
+            for n in (32, 64, 96, 128, 160, 192, 224, 256):
+                issue, done = C.c_double(0), C.c_double(0)
+                capi.call("tc_issue_rate", C.c_int(m), C.c_int(n), C.c_int(a_in_tmem), C.c_int(iters), C.byref(issue), C.byref(done))
+                out.append({"M": m, "N": n, "A": "tmem" if a_in_tmem else "smem", "issue_cycles": round(issue.value, 1),
+                            "cycles_per_mma": round(done.value, 1), "frac_of_full_rate": round(m * n * 8 / 2048.0 / done.value, 3)})
+    return out
+
+
+def data_parallel_check(rt, dist, config, dims, rank, world, local_rank, nccl_id, trainer_config, trained):
+    """Correctness evidence for the multi-GPU step, run after the timed region on every rank:
+    (1) the replicas trained by the benchmark hold bit-identical parameters (compared as 32-bit patterns: an all-reduce
+        MAX must equal an all-reduce MIN);
+    (2) a fresh data-parallel trainer, three steps on per-rank shards, ends within 1e-4 (the parity tolerance, with the
+        5e-4 * lr floor the tests use after an Adam step) of one GPU trained on the concatenated batch.
+    Returns a dict for the `dp_check` key; `ok` is true only if both hold."""
+    import torch
+
+    from rusttensor_b200.workloads import workload_data
+
+    flat = np.concatenate([t.numpy().ravel() for t in trained.params]).view(np.int32)
+    hi = torch.from_numpy(flat.copy()).cuda()
+    lo = hi.clone()
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    identical = bool(torch.equal(hi, lo))
+    if config not in (1, 3):
+        # C5 clips every rank's gradient before the exchange (clip, all-reduce, Adam), which one GPU on the joint batch
+        # does not reproduce; C2 / C4 are single-GPU workloads
+        return {"ok": identical, "replicas_bit_identical": identical, "joint_batch_within_tolerance": None,
+                "what": "params after the benchmark compared across ranks as bit patterns; the joint-batch comparison only exists for C1 / C3"}
+    # (2) small per-GPU batch so that the joint batch (world x) stays cheap on one GPU
+    small = list(dims)
+    small[0] = max(4, small[0] // 8)
+    steps = 3
+    dp = rt.DataParallelTrainer(trainer_config, small, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
+    if os.environ.get("RT_B200_DP_FUSED", "0") == "1":
+        if not dp.connect_peers(dist):
+            return {"ok": False, "error": "peer-memory exchange could not be set up for the check"}
+    params, _ = workload_data(config, small, seed=0)
+    for t, p in zip(dp.params, params):
+        t.update_from_host(p)
+    for step in range(steps):
+        dp.step(workload_data(config, small, seed=100 + step, rank=rank)[1])
+        dp.last_loss()
+    got = [t.numpy() for t in dp.params]
+    worst, ok2 = 0.0, True
+    if rank == 0:
+        joint = list(small)
+        joint[0] *= world
+        one = rt.DataParallelTrainer(trainer_config, joint, device=local_rank)
+        for t, p in zip(one.params, params):
+            t.update_from_host(p)
+        for step in range(steps):
+            shards = [workload_data(config, small, seed=100 + step, rank=r)[1] for r in range(world)]
+            one.step([np.concatenate([sh[i] for sh in shards], axis=0) for i in range(len(shards[0]))])
+            one.last_loss()
+        lr = 1e-3
+        for a, b in zip(got, [t.numpy() for t in one.params]):
+            a64, b64 = a.astype(np.float64), b.astype(np.float64)
+            scale = float(np.max(np.abs(b64))) if b64.size else 0.0
+            bound = 1e-4 * np.maximum(np.abs(a64), np.abs(b64)) + 1e-6 * scale + 5e-4 * lr
+            err = np.abs(a64 - b64)
+            ok2 = ok2 and bool(np.all(err <= bound))
+            worst = max(worst, float(np.max(err / np.maximum(bound, 1e-30))) if err.size else 0.0)
+    flag = torch.tensor([1 if ok2 else 0], dtype=torch.int32, device="cuda")
+    dist.broadcast(flag, 0)
+    return {"ok": bool(identical and flag.item() == 1), "replicas_bit_identical": identical, "joint_batch_within_tolerance": bool(flag.item() == 1),
+            "worst_error_over_bound": worst, "steps": steps, "per_gpu_batch_of_check": small[0],
+            "what": "params after the benchmark compared across ranks as bit patterns; a fresh data-parallel run of 3 steps compared "
+                    "with one GPU on the concatenated batch (1e-4 relative + 1e-6 of the tensor scale + 5e-4*lr)"}
 
 
 def kernel_bandwidth_table(capi, pk, rows=4096, cols=4096):
@@ -264,6 +416,10 @@ def main():
     ap.add_argument("--kernels-size", type=int, default=4096, help="rows = cols of the matrices of --kernels")
     ap.add_argument("--kernels", action="store_true",
                     help="print the bandwidth table of the HBM-bound kernels (one GPU) instead of the training-step line")
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="how many times the --steps-long timed region is measured; the line reports the median region and the spread")
+    ap.add_argument("--mma-rate", action="store_true",
+                    help="print the issue-rate table of tcgen05.mma.kind::tf32 (cycles per MMA by shape and A-operand source)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -275,8 +431,13 @@ def main():
         args.warmup = 3
 
     import rusttensor_b200 as rt
-    from helpers import workload_data
+    from rusttensor_b200.workloads import workload_data
 
+    if args.mma_rate:
+        if rank == 0:
+            rt.init(local_rank)
+            print(json.dumps({"mma_rate": mma_rate_table(rt.CApi(ctx=rt.context_handle()))}))
+        return
     if args.kernels:
         if rank == 0:
             rt.init(local_rank)
@@ -339,30 +500,36 @@ def main():
         tr.step(None)
     barrier()
 
-    def timed(fn, k):
-        ms = C.c_float(0)
-        barrier()
-        capi.call("timer_start")
-        for _ in range(k):
-            fn()
-        capi.call("timer_stop", C.byref(ms))
-        barrier()
-        v = ms.value
-        if dist is not None:
-            import torch
+    def timed(fn, k, repeats=1):
+        """`repeats` timed regions of k calls each, every region bracketed by barrier + synchronize on both sides and
+        timed with CUDA events on the library's stream; per region the maximum over the ranks.  Returns the list."""
+        out = []
+        for _ in range(repeats):
+            ms = C.c_float(0)
+            barrier()
+            capi.call("timer_start")
+            for _ in range(k):
+                fn()
+            capi.call("timer_stop", C.byref(ms))
+            barrier()
+            v = ms.value
+            if dist is not None:
+                import torch
 
-            tt = torch.tensor([v], device="cuda")
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            v = float(tt.item())
-        return v
+                tt = torch.tensor([v], device="cuda")
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                v = float(tt.item())
+            out.append(v)
+        return out
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     lb = capi.launches()
-    ms_resident = timed(lambda: tr.step(None), args.steps)
-    gpu_launches = (capi.launches() - lb) + launches_per_replay * args.steps
+    regions = timed(lambda: tr.step(None), args.steps, repeats=args.repeats)  # each region is exactly --steps steps
+    gpu_launches = (capi.launches() - lb) // args.repeats + launches_per_replay * args.steps  # per region
     clocks = sampler.stop() if rank == 0 else None
+    ms_resident = float(np.median(regions))
 
     # End to end through the trainer's public API: every step uploads its inputs from pinned host memory and the
     # host reads every step's loss.  The trainer pipelines: while step i runs on the device the host already hands
@@ -385,7 +552,7 @@ def main():
             e2e_step()
         losses.append(tr.pipeline_flush())
 
-    ms_e2e = timed(lambda: e2e_all(args.steps), 1)
+    ms_e2e = float(np.median(timed(lambda: e2e_all(args.steps), 1, repeats=min(3, args.repeats))))
     loss = losses[-1]
     code = C.c_int(0)
     capi.call("device_status", C.byref(code))  # raises if a bounded device-side wait (MMA pipeline, peer flags) expired
@@ -403,12 +570,14 @@ def main():
             tr2.last_loss()
             for _ in range(args.warmup):
                 tr2.step(None)
-            ms2 = timed(lambda: tr2.step(None), args.steps)
+            ms2 = float(np.median(timed(lambda: tr2.step(None), args.steps, repeats=min(3, args.repeats))))
             fused_line = {"value": per_gpu * world * args.steps / (ms2 * 1e-3), "unit": "samples/s", "ms_per_step": ms2 / args.steps,
                           "note": "same network from the fused forward ops (ops::fused_relu_max_pool2d, ops::fused_softmax_nll, ops::fused_lstm_cell_c/_h)"}
             del tr2
         except Exception as e:  # noqa: BLE001  (the headline above does not depend on this extra measurement)
             fused_line = {"unavailable": str(e)}
+
+    dp_check = data_parallel_check(rt, dist, config, dims, rank, world, local_rank, nccl_id, trainer_config, tr) if world > 1 else None
 
     if rank == 0:
         pk = peaks()
@@ -427,13 +596,17 @@ def main():
             "metric": "train_samples_per_s", "value": total * args.steps / (ms_resident * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_resident / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": desc, "per_gpu_batch": per_gpu, "global_batch": total, "parallelism": f"dp{world}",
-                       "l2": f"no explicit flush: device memory in use by one step is {in_use.value / 1e6:.0f} MB (L2 is 126 MB); steps run back to back",
-                       "step": f"CUDA-graph replay of forward+backward, {exchange}, one fused optimizer launch"},
+            "config": workload_config(desc, per_gpu, world, {
+                "l2": f"no explicit flush: device memory in use by one step is {in_use.value / 1e6:.0f} MB (L2 is 126 MB); steps run back to back",
+                "step": f"CUDA-graph replay of forward+backward, {exchange}, one fused optimizer launch"}),
             "e2e": {"value": total * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(gpu_launches), "final_loss": loss, "clocks": clocks,
+            "timed_regions": {"n": len(regions), "steps_each": args.steps, "ms_per_step_median": ms_resident / args.steps,
+                              "ms_per_step_min": min(regions) / args.steps, "ms_per_step_max": max(regions) / args.steps},
         }
+        if dp_check:
+            line["dp_check"] = dp_check
         if fused_line:
             line["fused_forward"] = fused_line
         if roof:

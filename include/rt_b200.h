@@ -104,6 +104,12 @@ rt_status rt_set_tensor_cores(rt_ctx* ctx, int enable);
  * Results are bit-identical either way.  No counterpart in the reference (a scheduling switch of this backend). */
 rt_status rt_set_concurrent_backward(rt_ctx* ctx, int enable);
 
+/* Measurement aid (no counterpart in the reference): SM cycles that one tcgen05.mma.kind::tf32 of shape M x N x 8
+ * occupies the tensor pipe when `iters` of them are issued back to back by one CTA (M = 64 or 128, N <= 256).
+ * a_in_tmem != 0 takes the A operand from tensor memory instead of shared memory.  issue_cycles = time to issue,
+ * complete_cycles = time until the last one has completed, both divided by iters.  Synchronises. */
+rt_status rt_tc_issue_rate(rt_ctx* ctx, int m, int n, int a_in_tmem, int iters, double* issue_cycles, double* complete_cycles);
+
 /* CUDA-graph capture of a fixed call sequence (one training step). */
 rt_status rt_graph_begin(rt_ctx* ctx);
 rt_status rt_graph_end(rt_ctx* ctx, rt_graph** out);

@@ -1129,6 +1129,21 @@ struct CpuBackend {
     for (size_t i = 0; i < x.size(); ++i) out.data[i] = std::cos(x.data[i]) * g.data[i];
     return out;
   }
+  static Array cos_backward(const OpB& op, const Array& g) {  // src/backend/cpu.rs:2133-2159: -sin(x) * g
+    if (op.inputs.size() != 1) throw Error::internal("cos_backward expects 1 input");
+    const Array& x = op.inputs[0].data();
+    if (x.shape != g.shape) throw Error::shape_mismatch(x.shape, g.shape);
+    Array out(std::vector<float>(x.size()), x.shape);
+    for (size_t i = 0; i < x.size(); ++i) out.data[i] = -std::sin(x.data[i]) * g.data[i];
+    return out;
+  }
+  static Array tan_backward(const OpB& op, const Array& g) {  // src/backend/cpu.rs:2177-2202: g * (1 / (cos x * cos x))
+    if (op.inputs.size() != 1) throw Error::internal("tan_backward expects 1 input");
+    Array c = cos(op.inputs[0].data());
+    Array c2 = mul(c, c);
+    Array d = div(ones(c2.shape), c2);
+    return mul(g, d);
+  }
   static Array clip_backward(const OpB& op, const Array& g) {  // src/backend/cpu.rs:2396-2413
     float lo = op.op_type.min_val, hi = op.op_type.max_val;
     Array mask = map(op.inputs.at(0).data(), [lo, hi](float v) { return (v >= lo && v <= hi) ? 1.0f : 0.0f; });

@@ -616,6 +616,19 @@ Tensor<B> argmax(const Tensor<B>& x, size_t axis) { return Tensor<B>(B::argmax(x
 template <class B>
 Tensor<B> argmin(const Tensor<B>& x, size_t axis) { return Tensor<B>(B::argmin(x.data(), axis), false); }
 
+// src/ops/mod.rs:1273-1331 and equal (src/ops/mod.rs:1232-1270 family): comparisons give 1.0 / 0.0, broadcast like the
+// arithmetic ops and are not differentiable.
+#define RT_COMPARE_OP(fname)                                                                  \
+  template <class B>                                                                          \
+  Tensor<B> fname(const Tensor<B>& a, const Tensor<B>& b) { return Tensor<B>(B::fname(a.data(), b.data()), false); }
+RT_COMPARE_OP(equal)
+RT_COMPARE_OP(not_equal)
+RT_COMPARE_OP(greater)
+RT_COMPARE_OP(greater_equal)
+RT_COMPARE_OP(less)
+RT_COMPARE_OP(less_equal)
+#undef RT_COMPARE_OP
+
 // src/ops/mod.rs:1148-1158
 template <class B>
 Tensor<B> powf_scalar(const Tensor<B>& a, float b) {

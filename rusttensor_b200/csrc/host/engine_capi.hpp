@@ -89,9 +89,20 @@ Tensor<B> run_op(const std::string& name, const std::vector<Tensor<B>>& in, cons
   RT_U1(relu) RT_U1(sigmoid) RT_U1(abs) RT_U1(exp) RT_U1(ln) RT_U1(sqrt) RT_U1(tanh) RT_U1(softplus)
   RT_U1(square) RT_U1(sin) RT_U1(transpose)
   RT_R1(mean) RT_R1(sum) RT_R1(max) RT_R1(min) RT_R1(prod) RT_R1(logsumexp)
+  RT_B2(equal) RT_B2(not_equal) RT_B2(greater) RT_B2(greater_equal) RT_B2(less) RT_B2(less_equal)
 #undef RT_B2
 #undef RT_U1
 #undef RT_R1
+  // cos / tan exist only at the Backend level in the reference (src/backend/mod.rs:486-507; its ops:: front-end has no
+  // cos/tan): "backend_cos" calls B::cos, "backend_cos_backward" calls B::cos_backward with an Op holding x (inputs x, g).
+  if (name == "backend_cos") { need(1); return Tensor<B>(B::cos(in[0].data()), false); }
+  if (name == "backend_tan") { need(1); return Tensor<B>(B::tan(in[0].data()), false); }
+  if (name == "backend_cos_backward" || name == "backend_tan_backward") {
+    need(2);
+    const bool is_cos = name == "backend_cos_backward";
+    Op<B> op(OpType(is_cos ? OpType::Cos : OpType::Tan), {in[0]}, nullptr);
+    return Tensor<B>(is_cos ? B::cos_backward(op, in[1].data()) : B::tan_backward(op, in[1].data()), false);
+  }
   if (name == "elu") { need(1); return ops::elu(in[0], fpa(0)); }
   if (name == "mul_scalar") { need(1); return ops::mul_scalar(in[0], fpa(0)); }
   if (name == "div_scalar") { need(1); return ops::div_scalar(in[0], fpa(0)); }

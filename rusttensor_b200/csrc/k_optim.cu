@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(kThreads) optimizer_peer_kernel(const __grid_c
       while (*f < pa.step) {
         if (++spins > kPeerSpinLimit) {
           ok = 0;
-          atomicCAS(pa.status, 0, 16 + r);
+          if (*(volatile int*)pa.status == 0) *(volatile int*)pa.status = 16 + r;
           break;
         }
         if (spins > 32) __nanosleep(100);

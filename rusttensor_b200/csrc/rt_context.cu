@@ -37,13 +37,32 @@ rt_status rt_ctx_create(int device, rt_ctx** out) {
   }
   cudaDeviceProp prop;
   if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
-  cudaEventCreate(&ctx->ev_start);
-  cudaEventCreate(&ctx->ev_stop);
-  if (cudaMalloc(&ctx->device_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->device_status, 0, sizeof(int)) != cudaSuccess) {
+  // The status word lives in pinned host memory mapped into the device's address space: a kernel whose bounded wait
+  // expires stores its code there, and every call that synchronises (rt_sync, rt_memcpy_d2h, rt_event_synchronize,
+  // rt_timer_stop, rt_device_status) reads it afterwards without another copy.
+  void* status_host = nullptr;
+  if (cudaEventCreate(&ctx->ev_start) != cudaSuccess || cudaEventCreate(&ctx->ev_stop) != cudaSuccess ||
+      cudaHostAlloc(&status_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
+    cudaGetLastError();
+    if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
+    if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     return RT_ERR_CUDA;
   }
+  ctx->host_status = static_cast<volatile int*>(status_host);
+  *ctx->host_status = 0;
+  void* status_dev = nullptr;
+  if (cudaHostGetDevicePointer(&status_dev, status_host, 0) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFreeHost(status_host);
+    cudaEventDestroy(ctx->ev_start);
+    cudaEventDestroy(ctx->ev_stop);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return RT_ERR_CUDA;
+  }
+  ctx->device_status = static_cast<int*>(status_dev);
   const char* no_tc = getenv("RT_B200_DISABLE_TENSOR_CORES");
   if (no_tc && no_tc[0] == '1') ctx->use_tensor_cores = false;
   const char* serial = getenv("RT_B200_SERIAL_BACKWARD");
@@ -68,7 +87,7 @@ rt_status rt_ctx_destroy(rt_ctx* ctx) {
   for (auto& kv : ctx->capture_free) cudaFree(kv.second);
   for (auto& kv : ctx->side_deferred) cudaFree(kv.second);
   for (auto& kv : ctx->live_blocks) cudaFree(kv.first);
-  if (ctx->device_status) cudaFree(ctx->device_status);
+  if (ctx->host_status) cudaFreeHost(const_cast<int*>(ctx->host_status));
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
   if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
   cudaStreamDestroy(ctx->stream);
@@ -183,7 +202,7 @@ rt_status rt_memcpy_d2h(rt_ctx* ctx, void* dst, const void* src, size_t bytes) {
   RT_CHECK_PTR(ctx, src);
   RT_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
   RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  return RT_OK;
+  return rt_take_status(ctx, nullptr);
 }
 
 rt_status rt_memcpy_h2d_async(rt_ctx* ctx, void* dst, const void* src, size_t bytes) {
@@ -223,7 +242,7 @@ rt_status rt_host_free(rt_ctx* ctx, void* ptr) {
 rt_status rt_sync(rt_ctx* ctx) {
   RT_CHECK_CTX(ctx);
   RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  return RT_OK;
+  return rt_take_status(ctx, nullptr);
 }
 
 void* rt_stream(rt_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
@@ -401,19 +420,14 @@ rt_status rt_event_synchronize(rt_ctx* ctx, rt_event* ev) {
   RT_CHECK_CTX(ctx);
   RT_CHECK_PTR(ctx, ev);
   RT_CUDA(ctx, cudaEventSynchronize(ev->ev));
-  return RT_OK;
+  return rt_take_status(ctx, nullptr);
 }
 
 rt_status rt_device_status(rt_ctx* ctx, int* code) {
   RT_CHECK_CTX(ctx);
   RT_CHECK_PTR(ctx, code);
-  RT_CUDA(ctx, cudaMemcpyAsync(code, ctx->device_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
   RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-  if (*code != 0) {
-    RT_CUDA(ctx, cudaMemsetAsync(ctx->device_status, 0, sizeof(int), ctx->stream));
-    RT_FAIL(ctx, RT_ERR_TIMEOUT, "a kernel gave up a bounded wait (code %d)", *code);
-  }
-  return RT_OK;
+  return rt_take_status(ctx, code);
 }
 
 rt_status rt_set_tensor_cores(rt_ctx* ctx, int enable) {
@@ -499,7 +513,7 @@ rt_status rt_timer_stop(rt_ctx* ctx, float* ms) {
   RT_CUDA(ctx, cudaEventRecord(ctx->ev_stop, ctx->stream));
   RT_CUDA(ctx, cudaEventSynchronize(ctx->ev_stop));
   RT_CUDA(ctx, cudaEventElapsedTime(ms, ctx->ev_start, ctx->ev_stop));
-  return RT_OK;
+  return rt_take_status(ctx, nullptr);
 }
 
 // ---- NCCL, resolved at run time so that the library loads on machines without it ---

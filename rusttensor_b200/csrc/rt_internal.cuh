@@ -42,8 +42,10 @@ struct rt_ctx {
   bool side_internal = false;
   std::vector<std::pair<size_t, void*>> side_deferred;
   bool concurrent_backward = true;  // independent halves of one backward call on two streams (RT_B200_SERIAL_BACKWARD=1: off)
-  // Error word written by kernels whose bounded waits expire (0 = none); see rt_device_status.
+  // Error word written by kernels whose bounded waits expire (0 = none): one int of pinned host memory mapped into the
+  // device's address space.  device_status is what kernels get, host_status the same word as the host reads it.
   int* device_status = nullptr;
+  volatile int* host_status = nullptr;
   // Route large contractions to the tcgen05 3xTF32 kernels (k_gemm_tc.cu).
   bool use_tensor_cores = true;
   // NCCL (loaded at run time on first use)
@@ -87,6 +89,17 @@ struct rt_ctx {
       RT_FAIL(ctx, RT_ERR_CUDA, "%s: kernel launch failed: %s", __func__, cudaGetErrorString(_e)); \
     }                                                                                      \
   } while (0)
+
+// After a synchronisation: reads and clears the status word; a recorded code becomes RT_ERR_TIMEOUT.
+static inline rt_status rt_take_status(rt_ctx* ctx, int* code) {
+  const int c = ctx->host_status ? *ctx->host_status : 0;
+  if (code) *code = c;
+  if (c != 0) {
+    *ctx->host_status = 0;
+    RT_FAIL(ctx, RT_ERR_TIMEOUT, "a kernel gave up a bounded wait (code %d): its work was skipped", c);
+  }
+  return RT_OK;
+}
 
 // Scratch memory from the context pool, released when the guard goes out of scope
 // (stream-ordered, so the block may be reused by the next call).

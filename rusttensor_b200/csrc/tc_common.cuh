@@ -28,13 +28,20 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Records `code` in the context's status word (host memory mapped into the device's address space) unless an earlier
+// code is still there.  Concurrent writers may overwrite each other: any non-zero code reports the failure.
+__device__ __forceinline__ void record_status(int* status, int code) {
+  volatile int* s = status;
+  if (*s == 0) *s = code;
+  __threadfence_system();
+}
 // Bounded wait.  Returns false (and records `code`) when the barrier never completes.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try(bar, parity)) return true;
     if (i > 64) __nanosleep(64);
   }
-  atomicCAS(status, 0, code);
+  record_status(status, code);
   return false;
 }
 // Bulk asynchronous copy global -> shared memory of this CTA, completion counted in bytes on an mbarrier.

@@ -121,6 +121,13 @@ _RED = {"none": 0, "sum": 1, "mean": 2}
 
 for _n in ("matmul", "mul", "add", "sub", "div", "powf", "maximum", "minimum"):
     setattr(_Ops, _n, (lambda n: lambda self, a, b: self._run(n, [a, b]))(_n))
+for _n in ("equal", "not_equal", "greater", "greater_equal", "less", "less_equal"):  # src/ops/mod.rs:1273-1331: not differentiable
+    setattr(_Ops, _n, (lambda n: lambda self, a, b: self._run(n, [a, b]))(_n))
+# Backend::cos / tan and their backward (src/backend/mod.rs:486-507); the reference's ops:: front-end does not expose them
+_Ops.backend_cos = lambda self, x: self._run("backend_cos", [x])
+_Ops.backend_tan = lambda self, x: self._run("backend_tan", [x])
+_Ops.backend_cos_backward = lambda self, x, g: self._run("backend_cos_backward", [x, g])
+_Ops.backend_tan_backward = lambda self, x, g: self._run("backend_tan_backward", [x, g])
 for _n in ("relu", "sigmoid", "abs", "exp", "ln", "sqrt", "tanh", "softplus", "square", "sin", "transpose"):
     setattr(_Ops, _n, (lambda n: lambda self, x: self._run(n, [x]))(_n))
 for _n in ("mean", "sum", "max", "min", "prod", "logsumexp"):

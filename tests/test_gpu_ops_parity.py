@@ -129,6 +129,58 @@ def test_comparisons_and_ties(oracle_engine, gpu_engine):
     compare(both(oracle_engine, gpu_engine, lambda e, t: e.ops.minimum(t[0], t[1]), [a, b]), "minimum ties")
 
 
+COMPARISONS = ["equal", "not_equal", "greater", "greater_equal", "less", "less_equal"]
+
+
+@pytest.mark.parametrize("sa,sb", [((5, 3), (5, 3)), ((33, 257), (257,)), ((6, 5), ()), ((3, 1), (1, 4)), ((2, 3, 4, 5), (4, 5)),
+                                   ((1031,), (1031,)), ((256, 1024), (1024,)), ((0, 3), (0, 3))], ids=str)
+@pytest.mark.parametrize("op", COMPARISONS)
+def test_comparisons_forward(oracle_engine, gpu_engine, op, sa, sb):
+    """1.0 / 0.0 outputs, bit-exact against the oracle (src/backend/cpu.rs:684-898): equal / not_equal use |a-b| < 1e-9,
+    the ordered comparisons are exact.  Inputs are rounded so that many elements tie; the results carry no gradient."""
+    r = rng(41)
+    a = np.round(r.standard_normal(sa) * 2).astype(np.float32)
+    b = np.round(r.standard_normal(sb) * 2).astype(np.float32)
+    if a.size:
+        a.flat[0] = np.float32(b.flat[0] if b.size else 0.0) + np.float32(1e-10)  # inside the 1e-9 band after fp32 rounding
+    res = []
+    for e in (oracle_engine, gpu_engine):
+        y = getattr(e.ops, op)(e.tensor(a, requires_grad=True), e.tensor(b, requires_grad=True))
+        assert not y.requires_grad
+        res.append((y.shape, y.numpy()))
+    assert res[0][0] == res[1][0]
+    assert np.array_equal(res[0][1], res[1][1]), op
+    want = {"equal": np.abs(a - b) < 1e-9, "not_equal": np.abs(a - b) >= 1e-9, "greater": a > b, "greater_equal": a >= b,
+            "less": a < b, "less_equal": a <= b}[op]
+    assert np.array_equal(res[1][1], np.broadcast_to(want, res[1][0]).astype(np.float32))
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=str)
+@pytest.mark.parametrize("op", ["cos", "tan"])
+def test_backend_cos_tan_forward_backward(oracle_engine, gpu_engine, op, shape):
+    """Backend::cos / tan and cos_backward / tan_backward (src/backend/cpu.rs:2118-2202) against the oracle and against
+    float64 numpy; tan's inputs stay away from its poles."""
+    r = rng(43)
+    x = (r.uniform(-1.3, 1.3, shape) if op == "tan" else r.standard_normal(shape) * 3).astype(np.float32)
+    g = r.standard_normal(shape).astype(np.float32)
+    out = []
+    for e in (oracle_engine, gpu_engine):
+        xt, gt = e.tensor(x), e.tensor(g)
+        y = getattr(e.ops, f"backend_{op}")(xt)
+        dx = getattr(e.ops, f"backend_{op}_backward")(xt, gt)
+        assert y.shape == tuple(shape) and dx.shape == tuple(shape)
+        out.append((y.numpy(), dx.numpy()))
+    assert_close(out[1][0], out[0][0], TOL, f"{op}{shape} forward")
+    assert_close(out[1][1], out[0][1], TOL, f"{op}{shape} backward")
+    x64 = x.astype(np.float64)
+    if op == "cos":
+        assert_close(out[1][0], np.cos(x64), TOL, "cos vs float64")
+        assert_close(out[1][1], -np.sin(x64) * g, TOL, "cos_backward vs float64")
+    else:
+        assert_close(out[1][0], np.tan(x64), TOL, "tan vs float64")
+        assert_close(out[1][1], g / np.cos(x64) ** 2, TOL, "tan_backward vs float64")
+
+
 RED_SHAPES = [((5,), 0), ((5, 3), 0), ((5, 3), 1), ((2, 3, 4), 1), ((64, 10), 1), ((256, 65), 1), ((3, 4099), 1), ((4099, 3), 0),
               ((300, 2000), 0), ((2, 5000, 3), 1), ((1, 1), 1), ((7, 1), 0), ((2, 3, 4, 5), 2)]
 

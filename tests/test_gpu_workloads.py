@@ -18,7 +18,7 @@ SMALL = {
     4: [2, 3, 8, 5],
     5: [11, 8, 4, 3],
 }
-FULL = {1: [64, 784, 128, 10], 3: [256, 28, 32, 64, 128, 10]}
+FULL = {1: [64, 784, 128, 10], 2: [4096, 4096], 3: [256, 28, 32, 64, 128, 10], 4: [8, 64, 56, 128], 5: [65, 512, 128, 64]}
 
 
 def run_reference_step(engine, config, dims, params, inputs, steps=1, conv_dx_correct=False, variant=0):
@@ -96,20 +96,40 @@ def adam_first_step_bound(p_ref, g_ref, lr=1e-3, eps=1e-8, tol=TOL):
     return tol * np.abs(np.asarray(p_ref, dtype=np.float64)) + lr * eps * dg / (g + eps) ** 2 + 1e-9
 
 
-@pytest.mark.parametrize("config", [1, 3])
-def test_full_size_workload_matches_oracle(oracle_engine, gpu_engine, config):
+_FULL_ORACLE = {}
+
+
+def full_size_oracle(oracle_engine, config):
+    """One oracle pass per configuration and test session (C2 takes ~5 s, C5 ~8 s, C4 at batch 8 ~5 s on one host thread)."""
+    if config not in _FULL_ORACLE:
+        dims = FULL[config]
+        params, inputs = workload_data(config, dims, seed=2)
+        _FULL_ORACLE[config] = (params, inputs, run_reference_step(oracle_engine, config, dims, params, inputs, steps=1,
+                                                                   conv_dx_correct=config in (3, 4)))
+    return _FULL_ORACLE[config]
+
+
+@pytest.mark.parametrize("config", [1, 2, 3, 4, 5])
+def test_full_size_workload_matches_oracle(oracle_engine, gpu_engine, contraction_path, config):
+    """The benchmark configurations at the sizes they are quoted on, on both contraction paths.  C4 keeps its full channel
+    counts and 56x56 images (the shapes that select the large-channel kernels: 128-column tiles, the four stride phases of
+    the transposed convolution, the 2048-step split-K chains) but runs at batch 8 instead of 128: the oracle's
+    transposed convolution is the reference's 7-deep scalar loop nest and takes minutes at batch 128."""
     dims = FULL[config]
-    params, inputs = workload_data(config, dims, seed=2)
-    cpu = run_reference_step(oracle_engine, config, dims, params, inputs, steps=1, conv_dx_correct=(config == 3))
+    params, inputs, cpu = full_size_oracle(oracle_engine, config)
     gpu = run_reference_step(gpu_engine, config, dims, params, inputs, steps=1)
     assert_close(np.array(gpu["loss"]), np.array(cpu["loss"]), TOL, "loss")
-    for k in ("grads", "states"):
+    for k in ("grads", "states", "extra"):
+        assert len(cpu[k]) == len(gpu[k])
         for i, (a, b) in enumerate(zip(cpu[k], gpu[k])):
             assert_close(b, a, TOL, f"C{config} full {k}[{i}]")
     for i, (a, b) in enumerate(zip(cpu["params"], gpu["params"])):
-        bound = adam_first_step_bound(a, cpu["grads"][i])
-        bad = np.abs(b.astype(np.float64) - a) > bound
-        assert not bad.any(), f"C{config} full params[{i}]: {int(bad.sum())} elements outside the propagated Adam bound, worst {np.max(np.abs(b - a)[bad]):.3e}"
+        if config in (1, 3, 5):  # Adam
+            bound = adam_first_step_bound(a, cpu["grads"][i])
+            bad = np.abs(b.astype(np.float64) - a) > bound
+            assert not bad.any(), f"C{config} full params[{i}]: {int(bad.sum())} elements outside the propagated Adam bound, worst {np.max(np.abs(b - a)[bad]):.3e}"
+        else:  # momentum SGD is linear in the gradient (C4); C2 has no optimizer
+            assert_close(b, a, TOL, f"C{config} full params[{i}]", abs_floor=5e-4 * LR[config])
 
 
 @pytest.mark.parametrize("config", [1, 3, 4, 5])
