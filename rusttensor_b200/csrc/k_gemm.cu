@@ -24,6 +24,7 @@ rt_status rt_conv_forward_tc_internal(rt_ctx* ctx, const float* x, const float* 
 rt_status rt_conv_gather_tc_internal(rt_ctx* ctx, const float* y, const float* w, const float* bias, const ConvGeom& g,
                                      int cm, float* out);
 rt_status rt_conv_weight_grad_tc_internal(rt_ctx* ctx, const float* x, const float* y, const ConvGeom& g, float* dw);
+rt_status rt_conv_dw_tma_internal(rt_ctx* ctx, const float* x, const float* y, const ConvGeom& g, float* dw, float* db);
 rt_status rt_conv_forward_thin_internal(rt_ctx* ctx, const float* x, const float* w, const float* bias, const ConvGeom& g,
                                         float* y);
 rt_status rt_conv_weight_grad_thin_internal(rt_ctx* ctx, const float* x, const float* gy, const ConvGeom& g, float* dw);
@@ -507,8 +508,17 @@ rt_status conv_forward_like(rt_ctx* ctx, const float* x, const float* w, const f
 }
 
 // dw[Cy, Cx*kh*kw] = sum over (b,yo,xo) of y * im2col(x)
-rt_status conv_weight_grad_like(rt_ctx* ctx, const float* x, const float* y, const ConvGeom& g, float* dw) {
+// With `db` not null the bias gradient db[Cy] = sum over (b, pixels) of y may be produced in the same pass; *db_done
+// tells whether it was.
+rt_status conv_weight_grad_like(rt_ctx* ctx, const float* x, const float* y, const ConvGeom& g, float* dw, float* db = nullptr,
+                                bool* db_done = nullptr) {
   int64_t M = g.Cy, N = (int64_t)g.Cx * g.kh * g.kw, K = (int64_t)g.Nb * g.Hy * g.Wy;
+  if (db_done) *db_done = false;
+  if (ctx->use_tensor_cores && ctx->use_tma_weight_grad && M > 0 && N > 0 && K > 0) {  // unit stride: TMA-fed, pixels as K
+    rt_status st = rt_conv_dw_tma_internal(ctx, x, y, g, dw, db);
+    if (st == RT_OK && db && db_done) *db_done = true;
+    if (st != RT_ERR_UNIMPLEMENTED) return st;
+  }
   if (ctx->use_tensor_cores && M > 0 && N > 0 && K > 0) {  // tiny reductions: direct FP32 kernel
     rt_status st = rt_conv_weight_grad_thin_internal(ctx, x, y, g, dw);
     if (st != RT_ERR_UNIMPLEMENTED) return st;
@@ -626,14 +636,12 @@ rt_status rt_conv2d_backward(rt_ctx* ctx, const float* x, const float* w, const 
   // where it overlaps the contraction kernels.
   RtFork fork(ctx, db && (dw || dx));
   rt_status st_b = RT_OK;
-  if (db) st_b = channel_sum(ctx, gr, n, cout, (int64_t)g.Hy * g.Wy, db);
-  // with an input gradient to compute, the weight gradient joins the bias gradient on the side stream
-  if (dw && dx && fork.open) {
-    st = conv_weight_grad_like(ctx, x, gr, g, dw);
-    dw = nullptr;
-  }
+  // The weight gradient goes to the side stream with the bias gradient (its kernel may produce the bias gradient in
+  // the same pass over the upstream gradient); the input gradient stays on the main stream.
+  bool db_done = false;
+  if (dw) st = conv_weight_grad_like(ctx, x, gr, g, dw, db, &db_done);
+  if (db && !db_done) st_b = channel_sum(ctx, gr, n, cout, (int64_t)g.Hy * g.Wy, db);
   rt_status e1 = fork.end();
-  if (dw) st = conv_weight_grad_like(ctx, x, gr, g, dw);
   if (st == RT_OK && dx) {
     // positions never touched by a window (possible when stride > kernel) must read as 0:
     // the gather computes every dx element, so no pre-fill is needed.

@@ -65,6 +65,8 @@ rt_status rt_ctx_create(int device, rt_ctx** out) {
   ctx->device_status = static_cast<int*>(status_dev);
   const char* no_tc = getenv("RT_B200_DISABLE_TENSOR_CORES");
   if (no_tc && no_tc[0] == '1') ctx->use_tensor_cores = false;
+  const char* dw_tma = getenv("RT_B200_CONV_DW_TMA");
+  if (dw_tma && dw_tma[0] == '0') ctx->use_tma_weight_grad = false;
   const char* serial = getenv("RT_B200_SERIAL_BACKWARD");
   if (serial && serial[0] == '1') ctx->concurrent_backward = false;
   *out = ctx;

@@ -48,6 +48,9 @@ struct rt_ctx {
   volatile int* host_status = nullptr;
   // Route large contractions to the tcgen05 3xTF32 kernels (k_gemm_tc.cu).
   bool use_tensor_cores = true;
+  // Unit-stride convolution weight gradients through the TMA-fed kernel with the pixels as the reduction index
+  // (k_conv_dw_tc.cu); RT_B200_CONV_DW_TMA=0 keeps the general implicit-GEMM kernel.
+  bool use_tma_weight_grad = true;
   // NCCL (loaded at run time on first use)
   void* nccl_comm = nullptr;
   int dp_rank = 0, dp_world = 1;
