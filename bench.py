@@ -545,16 +545,26 @@ def main():
     # host reads every step's loss.  The trainer pipelines: while step i runs on the device the host already hands
     # over the buffers of step i+1 (their upload overlaps step i) and reads the loss of step i-1; the last loss is
     # read by pipeline_flush() inside the timed region.
-    for _ in range(2):  # fill both pinned buffer pairs, untimed
-        for i, a in enumerate(inputs):
+    # Every step gets its own batch: eight distinct batches (this rank's shard) are cycled through, each copied into
+    # the pinned buffer the trainer hands out before the step is submitted, as a data loader would.
+    # (Workloads whose batch exceeds 16 MB keep one batch: copying 200 MB per step on the host would measure memcpy.)
+    many = bool(inputs) and h2d <= (16 << 20)
+    host_batches = [inputs] + ([workload_data(config, dims, seed=1000 + k, rank=rank)[1] for k in range(7)] if many else [])
+    for k in range(2):  # fill both pinned buffer pairs, untimed
+        for i, a in enumerate(host_batches[k % len(host_batches)]):
             tr.pipeline_buffer(i)[...] = a
         tr.step_pipelined()
     tr.pipeline_flush()
     losses = []
+    e2e_count = [0]
 
     def e2e_step():
-        for i in range(len(inputs)):
-            tr.pipeline_buffer(i)          # the pinned buffer a data loader would fill for this step
+        batch = host_batches[e2e_count[0] % len(host_batches)]
+        e2e_count[0] += 1
+        for i, a in enumerate(batch):
+            buf = tr.pipeline_buffer(i)           # the pinned buffer of this step
+            if many:
+                np.copyto(buf, a)                 # filled with this step's batch
         losses.append(tr.step_pipelined())  # H2D, graph, all-reduce, optimizer, D2H of the loss; returns the previous loss
 
     def e2e_all(k):
@@ -566,6 +576,31 @@ def main():
     loss = losses[-1]
     code = C.c_int(0)
     capi.call("device_status", C.byref(code))  # raises if a bounded device-side wait (MMA pipeline, peer flags) expired
+
+    # The data set resident on the device (data::get_random_batch without its host round trip): per step the host draws
+    # the batch's row numbers and uploads those (4 bytes per sample); the rows are gathered on the device.
+    dataset_line = None
+    if config in (1, 3) and os.environ.get("RT_BENCH_SKIP_DATASET") != "1":
+        try:
+            n_rows = 16 * per_gpu
+            parts = [workload_data(config, dims, seed=2000 + k, rank=rank)[1] for k in range(16)]
+            tr.attach_dataset([np.concatenate([p_[i] for p_ in parts], axis=0) for i in range(len(inputs))])
+            r_idx = np.random.default_rng(rank)
+            tr.step_dataset(r_idx.choice(n_rows, per_gpu, replace=False))
+            tr.pipeline_flush()
+
+            def ds_all(k):
+                for _ in range(k):
+                    tr.step_dataset(r_idx.choice(n_rows, per_gpu, replace=False))
+                tr.pipeline_flush()
+
+            ms_ds = float(np.median(timed(lambda: ds_all(args.steps), 1, repeats=min(3, args.repeats))))
+            dataset_line = {"value": per_gpu * world * args.steps / (ms_ds * 1e-3), "unit": "samples/s", "ms_per_step": ms_ds / args.steps,
+                            "h2d_bytes_per_step": 4 * per_gpu * world, "d2h_bytes_per_step": 4 * world, "dataset_rows_per_gpu": n_rows,
+                            "note": "data set resident on the device; the host samples the batch's rows without replacement and uploads the row "
+                                    "numbers, the batch is gathered on the device (rt_gather_rows); every loss read on the host"}
+        except Exception as e:  # noqa: BLE001  (the headline does not depend on this extra measurement)
+            dataset_line = {"unavailable": str(e)}
 
     # The same network built from the fused forward ops (relu + max_pool2d and the classification loss as single
     # kernels), timed the same way on device-resident inputs; reported beside the headline, which keeps the reference's
@@ -619,6 +654,8 @@ def main():
             line["dp_check"] = dp_check
         if fused_line:
             line["fused_forward"] = fused_line
+        if dataset_line:
+            line["e2e_device_dataset"] = dataset_line
         if roof:
             line["roofline"] = roof
         if cpu:

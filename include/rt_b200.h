@@ -41,7 +41,8 @@ enum {
   RT_ERR_UNIMPLEMENTED = 9,       /* Error::Unimplemented */
   RT_ERR_EMPTY_TENSOR = 10,       /* Error::EmptyTensor */
   RT_ERR_TIMEOUT = 14,            /* a bounded device-side wait gave up */
-  RT_ERR_NCCL = 15
+  RT_ERR_NCCL = 15,
+  RT_ERR_INITIALIZATION = 16      /* Error::InitializationError (invalid parameters of a random factory) */
 };
 
 #define RT_MAX_DIMS 8
@@ -61,6 +62,14 @@ rt_status rt_memcpy_h2d_async(rt_ctx* ctx, void* dst, const void* pinned_src, si
 rt_status rt_memcpy_d2h_async(rt_ctx* ctx, void* pinned_dst, const void* src, size_t bytes);
 rt_status rt_memcpy_d2d(rt_ctx* ctx, void* dst, const void* src, size_t bytes);
 rt_status rt_fill(rt_ctx* ctx, float* dst, float value, int64_t n);                  /* Backend::zeros / ones (mod.rs:44,46) */
+/* Random factories: random_uniform mod.rs:63 (U[low, high)), random_normal mod.rs:66 (N(mean, std_dev^2)), bernoulli mod.rs:69
+ * (1.0 with probability p), kaiming_uniform mod.rs:57 = uniform with bound sqrt(6 / fan_in) (src/init.rs:26-32).  Element i
+ * is a pure function of (seed, offset + i / 4) (Philox-4x32-10): a call consumes (n + 3) / 4 counter values; the caller
+ * advances `offset` by that much to continue the stream.  Invalid parameters -> RT_ERR_INITIALIZATION, as rand's
+ * Uniform::new / Normal::new / Bernoulli::new fail in the reference. */
+rt_status rt_random_uniform(rt_ctx* ctx, float* out, int64_t n, float low, float high, uint64_t seed, uint64_t offset);
+rt_status rt_random_normal(rt_ctx* ctx, float* out, int64_t n, float mean, float std_dev, uint64_t seed, uint64_t offset);
+rt_status rt_bernoulli(rt_ctx* ctx, float* out, int64_t n, float p, uint64_t seed, uint64_t offset);
 rt_status rt_host_alloc(rt_ctx* ctx, size_t bytes, void** out);                      /* pinned host memory */
 rt_status rt_host_free(rt_ctx* ctx, void* ptr);
 rt_status rt_sync(rt_ctx* ctx);
@@ -178,6 +187,10 @@ rt_status rt_slice_assign(rt_ctx* ctx, float* dst, const int64_t* dst_shape, int
 /* out[i] = x[starts + i]: slice mod.rs:522, concat_backward mod.rs:563. */
 rt_status rt_slice(rt_ctx* ctx, const float* x, const int64_t* x_shape, int ndim, const int64_t* starts,
                    const int64_t* out_shape, float* out);
+
+/* out[i, :] = src[idx[i], :] (idx: n_idx int32 row numbers in DEVICE memory): the row gather of data::get_random_batch
+ * (src/data.rs:125-209), done on the device instead of through a host copy of the whole data set. */
+rt_status rt_gather_rows(rt_ctx* ctx, const float* src, int64_t rows, int64_t row_len, const int32_t* idx, int64_t n_idx, float* out);
 
 /* ---- reductions over one axis of a tensor viewed as [outer, len, inner] ----------------------- */
 enum {

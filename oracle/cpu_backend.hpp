@@ -29,6 +29,7 @@
 #include <limits>
 #include <optional>
 #include <tuple>
+#include <random>
 #include <vector>
 
 #include "../rusttensor_b200/csrc/host/autograd.hpp"
@@ -216,7 +217,61 @@ struct CpuBackend {
   using OpB = Op<CpuBackend>;
 
   // ---- factories / shape access (src/backend/cpu.rs:129-242) -------------------
+  // the gather loop of data::get_random_batch (src/data.rs:176-200): rows idx[i] of the flat host copy
+  static Array gather_rows(const Array& x, size_t rows, size_t row_len, const std::vector<size_t>& idx) {
+    Array out(std::vector<float>(idx.size() * row_len), Shape{idx.size(), row_len});
+    for (size_t i = 0; i < idx.size(); ++i) {
+      if (idx[i] >= rows || (idx[i] + 1) * row_len > x.data.size()) throw Error::internal("Index out of bounds accessing data slice");
+      std::copy(x.data.begin() + idx[i] * row_len, x.data.begin() + (idx[i] + 1) * row_len, out.data.begin() + i * row_len);
+    }
+    return out;
+  }
   static Array zeros(const Shape& s) { return Array::filled(s, 0.f); }
+  // ---- random factories (src/backend/cpu.rs:133-194, src/init.rs:7-52) -------------------------------------------
+  // rand's generator and distribution code are not part of the reference tree; what is restated here is the contract:
+  // the distributions (U[low, high), N(mean, std^2), Bernoulli(p)), the empty-shape shortcuts and the parameter checks
+  // (Uniform::new fails unless low < high and both are finite; Normal::new fails for a non-finite deviation;
+  // Bernoulli::new fails unless 0 <= p <= 1).  std::mt19937_64 stands in for rand's ChaCha-based thread_rng.
+  static std::mt19937_64& engine() {
+    static std::mt19937_64 e{std::random_device{}()};
+    return e;
+  }
+  static void manual_seed(uint64_t seed) { engine().seed(seed); }
+  static Array random_uniform(const Shape& s, float low, float high) {
+    if (shape_numel(s) == 0) return zeros(s);
+    if (!(low < high) || !std::isfinite(low) || !std::isfinite(high) || !std::isfinite(high - low))
+      throw Error(ErrorKind::InitializationError, "random_uniform: invalid range");
+    Array a(std::vector<float>(shape_numel(s)), s);
+    std::uniform_real_distribution<double> d(0.0, 1.0);
+    for (auto& v : a.data) {
+      float t = low + (high - low) * (float)d(engine());
+      v = t < high ? t : std::nextafter(high, low);
+    }
+    return a;
+  }
+  static Array random_normal(const Shape& s, float mean, float std_dev) {
+    if (shape_numel(s) == 0) return zeros(s);
+    if (!std::isfinite(std_dev)) throw Error(ErrorKind::InitializationError, "random_normal: bad variance");
+    Array a(std::vector<float>(shape_numel(s)), s);
+    std::normal_distribution<double> d(0.0, 1.0);
+    for (auto& v : a.data) v = mean + std_dev * (float)d(engine());
+    return a;
+  }
+  static Array bernoulli(const Shape& s, float p) {
+    if (shape_numel(s) == 0) return zeros(s);
+    if (!(p >= 0.f && p <= 1.f)) throw Error(ErrorKind::InitializationError, "bernoulli: probability outside [0, 1]");
+    Array a(std::vector<float>(shape_numel(s)), s);
+    std::uniform_real_distribution<double> d(0.0, 1.0);
+    for (auto& v : a.data) v = d(engine()) < (double)p ? 1.f : 0.f;
+    return a;
+  }
+  static Array kaiming_uniform(size_t fan_in, const Shape& s) {  // src/init.rs:7-52
+    if (s.empty()) throw Error::invalid_op("Cannot initialize tensor with empty shape");
+    if (shape_numel(s) == 0) return zeros(s);
+    if (fan_in == 0) throw Error::invalid_op("Fan-in cannot be zero for Kaiming initialization");
+    const float bound = std::sqrt(6.0f / (float)fan_in);
+    return random_uniform(s, -bound, bound);
+  }
   static Array ones(const Shape& s) { return Array::filled(s, 1.f); }
   static Array from_vec(std::vector<float> v, const Shape& s) {
     if (v.size() != shape_numel(s)) throw Error::shape_mismatch(s, Shape{v.size()});  // src/array.rs:29-37

@@ -15,7 +15,7 @@ BUILD = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "librt_b200.so")
 HOST_LIB = os.path.join(HERE, "librt_b200_host.so")
 
-CU_SOURCES = ["rt_context.cu", "k_elementwise.cu", "k_reduce.cu", "k_pool.cu", "k_optim.cu", "k_gemm.cu", "k_gemm_tc.cu", "k_conv_tc.cu", "k_conv_thin.cu", "k_lstm.cu", "k_tc_probe.cu", "k_conv_dw_tc.cu"]
+CU_SOURCES = ["rt_context.cu", "k_elementwise.cu", "k_reduce.cu", "k_pool.cu", "k_optim.cu", "k_gemm.cu", "k_gemm_tc.cu", "k_conv_tc.cu", "k_conv_thin.cu", "k_lstm.cu", "k_tc_probe.cu", "k_conv_dw_tc.cu", "k_random.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function"]
 

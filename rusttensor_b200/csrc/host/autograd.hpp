@@ -62,6 +62,7 @@ enum class ErrorKind : int {
   GradientCheckError = 13,
   Timeout = 14,
   Nccl = 15,
+  InitializationError = 16,
 };
 
 struct Error : public std::exception {
@@ -167,6 +168,8 @@ class Tensor {
             TensorData<B>{next_tensor_id(), std::move(data), std::nullopt, requires_grad, nullptr})) {}
 
   static Tensor zeros(const Shape& s, bool rg) { return Tensor(B::zeros(s), rg); }
+  // src/tensor.rs:953-960
+  static Tensor kaiming_uniform(size_t fan_in, const Shape& s, bool rg) { return Tensor(B::kaiming_uniform(fan_in, s), rg); }
   static Tensor ones(const Shape& s, bool rg) { return Tensor(B::ones(s), rg); }
   static Tensor from_vec(std::vector<float> v, const Shape& s, bool rg) {
     return Tensor(B::from_vec(std::move(v), s), rg);
@@ -925,6 +928,51 @@ Tensor<B> Tensor<B>::broadcast_to(const Shape& s) const { return ops::broadcast_
 // Optimizers (src/optim.rs).  Parameters without a gradient, or whose gradient
 // shape differs from the data shape, are skipped.
 // =============================================================================
+// src/data.rs:125-209.  The reference copies x and y to the host, picks `batch_size` distinct random rows there and
+// uploads the two batches; here the rows are gathered by the backend (on the device for the CUDA backend) and only the
+// indices are chosen on the host.  get_batch takes the indices, get_random_batch samples them without replacement
+// (rand::seq::index::sample in the reference; a partial Fisher-Yates shuffle of a seeded generator here).
+namespace data {
+
+template <class B>
+std::pair<Tensor<B>, Tensor<B>> get_batch(const Tensor<B>& x, const Tensor<B>& y, const std::vector<size_t>& indices) {
+  const Shape xs = x.shape(), ys = y.shape();
+  if (xs.empty() || xs[0] == 0) throw Error(ErrorKind::EmptyTensor, "Cannot perform operation on empty tensor");
+  if (ys.empty() || ys[0] == 0) throw Error(ErrorKind::EmptyTensor, "Cannot perform operation on empty tensor");
+  const size_t n = xs[0];
+  if (ys[0] != n) throw Error::shape_mismatch(Shape{n}, Shape{ys[0]});
+  if (indices.empty()) throw Error::invalid_op("Batch size cannot be zero");
+  if (indices.size() > n) throw Error(ErrorKind::DimensionMismatch, "batch size exceeds the number of samples");
+  const size_t fx = xs.size() > 1 ? xs[1] : 1, fy = ys.size() > 1 ? ys[1] : 1;  // as the reference: 1 if 1-D
+  return {Tensor<B>(B::gather_rows(x.data(), n, fx, indices), false), Tensor<B>(B::gather_rows(y.data(), n, fy, indices), false)};
+}
+
+inline std::vector<size_t> sample_indices(size_t n, size_t k, uint64_t seed) {
+  std::vector<size_t> pool(n);
+  for (size_t i = 0; i < n; ++i) pool[i] = i;
+  uint64_t s = seed;
+  auto next = [&]() {  // splitmix64
+    uint64_t z = (s += 0x9E3779B97F4A7C15ull);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+  };
+  for (size_t i = 0; i < k; ++i) std::swap(pool[i], pool[i + (size_t)(next() % (n - i))]);
+  pool.resize(k);
+  return pool;
+}
+
+template <class B>
+std::pair<Tensor<B>, Tensor<B>> get_random_batch(const Tensor<B>& x, const Tensor<B>& y, size_t batch_size, uint64_t seed) {
+  const Shape xs = x.shape();
+  if (xs.empty() || xs[0] == 0) throw Error(ErrorKind::EmptyTensor, "Cannot perform operation on empty tensor");
+  if (batch_size == 0) throw Error::invalid_op("Batch size cannot be zero");
+  if (batch_size > xs[0]) throw Error(ErrorKind::DimensionMismatch, "batch size exceeds the number of samples");
+  return get_batch(x, y, sample_indices(xs[0], batch_size, seed));
+}
+
+}  // namespace data
+
 namespace optim {
 
 template <class B>

@@ -10,7 +10,9 @@
 // update_from_host) first make the buffer unique.
 #pragma once
 #include <memory>
+#include <cmath>
 #include <optional>
+#include <random>
 #include <tuple>
 #include <vector>
 
@@ -83,6 +85,72 @@ struct B200Backend {
     Storage r = alloc(s);
     check(rt_memcpy_h2d(ctx(), r.ptr(), v.data(), sizeof(float) * v.size()));
     return r;
+  }
+  // ---- random factories (mod.rs:57-69; src/backend/cpu.rs:133-194; src/init.rs:7-52) ------------------------
+  // The generator state is (seed, counter offset); manual_seed restarts the stream.  Without a seed the first use
+  // takes one from the operating system, like rand's thread-local generator.
+  struct RngState { uint64_t seed = 0, offset = 0; bool seeded = false; };
+  static RngState& rng() {
+    static RngState s;
+    return s;
+  }
+  static void manual_seed(uint64_t seed) { rng() = RngState{seed, 0, true}; }
+  static RngState& rng_ready() {
+    RngState& s = rng();
+    if (!s.seeded) {
+      std::random_device rd;
+      s = RngState{((uint64_t)rd() << 32) ^ rd(), 0, true};
+    }
+    return s;
+  }
+  static Storage random_uniform(const Shape& shape, float low, float high) {
+    if (shape_numel(shape) == 0) return zeros(shape);
+    RngState& s = rng_ready();
+    Storage r = alloc(shape);
+    check(rt_random_uniform(ctx(), r.ptr(), (int64_t)r.numel(), low, high, s.seed, s.offset));
+    s.offset += (r.numel() + 3) / 4;
+    return r;
+  }
+  static Storage random_normal(const Shape& shape, float mean, float std_dev) {
+    if (shape_numel(shape) == 0) return zeros(shape);
+    RngState& s = rng_ready();
+    Storage r = alloc(shape);
+    check(rt_random_normal(ctx(), r.ptr(), (int64_t)r.numel(), mean, std_dev, s.seed, s.offset));
+    s.offset += (r.numel() + 3) / 4;
+    return r;
+  }
+  static Storage bernoulli(const Shape& shape, float p) {
+    if (shape_numel(shape) == 0) return zeros(shape);
+    RngState& s = rng_ready();
+    Storage r = alloc(shape);
+    check(rt_bernoulli(ctx(), r.ptr(), (int64_t)r.numel(), p, s.seed, s.offset));
+    s.offset += (r.numel() + 3) / 4;
+    return r;
+  }
+  static Storage kaiming_uniform(size_t fan_in, const Shape& shape) {  // src/init.rs:7-52
+    if (shape.empty()) throw Error::invalid_op("Cannot initialize tensor with empty shape");
+    if (shape_numel(shape) == 0) return zeros(shape);
+    if (fan_in == 0) throw Error::invalid_op("Fan-in cannot be zero for Kaiming initialization");
+    const float bound = std::sqrt(6.0f / (float)fan_in);
+    return random_uniform(shape, -bound, bound);
+  }
+  // Rows idx[i] of x viewed as [rows, row_len] -> [idx.size(), row_len] (the gather of data::get_random_batch on the
+  // device: only the indices travel).  Indices are checked on the host.
+  static Storage gather_rows(const Storage& x, size_t rows, size_t row_len, const std::vector<size_t>& idx) {
+    std::vector<int32_t> h(idx.size());
+    for (size_t i = 0; i < idx.size(); ++i) {
+      if (idx[i] >= rows) throw Error(ErrorKind::InvalidIndex, "gather_rows: index out of range");
+      h[i] = (int32_t)idx[i];
+    }
+    Storage out = alloc(Shape{idx.size(), row_len});
+    if (idx.empty() || row_len == 0) return out;
+    void* d = nullptr;
+    check(rt_malloc(ctx(), sizeof(int32_t) * h.size(), &d));
+    rt_status st = rt_memcpy_h2d(ctx(), d, h.data(), sizeof(int32_t) * h.size());
+    if (st == RT_OK) st = rt_gather_rows(ctx(), x.ptr(), (int64_t)rows, (int64_t)row_len, static_cast<const int32_t*>(d), (int64_t)h.size(), out.ptr());
+    rt_free(ctx(), d);
+    check(st);
+    return out;
   }
   static const Shape& shape(const Storage& s) { return s.shape; }
   static size_t size(const Storage& s) { return s.numel(); }

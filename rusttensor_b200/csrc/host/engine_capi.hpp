@@ -103,6 +103,15 @@ Tensor<B> run_op(const std::string& name, const std::vector<Tensor<B>>& in, cons
     Op<B> op(OpType(is_cos ? OpType::Cos : OpType::Tan), {in[0]}, nullptr);
     return Tensor<B>(is_cos ? B::cos_backward(op, in[1].data()) : B::tan_backward(op, in[1].data()), false);
   }
+  // random factories (no inputs): ip = shape (kaiming_uniform: fan_in, then the shape), fp = distribution parameters
+  if (name == "manual_seed") { need(0); B::manual_seed((uint64_t)ipa(0)); return Tensor<B>(B::zeros(Shape{}), false); }
+  if (name == "random_uniform") { need(0); return Tensor<B>(B::random_uniform(to_shape(ip.data(), (int)ip.size()), fpa(0), fpa(1)), false); }
+  if (name == "random_normal") { need(0); return Tensor<B>(B::random_normal(to_shape(ip.data(), (int)ip.size()), fpa(0), fpa(1)), false); }
+  if (name == "bernoulli") { need(0); return Tensor<B>(B::bernoulli(to_shape(ip.data(), (int)ip.size()), fpa(0)), false); }
+  if (name == "kaiming_uniform") {
+    need(0);
+    return Tensor<B>::kaiming_uniform((size_t)ipa(0), to_shape(ip.data() + 1, (int)ip.size() - 1), fpa(0) != 0.f);
+  }
   if (name == "elu") { need(1); return ops::elu(in[0], fpa(0)); }
   if (name == "mul_scalar") { need(1); return ops::mul_scalar(in[0], fpa(0)); }
   if (name == "div_scalar") { need(1); return ops::div_scalar(in[0], fpa(0)); }
@@ -225,6 +234,16 @@ int guarded(F f) {
       std::vector<int64_t> ipv(ip, ip + n_ip);                                                                \
       std::vector<double> fpv(fp, fp + n_fp);                                                                 \
       *out = r.put(rt::capi::run_op<BK>(name, in, ipv, fpv));                                                 \
+    });                                                                                                       \
+  }                                                                                                           \
+  /* data::get_batch / get_random_batch (src/data.rs:125-209): n_idx > 0 -> the given rows; else `batch` random rows */  \
+  int P##_get_batch(int64_t xh, int64_t yh, const int64_t* idx, int n_idx, int64_t batch, uint64_t seed,      \
+                    int64_t* out_x, int64_t* out_y) {                                                         \
+    return rt::capi::guarded<BK>([&](auto& r) {                                                               \
+      auto res = n_idx > 0 ? rt::data::get_batch(r.get(xh), r.get(yh), std::vector<size_t>(idx, idx + n_idx)) \
+                           : rt::data::get_random_batch(r.get(xh), r.get(yh), (size_t)batch, seed);           \
+      *out_x = r.put(res.first);                                                                              \
+      *out_y = r.put(res.second);                                                                             \
     });                                                                                                       \
   }                                                                                                           \
   int P##_backward(int64_t h) {                                                                               \

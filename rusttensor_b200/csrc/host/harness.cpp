@@ -47,6 +47,10 @@ struct DpTrainer {
   rt_graph* graph_b = nullptr;  // rest of the backward pass, when the capture was split there
   int early_lo = 0, early_hi = 0;  // parameters [early_lo, early_hi) are exchanged while graph_b runs
   bool packed_in_graph = false;    // the captured graph ends with the pack kernel
+  // Device pointers the captured graph has baked in (inputs, parameters).  A copy-on-write of one of these tensors (a
+  // view of an input or a parameter shares its buffer; make_unique then moves the tensor to a new buffer) would leave
+  // the graph reading the old buffer, so every replay first compares and re-captures when one has moved.
+  std::vector<const float*> captured_ptrs;
   bool have_loss = false;
   // exchange fused into the optimizer step over peer memory (rt_optimizer_step_multi_peers): two flat buffers that
   // alternate per step, a flag array written by the peers, and the peers' buffers as opened on this rank
@@ -61,6 +65,12 @@ struct DpTrainer {
   float* pipe_loss[2] = {nullptr, nullptr};
   rt_event* pipe_done[2] = {nullptr, nullptr};
   int64_t pipe_steps = 0;
+  // device-resident data set (data::get_random_batch without the host round trip): per step only the row numbers
+  // travel; the rows are gathered on the device straight into the step's input tensors
+  std::vector<Storage> dataset;          // one [rows, sample elements] tensor per input
+  int64_t dataset_rows = 0;
+  int32_t* idx_pinned[2] = {nullptr, nullptr};
+  Storage idx_dev[2];
   // RT_B200_DP_OVERLAP=1 sends the early gradient slice while the backward pass is still running.  Off by default:
   // with this model (1.7 MB of gradients) on two B200s the extra NCCL launch and graph launch cost more than the
   // overlap hides (0.371 ms per step against 0.362 ms).
@@ -75,6 +85,8 @@ struct DpTrainer {
       if (pipe_loss[i]) rt_host_free(c, pipe_loss[i]);
       if (pipe_done[i]) rt_event_destroy(c, pipe_done[i]);
     }
+    for (int i = 0; i < 2; ++i)
+      if (idx_pinned[i]) rt_host_free(c, idx_pinned[i]);
     if (graph) rt_graph_destroy(c, graph);
     if (graph_b) rt_graph_destroy(c, graph_b);
     for (float* p : pinned_in) rt_host_free(c, p);
@@ -344,10 +356,32 @@ struct DpTrainer {
     if (graph) graph_b = last;  // the hook closed the first part
     else graph = last;
     have_loss = true;
+    captured_ptrs = graph_pointers();
+  }
+
+  std::vector<const float*> graph_pointers() {
+    std::vector<const float*> v;
+    for (auto& x : inputs) v.push_back(x.data().ptr());
+    for (auto& p : tr->w.params) v.push_back(p.data().ptr());
+    return v;
+  }
+  void ensure_capture_is_current() {
+    if (!graph || captured_ptrs == graph_pointers()) return;
+    rt_ctx* c = B200Backend::ctx();
+    B200Backend::check(rt_sync(c));  // nothing of the stale graph may still be running
+    rt_graph_destroy(c, graph);
+    graph = nullptr;
+    if (graph_b) {
+      rt_graph_destroy(c, graph_b);
+      graph_b = nullptr;
+    }
+    packed_in_graph = false;
+    capture();
   }
 
   // One replay of the captured step, with the gradient exchange between / after the two parts.
   void replay() {
+    ensure_capture_is_current();
     rt_ctx* c = B200Backend::ctx();
     B200Backend::check(rt_graph_launch(c, graph));
     if (graph_b) {
@@ -402,6 +436,61 @@ struct DpTrainer {
     replay();
     exchange_and_update();
     const int k = (int)(pipe_steps & 1);
+    B200Backend::check(rt_memcpy_d2h_async(c, pipe_loss[k], captured_loss.data().ptr(), sizeof(float)));
+    B200Backend::check(rt_event_record(c, pipe_done[k]));
+    const bool have_prev = pipe_steps > 0;
+    if (have_prev) {
+      B200Backend::check(rt_event_synchronize(c, pipe_done[k ^ 1]));
+      *prev_loss = *pipe_loss[k ^ 1];
+    }
+    ++pipe_steps;
+    return have_prev;
+  }
+  // ---- steps fed from a data set that lives on the device ----
+  void attach_dataset(const float* const* host_arrays, int n_arrays, int64_t rows) {
+    if (n_arrays != (int)inputs.size()) throw Error::invalid_op("attach_dataset: one array per input");
+    if (rows <= 0 || rows >= (1ll << 31)) throw Error::invalid_op("attach_dataset: row count out of range");
+    dataset.clear();
+    for (int i = 0; i < n_arrays; ++i) {
+      const size_t per = inputs[i].size() / inputs[i].shape()[0];
+      Storage d = B200Backend::zeros(rt::Shape{(size_t)rows, per});
+      B200Backend::check(rt_memcpy_h2d(B200Backend::ctx(), d.ptr(), host_arrays[i], sizeof(float) * (size_t)rows * per));
+      dataset.push_back(d);
+    }
+    dataset_rows = rows;
+    const size_t batch = inputs[0].shape()[0];
+    for (int i = 0; i < 2; ++i) {
+      if (!idx_pinned[i]) {
+        void* hp = nullptr;
+        B200Backend::check(rt_host_alloc(B200Backend::ctx(), sizeof(int32_t) * batch, &hp));
+        idx_pinned[i] = (int32_t*)hp;
+      }
+      idx_dev[i] = B200Backend::zeros(rt::Shape{batch});
+    }
+  }
+  // Like step_pipelined, but the inputs are rows `indices` of the attached data set: 4 bytes per sample go to the device.
+  bool step_dataset(const int64_t* indices, int64_t n, float* prev_loss) {
+    if (dataset.empty()) throw Error::invalid_op("no data set attached");
+    const int64_t batch = (int64_t)inputs[0].shape()[0];
+    if (n != batch) throw Error(ErrorKind::DimensionMismatch, "step_dataset: one index per sample of the batch");
+    pipe_setup();
+    if (!graph) capture();
+    rt_ctx* c = B200Backend::ctx();
+    const int k = (int)(pipe_steps & 1);
+    if (pipe_steps >= 2) B200Backend::check(rt_event_synchronize(c, pipe_done[k]));  // the copy that last read this index buffer is done
+    for (int64_t i = 0; i < n; ++i) {
+      if (indices[i] < 0 || indices[i] >= dataset_rows) throw Error(ErrorKind::InvalidIndex, "step_dataset: row outside the data set");
+      idx_pinned[k][i] = (int32_t)indices[i];
+    }
+    B200Backend::check(rt_memcpy_h2d_async(c, idx_dev[k].ptr(), idx_pinned[k], sizeof(int32_t) * (size_t)n));
+    for (size_t i = 0; i < inputs.size(); ++i) {
+      B200Backend::make_unique(inputs[i].data_mut());
+      const int64_t per = (int64_t)(inputs[i].size() / (size_t)batch);
+      B200Backend::check(rt_gather_rows(c, dataset[i].ptr(), dataset_rows, per, reinterpret_cast<const int32_t*>(idx_dev[k].ptr()), n,
+                                        inputs[i].data().ptr()));
+    }
+    replay();
+    exchange_and_update();
     B200Backend::check(rt_memcpy_d2h_async(c, pipe_loss[k], captured_loss.data().ptr(), sizeof(float)));
     B200Backend::check(rt_event_record(c, pipe_done[k]));
     const bool have_prev = pipe_steps > 0;
@@ -505,6 +594,27 @@ int rth_dp_state(int64_t h, int which, int i, int64_t* out) {
     *out = r.put(Tensor(which == 0 ? d.state1.at(i) : d.state2.at(i), false));
   });
 }
+// Checkpointing: the optimizer's step counter (Adam's t) and its state tensors can be read and restored; parameters
+// are restored through rth_tensor_update_from_host on the rth_dp_param handles.
+int rth_dp_get_step(int64_t h, int64_t* t) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { *t = dp_get(h).t; });
+}
+int rth_dp_set_step(int64_t h, int64_t t) {
+  return rt::capi::guarded<B200Backend>([&](auto&) {
+    if (t < 0) throw Error::invalid_op("step counter must not be negative");
+    dp_get(h).t = t;
+  });
+}
+int rth_dp_set_state(int64_t h, int which, int i, const float* data, int64_t n) {
+  return rt::capi::guarded<B200Backend>([&](auto&) {
+    auto& d = dp_get(h);
+    auto& st = which == 0 ? d.state1.at(i) : d.state2.at(i);
+    B200Backend::update_from_host(st, std::vector<float>(data, data + n));
+  });
+}
+int rth_dp_optimizer_kind(int64_t h, int* kind) {  // 0 none, 1 Adam, 2 MomentumSGD
+  return rt::capi::guarded<B200Backend>([&](auto&) { *kind = dp_get(h).tr->w.optimizer; });
+}
 int rth_dp_set_hyper(int64_t h, const double* hp, int n) {
   return rt::capi::guarded<B200Backend>([&](auto&) {
     auto& w = dp_get(h).tr->w;
@@ -544,6 +654,15 @@ int rth_dp_pipeline_buffer(int64_t h, int i, float** out) {
 // Enqueues one step from the pipeline buffers; *has_prev tells whether *prev_loss (the previous step's loss) is valid.
 int rth_dp_step_pipelined(int64_t h, float* prev_loss, int* has_prev) {
   return rt::capi::guarded<B200Backend>([&](auto&) { *has_prev = dp_get(h).step_pipelined(prev_loss) ? 1 : 0; });
+}
+// Device-resident data set: rth_dp_attach_dataset uploads one [rows, sample] array per input once; rth_dp_step_dataset
+// enqueues a step on the rows `indices` (gathered on the device) and returns the previous step's loss like
+// rth_dp_step_pipelined.
+int rth_dp_attach_dataset(int64_t h, const float* const* host_arrays, int n_arrays, int64_t rows) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { dp_get(h).attach_dataset(host_arrays, n_arrays, rows); });
+}
+int rth_dp_step_dataset(int64_t h, const int64_t* indices, int64_t n, float* prev_loss, int* has_prev) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { *has_prev = dp_get(h).step_dataset(indices, n, prev_loss) ? 1 : 0; });
 }
 // Waits for the last pipelined step and returns its loss.
 int rth_dp_pipeline_flush(int64_t h, float* loss) {

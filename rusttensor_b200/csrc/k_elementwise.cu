@@ -634,6 +634,26 @@ rt_status binary_backward(rt_ctx* ctx, const float* a, const int64_t* as, int an
 
 }  // namespace
 
+// Row gather: one thread per 16 bytes (or per element when rows are not 16-byte multiples) of the output.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads) gather_rows_kernel(const float* __restrict__ src, int64_t rows, int64_t row_len,
+                                                               const int32_t* __restrict__ idx, int64_t n_idx, float* __restrict__ out) {
+  const int64_t per_row = VEC ? row_len / 4 : row_len;
+  const int64_t total = n_idx * per_row;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t i = t / per_row, c = t - i * per_row;
+    const int64_t r = __ldg(idx + i);
+    const bool ok = r >= 0 && r < rows;
+    if (VEC) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ok) v = __ldg(reinterpret_cast<const float4*>(src + r * row_len) + c);
+      reinterpret_cast<float4*>(out + i * row_len)[c] = v;
+    } else {
+      out[i * row_len + c] = ok ? __ldg(src + r * row_len + c) : 0.f;
+    }
+  }
+}
+
 extern "C" {
 
 rt_status rt_fill(rt_ctx* ctx, float* dst, float value, int64_t n) {
@@ -881,6 +901,27 @@ rt_status rt_slice(rt_ctx* ctx, const float* x, const int64_t* x_shape, int ndim
   RT_CHECK_PTR(ctx, x);
   RT_CHECK_PTR(ctx, out);
   box_copy_kernel<false><<<rt_grid_for(ctx, geo.numel, kThreads * 2), kThreads, 0, ctx->stream>>>(const_cast<float*>(x), out, geo);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+// out[i, :] = src[idx[i], :] for i < n_idx: the batch gather of data::get_random_batch (src/data.rs:125-209), which in the
+// reference copies the whole data set to the host, picks the rows there and uploads the batch.  `idx` is a device array;
+// an index outside [0, rows) (the host wrapper has already refused it) yields a row of zeros.
+rt_status rt_gather_rows(rt_ctx* ctx, const float* src, int64_t rows, int64_t row_len, const int32_t* idx, int64_t n_idx, float* out) {
+  RT_CHECK_CTX(ctx);
+  if (rows < 0 || row_len < 0 || n_idx < 0) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_gather_rows: negative size");
+  if (n_idx == 0 || row_len == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, src);
+  RT_CHECK_PTR(ctx, idx);
+  RT_CHECK_PTR(ctx, out);
+  if (rows >= (1ll << 31) || n_idx * row_len >= (1ll << 40)) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_gather_rows: size out of range");
+  const bool vec = (row_len % 4 == 0) && rt_aligned16(src) && rt_aligned16(out);
+  const int64_t work = n_idx * (vec ? row_len / 4 : row_len);
+  if (vec)
+    gather_rows_kernel<true><<<rt_grid_for(ctx, work, kThreads), kThreads, 0, ctx->stream>>>(src, rows, row_len, idx, n_idx, out);
+  else
+    gather_rows_kernel<false><<<rt_grid_for(ctx, work, kThreads), kThreads, 0, ctx->stream>>>(src, rows, row_len, idx, n_idx, out);
   RT_LAUNCHED(ctx);
   return RT_OK;
 }

@@ -18,7 +18,7 @@ ERROR_KINDS = {
     1: "ShapeMismatch", 2: "IncompatibleShapes", 3: "InvalidIndex", 4: "InvalidOperation",
     5: "InternalLogicError", 6: "DimensionMismatch", 7: "CudaError", 8: "OutOfMemory",
     9: "Unimplemented", 10: "EmptyTensor", 11: "ShapeError", 12: "NoGradientError",
-    13: "GradientCheckError", 14: "Timeout", 15: "Nccl",
+    13: "GradientCheckError", 14: "Timeout", 15: "Nccl", 16: "InitializationError",
 }
 
 
@@ -259,6 +259,39 @@ class Engine:
         self._call("tensor_from_host", a.ctypes.data_as(_f32p), _i64(shape), C.c_int(len(shape)),
                    C.c_int(1 if requires_grad else 0), C.byref(out))
         return Tensor(self, out.value)
+
+    # ---- random factories (Backend::random_uniform / random_normal / bernoulli / kaiming_uniform, src/backend/mod.rs:57-69) ----
+    def manual_seed(self, seed):
+        """Seeds the backend's generator (the reference draws from rand's unseedable thread-local generator)."""
+        self.op("manual_seed", [], [int(seed)])
+
+    def random_uniform(self, shape, low, high):
+        return self.op("random_uniform", [], list(shape), [low, high])
+
+    def random_normal(self, shape, mean, std_dev):
+        return self.op("random_normal", [], list(shape), [mean, std_dev])
+
+    def bernoulli(self, shape, p):
+        return self.op("bernoulli", [], list(shape), [p])
+
+    def kaiming_uniform(self, fan_in, shape, requires_grad=False):
+        """``Tensor::kaiming_uniform(fan_in, shape, requires_grad)`` (src/tensor.rs:953-960)."""
+        return self.op("kaiming_uniform", [], [int(fan_in)] + list(shape), [1.0 if requires_grad else 0.0])
+
+    # ---- data::get_random_batch (src/data.rs:125-209) ----
+    def get_batch(self, x, y, indices):
+        """Rows ``indices`` of x and y as two new tensors (gathered by the backend: on the device for CUDA)."""
+        ox, oy = C.c_int64(0), C.c_int64(0)
+        self._call("get_batch", C.c_int64(x.handle), C.c_int64(y.handle), _i64(indices), C.c_int(len(indices)), C.c_int64(0),
+                   C.c_uint64(0), C.byref(ox), C.byref(oy))
+        return Tensor(self, ox.value), Tensor(self, oy.value)
+
+    def get_random_batch(self, x, y, batch_size, seed=0):
+        """``batch_size`` distinct random rows of x and y (sampling without replacement, seeded)."""
+        ox, oy = C.c_int64(0), C.c_int64(0)
+        self._call("get_batch", C.c_int64(x.handle), C.c_int64(y.handle), _i64([]), C.c_int(0), C.c_int64(int(batch_size)),
+                   C.c_uint64(int(seed)), C.byref(ox), C.byref(oy))
+        return Tensor(self, ox.value), Tensor(self, oy.value)
 
     def op(self, name, inputs, ip=(), fp=()):
         out = C.c_int64(0)

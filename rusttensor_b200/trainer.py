@@ -70,6 +70,28 @@ class DataParallelTrainer:
     def set_hyper(self, *hp):
         self._call("dp_set_hyper", C.c_int64(self.handle), _f64(hp), C.c_int(len(hp)))
 
+    @property
+    def optimizer_kind(self):
+        """0: none, 1: Adam, 2: MomentumSGD."""
+        k = C.c_int(0)
+        self._call("dp_optimizer_kind", C.c_int64(self.handle), C.byref(k))
+        return k.value
+
+    @property
+    def step_count(self):
+        """Number of optimizer steps taken (Adam's ``t``)."""
+        t = C.c_int64(0)
+        self._call("dp_get_step", C.c_int64(self.handle), C.byref(t))
+        return t.value
+
+    @step_count.setter
+    def step_count(self, t):
+        self._call("dp_set_step", C.c_int64(self.handle), C.c_int64(int(t)))
+
+    def set_state(self, which, i, array):
+        a = np.require(array, dtype=np.float32, requirements='C')
+        self._call("dp_set_state", C.c_int64(self.handle), C.c_int(which), C.c_int(i), a.ctypes.data_as(_f32p), C.c_int64(a.size))
+
     def state(self, which, i):
         return self._tensor("dp_state", i, C.c_int(which))
 
@@ -161,6 +183,23 @@ class DataParallelTrainer:
         step (None for the first one): the host never waits for the step it has just enqueued."""
         loss, has = C.c_float(0), C.c_int(0)
         self._call("dp_step_pipelined", C.c_int64(self.handle), C.byref(loss), C.byref(has))
+        return loss.value if has.value else None
+
+    # ---- steps fed from a data set resident on the device (src/data.rs:125-209 without the host round trip) ----
+    def attach_dataset(self, arrays):
+        """``arrays``: one host array per input with the samples along axis 0 (same number of rows each); uploaded once."""
+        keep, arr = self._ptrs([np.asarray(a, dtype=np.float32).reshape(len(a), -1) for a in arrays])
+        rows = keep[0].shape[0]
+        assert all(a.shape[0] == rows for a in keep)
+        self._call("dp_attach_dataset", C.c_int64(self.handle), arr, C.c_int(len(keep)), C.c_int64(rows))
+
+    def step_dataset(self, indices):
+        """Enqueues one step on rows ``indices`` of the attached data set (only the indices are uploaded; the batch is gathered on
+        the device) and returns the loss of the previous such step (None for the first)."""
+        idx = np.require(indices, dtype=np.int64, requirements='C')
+        loss, has = C.c_float(0), C.c_int(0)
+        self._call("dp_step_dataset", C.c_int64(self.handle), idx.ctypes.data_as(C.POINTER(C.c_int64)), C.c_int64(idx.size),
+                   C.byref(loss), C.byref(has))
         return loss.value if has.value else None
 
     def pipeline_flush(self):
