@@ -325,25 +325,46 @@ rt_status rt_dp_finalize(rt_ctx* ctx);
  * order on every rank, so all ranks compute bit-identical sums) and applies the update: one kernel does the exchange
  * and the step.  Set-up: each rank exports its buffers with rt_ipc_export, the 64-byte handles travel between the
  * processes by any means, and each rank opens the others' with rt_ipc_open.
- * Per step: pack the gradients into flat[step & 1], rt_dp_signal_peers (writes `step` into slot `rank` of every peer's
- * flag array once the pack has finished), rt_optimizer_step_multi_peers.  The optimizer kernel waits, with a bounded
- * number of polls, until every peer has signalled `step`; on expiry it leaves the parameters untouched and records a
- * code in the context's status word (rt_device_status).  Two flat buffers alternate: a rank can only overwrite
- * flat[s & 1] at step s+2, after every peer has signalled step s+1 and has therefore finished reading it. */
+ * Per step: rt_dp_step_begin, (forward, backward), rt_pack_flat_alternating into flat[step & 1], rt_dp_signal_peers (writes
+ * the step number into slot `rank` of every peer's flag array once the pack has finished), rt_dp_wait_peers (one block
+ * waits, with a bounded number of polls, until every peer has signalled the step), rt_optimizer_step_multi_peers.  All of
+ * them take their step number from device memory, so the sequence can be captured once and replayed as one CUDA graph.
+ * Two flat buffers alternate: a rank can only overwrite flat[s & 1] at step s+2, after every peer has signalled step s+1
+ * and has therefore finished reading it. */
 #define RT_IPC_HANDLE_BYTES 64
 #define RT_DP_MAX_PEERS 8
 rt_status rt_ipc_export(rt_ctx* ctx, void* device_ptr, uint8_t handle[RT_IPC_HANDLE_BYTES]); /* ptr: start of an rt_malloc block */
 rt_status rt_ipc_open(rt_ctx* ctx, const uint8_t handle[RT_IPC_HANDLE_BYTES], void** peer_ptr);
 rt_status rt_ipc_close(rt_ctx* ctx, void* peer_ptr);
-/* peer_flags[r] = rank r's flag array (world ints) as opened on this rank; the entry of this rank is ignored. */
-rt_status rt_dp_signal_peers(rt_ctx* ctx, int* const* peer_flags, int rank, int world, int step);
-/* Like rt_optimizer_step_multi, with grads[i] pointing into THIS rank's flat buffer `flats[rank]`; the same offsets are
- * read from every flats[r].  local_flags = this rank's flag array.  grad_scale is normally 1/world. */
-rt_status rt_optimizer_step_multi_peers(rt_ctx* ctx, int kind, int n_tensors, float* const* params,
-                                        const float* const* grads, float* const* state1, float* const* state2,
-                                        const int64_t* sizes, float lr, float beta1, float beta2, float epsilon,
-                                        float momentum, int64_t t, float grad_scale, const float* const* flats, int rank,
-                                        int world, const int* local_flags, int step);
+/* Step state in device memory: RT_STEP_STATE_WORDS ints, zero before the first step.  word 0 = exchange step number,
+ * word 1 = step for which the peers' gradients are complete (negative: the wait for that step ran out), word 2 = optimizer
+ * step count t.  Keeping it on the device lets a whole training step - including the exchange and Adam's bias
+ * corrections - be replayed from one CUDA graph.  rt_dp_step_begin adds one to words 0 and 2. */
+#define RT_STEP_STATE_WORDS 4
+rt_status rt_dp_step_begin(rt_ctx* ctx, int* step_state);
+/* rt_optimizer_step_multi with t read from step_state (word 2) on the device. */
+rt_status rt_optimizer_step_multi_device_t(rt_ctx* ctx, int kind, int n_tensors, float* const* params, const float* const* grads,
+                                           float* const* state1, float* const* state2, const int64_t* sizes, float lr, float beta1,
+                                           float beta2, float epsilon, float momentum, const int* step_state, float grad_scale,
+                                           int clip, float clip_lo, float clip_hi);
+/* rt_pack_flat into flat0 or flat1, whichever the step number selects (buffer = step & 1). */
+rt_status rt_pack_flat_alternating(rt_ctx* ctx, int n_tensors, const float* const* srcs, const int64_t* sizes, float* flat0,
+                                   float* flat1, const int* step_state, int clip, float clip_lo, float clip_hi);
+/* peer_flags[r] = rank r's flag array (world ints) as opened on this rank; the entry of this rank is ignored.  Writes the
+ * current step number into slot `rank` of every peer's array, after everything queued before it on the stream. */
+rt_status rt_dp_signal_peers(rt_ctx* ctx, int* const* peer_flags, int rank, int world, const int* step_state);
+/* One block waits until every peer has signalled the current step (local_flags = this rank's flag array) and marks the
+ * step ready in step_state; after spin_limit polls per peer (0 = default, about ten seconds) it gives up: the step is marked
+ * failed, a code (16 + the silent rank) goes to the status word, and rt_optimizer_step_multi_peers for this step changes
+ * nothing - in none of its blocks.  The next synchronising call returns RT_ERR_TIMEOUT. */
+rt_status rt_dp_wait_peers(rt_ctx* ctx, const int* local_flags, int rank, int world, int* step_state, uint32_t spin_limit);
+/* Like rt_optimizer_step_multi_device_t, with the gradient of every element read from all ranks: grads[i] points into THIS
+ * rank's flats0[rank]; the same offsets are read from every flats0[r] (odd steps: flats1[r]) and added in rank order.
+ * grad_scale is normally 1/world.  Runs only if rt_dp_wait_peers marked the step ready. */
+rt_status rt_optimizer_step_multi_peers(rt_ctx* ctx, int kind, int n_tensors, float* const* params, const float* const* grads,
+                                        float* const* state1, float* const* state2, const int64_t* sizes, float lr, float beta1,
+                                        float beta2, float epsilon, float momentum, float grad_scale, const float* const* flats0,
+                                        const float* const* flats1, int rank, int world, const int* step_state);
 
 #ifdef __cplusplus
 }

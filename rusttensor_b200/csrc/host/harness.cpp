@@ -59,7 +59,12 @@ struct DpTrainer {
   std::vector<const float*> peer_flat[2];
   std::vector<int*> peer_flags;
   std::vector<void*> opened;
-  int64_t fused_step = 0;
+  // Step state on the device (RT_STEP_STATE_WORDS ints): exchange step, ready mark, optimizer step count.  With one
+  // GPU and with the peer-memory exchange the optimizer step (and the exchange) is part of the captured graph and reads
+  // its step numbers from here; the host's `t` is kept in step for checkpoints.
+  Storage ctrl;
+  int* ctrl_ptr() { return reinterpret_cast<int*>(ctrl.ptr()); }
+  bool update_in_stream() const { return tr->w.optimizer != 0 && (world == 1 || fused); }
   // pipelined steps: double-buffered uploads, two loss slots with completion events
   std::vector<rt_upload*> uploads;
   float* pipe_loss[2] = {nullptr, nullptr};
@@ -105,6 +110,7 @@ struct DpTrainer {
       if (w.optimizer == 1) state2.push_back(B200Backend::zeros(p.shape()));
     }
     flat_len = off;
+    ctrl = B200Backend::zeros(rt::Shape{RT_STEP_STATE_WORDS});  // all-zero bits: step 0, nothing ready, t = 0
     if (world > 1) flat = B200Backend::zeros(rt::Shape{(size_t)flat_len});
     for (auto& s : w.input_shapes) {
       // C4's first input receives a gradient ("backward to input")
@@ -131,11 +137,11 @@ struct DpTrainer {
     }
     rt_ctx* c = B200Backend::ctx();
     const int64_t begin = offsets[lo], end = hi < (int)offsets.size() ? offsets[hi] : flat_len;
-    float* dst = fused ? flat2[fused_step & 1].ptr() : flat.ptr();
+    float* dst = flat.ptr();
     if (do_pack)
       B200Backend::check(rt_pack_flat(c, hi - lo, srcs.data(), sizes.data() + lo, dst + begin, w.clip_grads ? 1 : 0, w.clip_lo,
                                       w.clip_hi));
-    if (do_reduce && !fused) B200Backend::check(rt_dp_allreduce_sum(c, dst + begin, end - begin));
+    if (do_reduce) B200Backend::check(rt_dp_allreduce_sum(c, dst + begin, end - begin));
   }
 
   // forward + backward (+ gradient exchange when world > 1); everything asynchronous.
@@ -147,12 +153,18 @@ struct DpTrainer {
   // exchange between the two replays (exchange_early / exchange_rest).
   Tensor forward_backward(bool capturing) {
     auto& w = tr->w;
+    rt_ctx* cx = B200Backend::ctx();
+    if (update_in_stream()) {
+      own_buffers();  // the launches below (and the graph, when capturing) keep these pointers
+      B200Backend::check(rt_dp_step_begin(cx, ctrl_ptr()));
+    }
     for (auto& p : w.params) p.zero_grad();
     for (auto& x : inputs) x.zero_grad();
     Tensor loss = rt::models::forward_loss(w, inputs);
     early_lo = early_hi = 0;
-    if (world == 1) {
+    if (world == 1 || fused) {
       loss.backward();
+      if (update_in_stream()) update_on_device();
       return loss;
     }
     const int n = (int)w.params.size();
@@ -211,13 +223,7 @@ struct DpTrainer {
     B200Backend::check(rt_side_stream_end(c));
   }
   void exchange_rest() {
-    if (world == 1) return;
-    if (fused) {  // pack into this step's buffer, then tell the peers it is complete; the optimizer kernel does the rest
-      fused_step += 1;
-      pack_and_reduce(0, (int)tr->w.params.size());
-      B200Backend::check(rt_dp_signal_peers(B200Backend::ctx(), peer_flags.data(), rank, world, (int)fused_step));
-      return;
-    }
+    if (world == 1 || fused) return;  // fused: pack, signal, wait and update are part of forward_backward's stream work
     if (packed_in_graph && graph) {  // replaying: the graph has already packed
       pack_and_reduce(0, (int)tr->w.params.size(), false, true);
       return;
@@ -269,39 +275,84 @@ struct DpTrainer {
     fused = true;
   }
 
+  // Parameters and optimizer state get buffers of their own (copy on write) before their pointers go into launches.
+  void own_buffers() {
+    auto& w = tr->w;
+    for (size_t i = 0; i < w.params.size(); ++i) {
+      B200Backend::make_unique(w.params[i].data_mut());
+      if (w.optimizer != 0) B200Backend::make_unique(state1[i]);
+      if (w.optimizer == 1) B200Backend::make_unique(state2[i]);
+    }
+  }
+  struct UpdatePointers {
+    std::vector<float*> ps, s1, s2;
+    std::vector<const float*> gs;
+  };
+  UpdatePointers update_pointers(const float* flat_base) {
+    auto& w = tr->w;
+    UpdatePointers u;
+    for (size_t i = 0; i < w.params.size(); ++i) {
+      auto& p = w.params[i];
+      u.ps.push_back(p.data().ptr());
+      u.s1.push_back(state1[i].ptr());
+      u.s2.push_back(w.optimizer == 1 ? state2[i].ptr() : nullptr);
+      if (flat_base) u.gs.push_back(flat_base + offsets[i]);
+      else {
+        if (!p.grad()) throw Error(ErrorKind::NoGradientError, "parameter received no gradient");
+        u.gs.push_back(p.grad()->ptr());
+      }
+    }
+    return u;
+  }
+  // The optimizer step as stream work behind the backward pass, with every step number read on the device: one GPU
+  // (fused multi-tensor launch) or the peer-memory exchange (pack into this step's flat buffer, tell the peers, wait for
+  // theirs, then read all ranks' gradients inside the optimizer kernel).  Capturable.
+  void update_on_device() {
+    auto& w = tr->w;
+    rt_ctx* c = B200Backend::ctx();
+    const int kind = w.optimizer == 1 ? 1 : 2;
+    if (!fused) {
+      UpdatePointers u = update_pointers(nullptr);
+      B200Backend::check(rt_optimizer_step_multi_device_t(c, kind, (int)u.ps.size(), u.ps.data(), u.gs.data(), u.s1.data(), u.s2.data(),
+                                                          sizes.data(), w.lr, w.beta1, w.beta2, w.eps, w.momentum, ctrl_ptr(), 1.0f,
+                                                          w.clip_grads ? 1 : 0, w.clip_lo, w.clip_hi));
+      return;
+    }
+    std::vector<const float*> srcs;
+    for (auto& p : w.params) {
+      if (!p.grad()) throw Error(ErrorKind::NoGradientError, "parameter received no gradient");
+      srcs.push_back(p.grad()->ptr());
+    }
+    B200Backend::check(rt_pack_flat_alternating(c, (int)srcs.size(), srcs.data(), sizes.data(), flat2[0].ptr(), flat2[1].ptr(), ctrl_ptr(),
+                                                w.clip_grads ? 1 : 0, w.clip_lo, w.clip_hi));
+    B200Backend::check(rt_dp_signal_peers(c, peer_flags.data(), rank, world, ctrl_ptr()));
+    B200Backend::check(rt_dp_wait_peers(c, reinterpret_cast<const int*>(flag_store.ptr()), rank, world, ctrl_ptr(), 0));
+    UpdatePointers u = update_pointers(flat2[0].ptr());
+    B200Backend::check(rt_optimizer_step_multi_peers(c, kind, (int)u.ps.size(), u.ps.data(), u.gs.data(), u.s1.data(), u.s2.data(),
+                                                     sizes.data(), w.lr, w.beta1, w.beta2, w.eps, w.momentum, 1.0f / (float)world,
+                                                     peer_flat[0].data(), peer_flat[1].data(), rank, world, ctrl_ptr()));
+  }
+
+  // After the backward pass (and the exchange): the optimizer step, unless it already is part of the stream work of
+  // forward_backward.  The host's step count moves either way.
   void exchange_and_update() {
     auto& w = tr->w;
     rt_ctx* c = B200Backend::ctx();
     if (w.optimizer == 0) return;
     t += 1;
-    std::vector<float*> ps, s1, s2;
-    std::vector<const float*> gs;
-    for (size_t i = 0; i < w.params.size(); ++i) {
-      auto& p = w.params[i];
-      B200Backend::make_unique(p.data_mut());
-      B200Backend::make_unique(state1[i]);
-      if (w.optimizer == 1) B200Backend::make_unique(state2[i]);
-      ps.push_back(p.data().ptr());
-      s1.push_back(state1[i].ptr());
-      s2.push_back(w.optimizer == 1 ? state2[i].ptr() : nullptr);
-      if (world > 1) gs.push_back((fused ? flat2[fused_step & 1].ptr() : flat.ptr()) + offsets[i]);
-      else {
-        if (!p.grad()) throw Error(ErrorKind::NoGradientError, "parameter received no gradient");
-        gs.push_back(p.grad()->ptr());
-      }
-    }
-    if (fused) {  // the gradients of all ranks are read and added inside the optimizer kernel
-      B200Backend::check(rt_optimizer_step_multi_peers(c, w.optimizer == 1 ? 1 : 2, (int)ps.size(), ps.data(), gs.data(), s1.data(),
-                                                       s2.data(), sizes.data(), w.lr, w.beta1, w.beta2, w.eps, w.momentum, t,
-                                                       1.0f / (float)world, peer_flat[fused_step & 1].data(), rank, world,
-                                                       reinterpret_cast<const int*>(flag_store.ptr()), (int)fused_step));
-      return;
-    }
-    // single GPU: clip fused here; multi GPU: the clip already happened while packing
-    int clip = (world == 1 && w.clip_grads) ? 1 : 0;
-    B200Backend::check(rt_optimizer_step_multi(c, w.optimizer == 1 ? 1 : 2, (int)ps.size(), ps.data(), gs.data(), s1.data(),
-                                               s2.data(), sizes.data(), w.lr, w.beta1, w.beta2, w.eps, w.momentum, t,
-                                               1.0f / (float)world, clip, w.clip_lo, w.clip_hi));
+    if (update_in_stream()) return;
+    own_buffers();
+    UpdatePointers u = update_pointers(flat.ptr());
+    // the clip already happened while packing
+    B200Backend::check(rt_optimizer_step_multi(c, w.optimizer == 1 ? 1 : 2, (int)u.ps.size(), u.ps.data(), u.gs.data(), u.s1.data(),
+                                               u.s2.data(), sizes.data(), w.lr, w.beta1, w.beta2, w.eps, w.momentum, t,
+                                               1.0f / (float)world, 0, w.clip_lo, w.clip_hi));
+  }
+  // Restores the optimizer's step count (checkpoints): host and device copies.
+  void set_step(int64_t v) {
+    t = v;
+    const int tv = (int)v;
+    B200Backend::check(rt_memcpy_h2d(B200Backend::ctx(), ctrl_ptr() + 2, &tv, sizeof(int)));
   }
 
   void upload_inputs(const float* const* host_inputs, int n, bool from_pinned) {
@@ -363,10 +414,40 @@ struct DpTrainer {
     std::vector<const float*> v;
     for (auto& x : inputs) v.push_back(x.data().ptr());
     for (auto& p : tr->w.params) v.push_back(p.data().ptr());
+    if (update_in_stream()) {  // the captured optimizer launch holds the state pointers too
+      for (auto& st : state1) v.push_back(st.ptr());
+      for (auto& st : state2) v.push_back(st.ptr());
+    }
     return v;
   }
+  // A parameter or state buffer that somebody else holds too (a tensor handle obtained between steps) must not be
+  // updated in place by the captured optimizer launch: such buffers are replaced by copies, which moves their pointers.
+  bool shared_update_buffers() {
+    if (!update_in_stream()) return false;
+    for (auto& p : tr->w.params)
+      if (p.data().buf && p.data().buf.use_count() > 1) return true;
+    for (auto& st : state1)
+      if (st.buf && st.buf.use_count() > 1) return true;
+    for (auto& st : state2)
+      if (st.buf && st.buf.use_count() > 1) return true;
+    return false;
+  }
+  void invalidate_capture() {
+    if (!graph) return;
+    rt_ctx* c = B200Backend::ctx();
+    B200Backend::check(rt_sync(c));
+    rt_graph_destroy(c, graph);
+    graph = nullptr;
+    if (graph_b) {
+      rt_graph_destroy(c, graph_b);
+      graph_b = nullptr;
+    }
+    packed_in_graph = false;
+  }
   void ensure_capture_is_current() {
-    if (!graph || captured_ptrs == graph_pointers()) return;
+    if (!graph) return;
+    if (shared_update_buffers()) own_buffers();
+    if (captured_ptrs == graph_pointers()) return;
     rt_ctx* c = B200Backend::ctx();
     B200Backend::check(rt_sync(c));  // nothing of the stale graph may still be running
     rt_graph_destroy(c, graph);
@@ -601,8 +682,8 @@ int rth_dp_get_step(int64_t h, int64_t* t) {
 }
 int rth_dp_set_step(int64_t h, int64_t t) {
   return rt::capi::guarded<B200Backend>([&](auto&) {
-    if (t < 0) throw Error::invalid_op("step counter must not be negative");
-    dp_get(h).t = t;
+    if (t < 0 || t >= (1ll << 31)) throw Error::invalid_op("step counter out of range");
+    dp_get(h).set_step(t);
   });
 }
 int rth_dp_set_state(int64_t h, int which, int i, const float* data, int64_t n) {
@@ -617,6 +698,7 @@ int rth_dp_optimizer_kind(int64_t h, int* kind) {  // 0 none, 1 Adam, 2 Momentum
 }
 int rth_dp_set_hyper(int64_t h, const double* hp, int n) {
   return rt::capi::guarded<B200Backend>([&](auto&) {
+    dp_get(h).invalidate_capture();  // a captured optimizer launch holds the old values
     auto& w = dp_get(h).tr->w;
     if (n > 0) w.lr = (float)hp[0];
     if (n > 1) w.beta1 = (float)hp[1];

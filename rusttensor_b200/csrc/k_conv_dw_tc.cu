@@ -38,10 +38,11 @@ constexpr int kConvWarps = 8;                      // converter / epilogue warps
 constexpr int kGroupWarps = 4, kGroupThreads = kGroupWarps * 32;  // warps 0..3 convert x rows, warps 4..7 convert g rows
 constexpr int kThreads = (kConvWarps + 2) * 32;    // + TMA warp + MMA warp
 constexpr int kCoTile = 64;
-constexpr int RG = 4, RX = 4, DA = 4;              // ring depths: raw g rows, raw x rows, A slots in tensor memory
-constexpr int kMaxDB = 8, kMaxKh = 5, kMaxKw = 4;
+constexpr int RG = 4, RX = 4;                      // ring depths: raw g rows, raw x rows
+constexpr int kMaxDA = 8;                          // A slots in tensor memory (2 * group size)
+constexpr int kMaxDB = 12, kMaxKh = 5, kMaxKw = 4;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kNumBars = 2 * RG + 2 * RX + 2 * DA + 2 * kMaxDB + 2;
+constexpr int kNumBars = 2 * RG + 2 * RX + 2 * kMaxDA + 2 * kMaxDB + 2;
 
 struct Params {
   float* ws;      // [n_combo][cpc*SEG][64][kh][kw][CIT] partial weight gradients (the accumulators' own column order)
@@ -53,6 +54,8 @@ struct Params {
   int units;      // Nb * nseg * Ho
   int BWg, BWx;   // TMA box widths (floats), 4 * odd
   int DB;         // depth of the window-row ring
+  int R;          // units the MMA warp issues back to back (one round of waits and commits per group)
+  int DA, da_shift;  // A slots in tensor memory (a power of two, 2 * R), log2
   int row_len;    // CIT * kh * kw
   uint32_t off_raw_x, off_b, off_bar;  // shared memory offsets (raw g rows start at 0)
   uint32_t raw_g_bytes, raw_x_bytes, b_img_bytes;
@@ -214,7 +217,7 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t bars = smem_base + p.off_bar;
   const uint32_t bar_gf = bars, bar_ge = bar_gf + 8 * RG, bar_xf = bar_ge + 8 * RG, bar_xe = bar_xf + 8 * RX;
-  const uint32_t bar_af = bar_xe + 8 * RX, bar_ae = bar_af + 8 * DA, bar_bf = bar_ae + 8 * DA, bar_be = bar_bf + 8 * kMaxDB;
+  const uint32_t bar_af = bar_xe + 8 * RX, bar_ae = bar_af + 8 * kMaxDA, bar_bf = bar_ae + 8 * kMaxDA, bar_be = bar_bf + 8 * kMaxDB;
   const uint32_t bar_df = bar_be + 8 * kMaxDB, bar_de = bar_df + 8;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + p.off_bar + kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -223,7 +226,7 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < RG; ++s) { mbar_init(bar_gf + 8 * s, 1); mbar_init(bar_ge + 8 * s, kGroupWarps); }
     for (int s = 0; s < RX; ++s) { mbar_init(bar_xf + 8 * s, 1); mbar_init(bar_xe + 8 * s, kGroupWarps); }
-    for (int s = 0; s < DA; ++s) { mbar_init(bar_af + 8 * s, kGroupWarps); mbar_init(bar_ae + 8 * s, 1); }
+    for (int s = 0; s < kMaxDA; ++s) { mbar_init(bar_af + 8 * s, kGroupWarps); mbar_init(bar_ae + 8 * s, 1); }
     for (int s = 0; s < kMaxDB; ++s) { mbar_init(bar_bf + 8 * s, kGroupWarps); mbar_init(bar_be + 8 * s, 1); }
     mbar_init(bar_df, 1);
     mbar_init(bar_de, kConvWarps);
@@ -291,36 +294,45 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
       for (int u = s_begin; u < s_end && ok;) {
         const Run r(p, u, s_end);
         int next_row = max(0, r.y0 - p.ph), live_lo = next_row;
-        for (int yo = r.y0; yo < r.y_end && ok; ++yo, ++i) {
-          const int top = min(p.H - 1, yo - p.ph + p.kh - 1);
+        // Groups of up to R units: one round of waits, then all their MMAs back to back, then the commits - the
+        // tensor pipe idles while this warp waits and commits, so that part is paid once per group.
+        for (int yo = r.y0; yo < r.y_end && ok;) {
+          const int rn = min(p.R, r.y_end - yo);
+          const int top = min(p.H - 1, yo + rn - 1 - p.ph + p.kh - 1);
           for (; next_row <= top && ok; ++next_row) {
             ok = __all_sync(0xffffffffu, wait_bar(bar_bf + 8 * ring.pos, ring.par, status, 34, abort_flag));
             ring.advance(p.DB);
           }
-          if (!ok) break;
-          const int sa = i % DA;
-          ok = __all_sync(0xffffffffu, wait_bar(bar_af + 8 * sa, (i / DA) & 1, status, 35, abort_flag));
+          for (int k = 0; k < rn && ok; ++k) {
+            const int sa = (i + k) & (p.DA - 1);
+            ok = __all_sync(0xffffffffu, wait_bar(bar_af + 8 * sa, ((i + k) >> p.da_shift) & 1, status, 35, abort_flag));
+          }
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_t = tmem_base + a_col0 + (uint32_t)(sa * P);
-          // the lowest live row belongs to the first valid kernel row; the following rows sit in the following slots
-          const int ky_lo = max(0, p.ph - yo), ky_hi = min(p.kh, p.H + p.ph - yo);
-          int slot = live_slot;
-          uint32_t d = tmem_base + (uint32_t)(ky_lo * p.N);
-          for (int ky = ky_lo; ky < ky_hi; ++ky, d += (uint32_t)p.N) {
-            const uint32_t b0 = b_ring + (uint32_t)slot * b_slot_units;
-            umma_ts_pair_elect(d, a_t, b0, b0 + b_img_units, b_hi32, idesc, (started >> ky) & 1u);
+          for (int k = 0; k < rn; ++k) {
+            const int y = yo + k, sa = (i + k) & (p.DA - 1);
+            const uint32_t a_t = tmem_base + a_col0 + (uint32_t)(sa * P);
+            // the rows of the window are consecutive events: the slot of a row follows from its distance to the lowest live row
+            const int ky_lo = max(0, p.ph - y), ky_hi = min(p.kh, p.H + p.ph - y);
+            int slot = live_slot + (y - p.ph + ky_lo - live_lo);
+            if (slot >= p.DB) slot -= p.DB;
+            uint32_t d = tmem_base + (uint32_t)(ky_lo * p.N);
+            for (int ky = ky_lo; ky < ky_hi; ++ky, d += (uint32_t)p.N) {
+              const uint32_t b0 = b_ring + (uint32_t)slot * b_slot_units;
+              umma_ts_pair_elect(d, a_t, b0, b0 + b_img_units, b_hi32, idesc, (started >> ky) & 1u);
 #pragma unroll
-            for (int j = 1; j < KSTEPS; ++j) umma_ts_pair_elect(d, a_t + 8 * j, b0 + 16 * j, b0 + b_img_units + 16 * j, b_hi32, idesc, 1u);
-            started |= 1u << ky;
-            if (++slot == p.DB) slot = 0;
+              for (int j = 1; j < KSTEPS; ++j) umma_ts_pair_elect(d, a_t + 8 * j, b0 + 16 * j, b0 + b_img_units + 16 * j, b_hi32, idesc, 1u);
+              started |= 1u << ky;
+              if (++slot == p.DB) slot = 0;
+            }
+            umma_commit_elect(bar_ae + 8 * sa);
           }
-          umma_commit_elect(bar_ae + 8 * sa);
-          if (live_lo < min(next_row, yo + 1 - p.ph)) {  // the top row of this unit's window is dead now
+          for (; live_lo < min(next_row, yo + rn - p.ph); ++live_lo) {  // rows above the next group's window are dead now
             umma_commit_elect(bar_be + 8 * live_slot);
-            ++live_lo;
             if (++live_slot == p.DB) live_slot = 0;
           }
+          yo += rn;
+          i += rn;
         }
         for (; live_lo < next_row; ++live_lo) {  // end of the run: the rows still live are released (the next run loads its own)
           umma_commit_elect(bar_be + 8 * live_slot);
@@ -413,9 +425,9 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
           // the g row of every unit -> an A slot in tensor memory (this thread: one output channel, hi or lo part)
           const uint32_t g_mask = r.swv >= 32 ? 0xffffffffu : ((1u << r.swv) - 1u);
           for (int yo = r.y0; yo < r.y_end && ok; ++yo, ++i) {
-            const int rs = i % RG, sa = i % DA;
+            const int rs = i % RG, sa = i & (p.DA - 1);
             ok = wait_bar(bar_gf + 8 * rs, (i / RG) & 1, status, 39, abort_flag);
-            if (ok && i >= DA) ok = wait_bar(bar_ae + 8 * sa, ((i / DA) - 1) & 1, status, 40, abort_flag);
+            if (ok && i >= p.DA) ok = wait_bar(bar_ae + 8 * sa, ((i >> p.da_shift) - 1) & 1, status, 40, abort_flag);
             if (!ok) break;
             tc_fence_after();
             const int off = (yo * p.Wo + r.c0) & 3;
@@ -596,7 +608,10 @@ rt_status rt_conv_dw_tma_internal(rt_ctx* ctx, const float* x, const float* y, c
   // input channels per tile: kh accumulators of N = kw * CIT columns plus the A slots must fit the 512 tensor-memory columns
   int cit = g.Cx >= 32 ? 32 : (g.Cx + 7) / 8 * 8;
   auto n_of = [&](int c) { return g.kw * c; };
-  while (cit >= 8 && (g.kh * n_of(cit) + DA * P > (int)kTmemCols || n_of(cit) > 256)) cit -= 8;
+  p.R = P == 32 ? 2 : 4;
+  p.DA = 2 * p.R;
+  p.da_shift = p.DA == 8 ? 3 : 2;
+  while (cit >= 8 && (g.kh * n_of(cit) + p.DA * P > (int)kTmemCols || n_of(cit) > 256)) cit -= 8;
   if (cit >= 16 && (n_of(cit) & 15)) cit = cit / 16 * 16;   // N must be a multiple of 16
   if (cit < 8 || (n_of(cit) & 15)) return RT_ERR_UNIMPLEMENTED;
   p.CIT = cit;
@@ -620,7 +635,7 @@ rt_status rt_conv_dw_tma_internal(rt_ctx* ctx, const float* x, const float* y, c
   p.raw_g_bytes = (uint32_t)(kCoTile * p.BWg * 4);
   p.raw_x_bytes = (uint32_t)(cit * p.BWx * 4);
   p.b_img_bytes = (uint32_t)(p.N * P * 4);
-  p.DB = min(kMaxDB, g.kh + 3);
+  p.DB = min(kMaxDB, g.kh - 1 + 2 * p.R);   // the window of one group plus the new rows of the next
   p.off_raw_x = RG * p.raw_g_bytes;
   p.off_b = p.off_raw_x + RX * p.raw_x_bytes;
   p.off_bar = (p.off_b + (uint32_t)p.DB * 2u * p.b_img_bytes + 127u) & ~127u;

@@ -75,7 +75,10 @@ __global__ void pack_weights_kernel(const float* __restrict__ w, float* __restri
   }
 }
 
-template <int BN>
+// CGQ = channel quads per window stage (2, 4, 6 or 8), a compile-time constant so that the producers' load / convert /
+// store loops are straight-line code: these nine warps are issue-bound, every predicate and address computation in the
+// per-element path shows up in the kernel's run time.
+template <int BN, int CGQ>
 __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p, int* status) {
   extern __shared__ __align__(128) char smem[];
   constexpr uint32_t kTmemCols = BN == 32 ? 256 : 512;  // two accumulator sets of 3*BN columns, rounded to a power of two
@@ -83,7 +86,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int taps = p.kh * p.kw;
   const uint32_t plane = (uint32_t)p.win * 16;               // bytes of one channel-quad plane
-  const uint32_t a_half = (uint32_t)p.CGQ * plane;           // hi (or lo) part of a window stage
+  const uint32_t a_half = (uint32_t)CGQ * plane;           // hi (or lo) part of a window stage
   const uint32_t a_stage = 2 * a_half;
   const uint32_t b_half = (uint32_t)p.wimg_floats * 4;       // hi (or lo) weight image
   const uint32_t tap_bytes = 2u * BN * p.NQ * 16;            // one tap: hi tile + lo tile
@@ -172,16 +175,24 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
       }
       return ps;
     };
-    struct Buf { float v[kMaxCGQ][4]; };
+    struct Buf { float v[CGQ][4]; };
     auto load = [&](const Pos& ps, int g, Buf& bf) {
-      const int c00 = g * p.CGQ * 4;
+      const int c00 = g * CGQ * 4;
+      if (ps.inside && c00 + CGQ * 4 <= p.C) {  // the common case: a whole group of real channels, no per-element tests
+        const float* src = p.src + ps.soff + c00 * hw;
 #pragma unroll
-      for (int q = 0; q < kMaxCGQ; ++q)
+        for (int q = 0; q < CGQ; ++q)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int c = c00 + q * 4 + j;
-          bf.v[q][j] = (ps.inside && q < p.CGQ && c < p.C) ? __ldg(p.src + ps.soff + c * hw) : 0.f;
-        }
+          for (int j = 0; j < 4; ++j) bf.v[q][j] = __ldg(src + (q * 4 + j) * hw);
+      } else {
+#pragma unroll
+        for (int q = 0; q < CGQ; ++q)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int c = c00 + q * 4 + j;
+            bf.v[q][j] = (ps.inside && c < p.C) ? __ldg(p.src + ps.soff + c * hw) : 0.f;
+          }
+      }
     };
     auto store = [&](int scnt, int g, const Buf& bf) -> bool {
       const int slot = scnt & 1;
@@ -189,9 +200,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
       if (tid < p.win) {
         char* a_hi = smem + off_a + slot * a_stage + (uint32_t)tid * 16;
         char* a_lo = a_hi + a_half;
-        const int nq = min(p.CGQ, p.NQ - g * p.CGQ);
+        const int nq = min(CGQ, p.NQ - g * CGQ);
 #pragma unroll
-        for (int q = 0; q < kMaxCGQ; ++q)
+        for (int q = 0; q < CGQ; ++q)
           if (q < nq) {
             float4 vh, vl;
             split4(bf.v[q], vh, vl);
@@ -263,8 +274,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
         ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * slot, (scnt >> 1) & 1, status, 7));
         if (!ok) break;
         tc_fence_after();
-        const int q0 = g * p.CGQ;
-        const int nk = min(p.CGQ, p.NQ - q0) >> 1;  // K-steps of 8 channels
+        const int q0 = g * CGQ;
+        const int nk = min(CGQ, p.NQ - q0) >> 1;  // K-steps of 8 channels
         const uint32_t a_base = desc_lo32(smem_base + off_a + slot * a_stage, plane);
         uint32_t b_tap = desc_lo32(smem_base + (uint32_t)q0 * 128, 128);
         for (int ky = 0; ky < p.kh; ++ky) {
@@ -346,13 +357,20 @@ rt_status rt_conv_window_tc_internal(rt_ctx* ctx, const float* src, int Nb, int 
                                                                                     sc, sky, skx, off0);
   RT_LAUNCHED(ctx);
   const int grid = p.tiles < ctx->sm_count ? p.tiles : ctx->sm_count;
+  auto launch = [&](auto kern) -> rt_status {
+    RT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    kern<<<grid, kThreads, smem_bytes, ctx->stream>>>(p, ctx->device_status);
+    return RT_OK;
+  };
+  rt_status ls;
   if (BN == 32) {
-    RT_CUDA(ctx, cudaFuncSetAttribute(conv_window_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-    conv_window_kernel<32><<<grid, kThreads, smem_bytes, ctx->stream>>>(p, ctx->device_status);
+    ls = p.CGQ == 2 ? launch(conv_window_kernel<32, 2>) : p.CGQ == 4 ? launch(conv_window_kernel<32, 4>)
+       : p.CGQ == 6 ? launch(conv_window_kernel<32, 6>) : launch(conv_window_kernel<32, 8>);
   } else {
-    RT_CUDA(ctx, cudaFuncSetAttribute(conv_window_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-    conv_window_kernel<64><<<grid, kThreads, smem_bytes, ctx->stream>>>(p, ctx->device_status);
+    ls = p.CGQ == 2 ? launch(conv_window_kernel<64, 2>) : p.CGQ == 4 ? launch(conv_window_kernel<64, 4>)
+       : p.CGQ == 6 ? launch(conv_window_kernel<64, 6>) : launch(conv_window_kernel<64, 8>);
   }
+  if (ls != RT_OK) return ls;
   RT_LAUNCHED(ctx);
   return RT_OK;
 }

@@ -396,3 +396,64 @@ def test_fused_lstm_cell(capi):
     capi.call("lstm_cell_c", dg_.ptr, dcp.ptr, C.c_int64(0), C.c_int64(4), c.ptr)   # empty batch: nothing to do
     with pytest.raises(RtError):
         capi.call("lstm_cell_h", dg_.ptr, dcp.ptr, C.c_int64(-1), C.c_int64(4), h.ptr)
+
+
+def test_peer_wait_runs_out_and_the_update_is_skipped_everywhere(capi):
+    """The exchange over peer memory, emulated on one GPU (both "ranks" are local buffers; nothing here waits on another
+    launch).  First the flag of rank 1 is never written: rt_dp_wait_peers gives up after its poll limit, the optimizer
+    kernel that follows changes nothing - parameters, first and second moments stay bit-identical - and the next
+    synchronising call reports RT_ERR_TIMEOUT.  Then the flag is set from the host and the same sequence applies one
+    Adam step on the sum of both ranks' gradients."""
+    from rusttensor_b200.capi import RtError
+
+    r = np.random.default_rng(5)
+    n1, n2 = 70001, 333
+    sizes = capi.i64([n1, n2])
+    pad1 = (n1 + 3) // 4 * 4
+    flat_len = pad1 + (n2 + 3) // 4 * 4
+    p_host = [r.standard_normal(n).astype(np.float32) for n in (n1, n2)]
+    g0, g1 = r.standard_normal(flat_len).astype(np.float32), r.standard_normal(flat_len).astype(np.float32)
+    params = [capi.to_device(a) for a in p_host]
+    m = [capi.to_device(np.zeros(n, np.float32)) for n in (n1, n2)]
+    v = [capi.to_device(np.zeros(n, np.float32)) for n in (n1, n2)]
+    flat0 = [capi.to_device(g0), capi.to_device(g1)]      # even steps: rank 0's and rank 1's packed gradients
+    flat1 = [capi.to_device(g1), capi.to_device(g0)]      # odd steps (the other way round, to tell the buffers apart)
+    state = capi.to_device(np.zeros(4, np.float32))       # RT_STEP_STATE_WORDS ints, all zero
+    flags = capi.to_device(np.zeros(8, np.float32))       # this rank's flag array
+    ptrs = lambda arrs: (C.c_void_p * len(arrs))(*[a.ptr for a in arrs])
+    grads = (C.c_void_p * 2)(flat0[0].ptr.value, flat0[0].ptr.value + 4 * pad1)
+
+    def step(spin_limit):
+        capi.call("dp_step_begin", state.ptr)
+        capi.call("dp_wait_peers", flags.ptr, C.c_int(0), C.c_int(2), state.ptr, C.c_uint32(spin_limit))
+        capi.call("optimizer_step_multi_peers", C.c_int(1), C.c_int(2), ptrs(params), grads, ptrs(m), ptrs(v), sizes, C.c_float(1e-3),
+                  C.c_float(0.9), C.c_float(0.999), C.c_float(1e-8), C.c_float(0.0), C.c_float(0.5), ptrs(flat0), ptrs(flat1), C.c_int(0),
+                  C.c_int(2), state.ptr)
+
+    step(spin_limit=2000)                                  # rank 1 never signals step 1
+    with pytest.raises(RtError) as ei:
+        capi.sync()
+    assert ei.value.code == 14                             # RT_ERR_TIMEOUT
+    for a, b in zip(params, p_host):
+        assert np.array_equal(a.numpy(), b)
+    assert all(not x.numpy().any() for x in m + v)
+    words = state.numpy().view(np.int32)
+    assert words[0] == 1 and words[1] == -1 and words[2] == 1
+    # rank 1 "signals" step 2; step 2 reads buffer 0 (2 & 1 == 0): gradient = (g0 + g1) / 2
+    fl = np.zeros(8, np.int32)
+    fl[1] = 2
+    capi.check(capi.lib.rt_memcpy_h2d(capi.ctx, flags.ptr, fl.ctypes.data_as(C.c_void_p), C.c_size_t(fl.nbytes)))
+    step(spin_limit=0)
+    capi.sync()
+    words = state.numpy().view(np.int32)
+    assert words[0] == 2 and words[1] == 2 and words[2] == 2
+    g = (g0 + g1) * np.float32(0.5)
+    t = 2                                                   # the optimizer step count advanced with the failed step too
+    for i, (n, off) in enumerate(((n1, 0), (n2, pad1))):
+        gi = g[off:off + n].astype(np.float32)
+        mi = np.float32(0.1) * gi
+        vi = np.float32(0.001) * (gi * gi)
+        bc1, bc2 = np.float32(1) - np.float32(0.9) ** t, np.float32(1) - np.float32(0.999) * np.float32(0.999)
+        want = p_host[i] - np.float32(1e-3) * (mi / bc1) / (np.sqrt(vi / bc2) + np.float32(1e-8))
+        assert_close(params[i].numpy(), want, 1e-5, f"peer Adam step, tensor {i}")
+        assert_close(m[i].numpy(), mi, 1e-6, "first moment")
