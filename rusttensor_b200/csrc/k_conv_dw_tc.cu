@@ -38,7 +38,7 @@ constexpr int kConvWarps = 8;                      // converter / epilogue warps
 constexpr int kGroupWarps = 4, kGroupThreads = kGroupWarps * 32;  // warps 0..3 convert x rows, warps 4..7 convert g rows
 constexpr int kThreads = (kConvWarps + 2) * 32;    // + TMA warp + MMA warp
 constexpr int kCoTile = 64;
-constexpr int RG = 4, RX = 4;                      // ring depths: raw g rows, raw x rows
+constexpr int RG = 3, RX = 3;                      // ring depths: raw g boxes, raw x boxes
 constexpr int kMaxDA = 8;                          // A slots in tensor memory (2 * group size)
 constexpr int kMaxDB = 12, kMaxKh = 5, kMaxKw = 4;
 constexpr uint32_t kTmemCols = 512;
@@ -55,6 +55,9 @@ struct Params {
   int BWg, BWx;   // TMA box widths (floats), 4 * odd
   int DB;         // depth of the window-row ring
   int R;          // units the MMA warp issues back to back (one round of waits and commits per group)
+  int GL, RB;     // units per g box / window rows per x box: R when the units of a strip are contiguous in memory (one
+                  // column segment per row), else 1.  The TMA unit spends its time per box ROW (one contiguous run per
+                  // channel), about 26 cycles each, so the runs are made as long as the layout allows.
   int DA, da_shift;  // A slots in tensor memory (a power of two, 2 * R), log2
   int row_len;    // CIT * kh * kw
   uint32_t off_raw_x, off_b, off_bar;  // shared memory offsets (raw g rows start at 0)
@@ -245,29 +248,34 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
     // ---------------------------------------------- TMA thread ----------------------------------------------
     if (lane == 0) {
       bool ok = true;
-      int i = 0, e = 0;  // units / window-row events so far
+      int gi = 0, e = 0;  // g boxes / x boxes so far
       for (int sg = 0; sg < p.SEG && ok; ++sg) {
         const int s_begin = min(u_end, u_begin + sg * seg_len), s_end = min(u_end, s_begin + seg_len);
         for (int u = s_begin; u < s_end && ok;) {
           const Run r(p, u, s_end);
           int next_row = max(0, r.y0 - p.ph);
-          for (int yo = r.y0; yo < r.y_end && ok; ++yo, ++i) {
-            const int top = min(p.H - 1, yo - p.ph + p.kh - 1);
-            for (; next_row <= top && ok; ++next_row, ++e) {
-              const int s = e % RX;
+          for (int yo = r.y0; yo < r.y_end && ok;) {  // one group of units at a time, as the MMA warp takes them
+            const int rn = min(p.R, r.y_end - yo);
+            const int top = min(p.H - 1, yo + rn - 1 - p.ph + p.kh - 1);
+            while (next_row <= top && ok) {            // x boxes: the window rows this group adds
+              const int nb = min(p.RB, top + 1 - next_row), s = e % RX;
               if (e >= RX) ok = wait_bar(bar_xe + 8 * s, ((e / RX) - 1) & 1, status, 31, abort_flag);
               if (!ok) break;
               const int e0 = next_row * p.W + r.c0 - p.pw;
               mbar_expect_tx(bar_xf + 8 * s, p.raw_x_bytes);
               tma_load_3d(smem_base + p.off_raw_x + (uint32_t)s * p.raw_x_bytes, &map_x, (e0 >> 2) << 2, cit * p.CIT, r.b, bar_xf + 8 * s);
+              next_row += nb;
+              ++e;
             }
-            if (!ok) break;
-            const int s = i % RG;
-            if (i >= RG) ok = wait_bar(bar_ge + 8 * s, ((i / RG) - 1) & 1, status, 32, abort_flag);
-            if (!ok) break;
-            const int e0 = yo * p.Wo + r.c0;
-            mbar_expect_tx(bar_gf + 8 * s, p.raw_g_bytes);
-            tma_load_3d(smem_base + (uint32_t)s * p.raw_g_bytes, &map_g, e0 & ~3, cot * kCoTile, r.b, bar_gf + 8 * s);
+            for (int k0 = 0; k0 < rn && ok; k0 += p.GL, ++gi) {  // g boxes: the rows of this group's units
+              const int s = gi % RG;
+              if (gi >= RG) ok = wait_bar(bar_ge + 8 * s, ((gi / RG) - 1) & 1, status, 32, abort_flag);
+              if (!ok) break;
+              const int e0 = (yo + k0) * p.Wo + r.c0;
+              mbar_expect_tx(bar_gf + 8 * s, p.raw_g_bytes);
+              tma_load_3d(smem_base + (uint32_t)s * p.raw_g_bytes, &map_g, e0 & ~3, cot * kCoTile, r.b, bar_gf + 8 * s);
+            }
+            yo += rn;
           }
           u += r.y_end - r.y0;
         }
@@ -389,65 +397,83 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
             it_mask[k] = m;
           }
           int next_row = max(0, r.y0 - p.ph);
-          for (int yo = r.y0; yo < r.y_end && ok; ++yo) {
-            const int top = min(p.H - 1, yo - p.ph + p.kh - 1);
-            for (; next_row <= top && ok; ++next_row, ++e) {  // window rows that become live with this unit
-              const int rs = e % RX, bs = ring.pos;
+          for (int yo = r.y0; yo < r.y_end && ok;) {
+            const int rn = min(p.R, r.y_end - yo);
+            const int top = min(p.H - 1, yo + rn - 1 - p.ph + p.kh - 1);
+            while (next_row <= top && ok) {  // one x box = up to RB window rows, each converted into its own ring slot
+              const int nb = min(p.RB, top + 1 - next_row), rs = e % RX;
               ok = wait_bar(bar_xf + 8 * rs, (e / RX) & 1, status, 37, abort_flag);
-              if (ok && ring.wrapped) ok = wait_bar(bar_be + 8 * bs, ring.par ^ 1u, status, 38, abort_flag);
-              ring.advance(p.DB);
               if (!ok) break;
-              const int off = (next_row * p.W + r.c0 - p.pw) & 3;  // distance to the 16-byte boundary below, also for -1
               const float* raw = reinterpret_cast<const float*>(smem + p.off_raw_x + (uint32_t)rs * p.raw_x_bytes);
-              char* slot = smem + p.off_b + (uint32_t)bs * 2u * p.b_img_bytes;
+              const int off0 = (next_row * p.W + r.c0 - p.pw) & 3;  // distance of the box's first element to the 16-byte boundary below
+              for (int k = 0; k < nb && ok; ++k) {
+                const int bs = ring.pos;
+                if (ring.wrapped) ok = wait_bar(bar_be + 8 * bs, ring.par ^ 1u, status, 38, abort_flag);
+                ring.advance(p.DB);
+                if (!ok) break;
+                const int el = off0 + k * p.W, off = el & 3;
+                const float* row = raw + (el & ~3);
+                char* slot = smem + p.off_b + (uint32_t)bs * 2u * p.b_img_bytes;
 #pragma unroll
-              for (int k = 0; k < 2; ++k) {
-                if (it_c4[k] >= 0) {
-                  const float* src = raw + it_src[k];
-                  char* dst = slot + it_dst[k];
-                  switch (off) {
-                    case 0: convert_x_item<0>(src, it_mask[k], p.kw, dst, kx_step, p.b_img_bytes); break;
-                    case 1: convert_x_item<1>(src, it_mask[k], p.kw, dst, kx_step, p.b_img_bytes); break;
-                    case 2: convert_x_item<2>(src, it_mask[k], p.kw, dst, kx_step, p.b_img_bytes); break;
-                    default: convert_x_item<3>(src, it_mask[k], p.kw, dst, kx_step, p.b_img_bytes); break;
+                for (int k2 = 0; k2 < 2; ++k2) {
+                  if (it_c4[k2] >= 0) {
+                    const float* src = row + it_src[k2];
+                    char* dst = slot + it_dst[k2];
+                    switch (off) {
+                      case 0: convert_x_item<0>(src, it_mask[k2], p.kw, dst, kx_step, p.b_img_bytes); break;
+                      case 1: convert_x_item<1>(src, it_mask[k2], p.kw, dst, kx_step, p.b_img_bytes); break;
+                      case 2: convert_x_item<2>(src, it_mask[k2], p.kw, dst, kx_step, p.b_img_bytes); break;
+                      default: convert_x_item<3>(src, it_mask[k2], p.kw, dst, kx_step, p.b_img_bytes); break;
+                    }
                   }
                 }
+                fence_async_smem();  // the tensor core reads these stores through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_bf + 8 * bs);
               }
-              fence_async_smem();  // the tensor core reads these stores through the async proxy
               __syncwarp();
-              if (lane == 0) {
-                mbar_arrive(bar_bf + 8 * bs);
-                mbar_arrive(bar_xe + 8 * rs);
-              }
+              if (lane == 0) mbar_arrive(bar_xe + 8 * rs);
+              next_row += nb;
+              ++e;
             }
+            yo += rn;
           }
         } else {
           // the g row of every unit -> an A slot in tensor memory (this thread: one output channel, hi or lo part)
           const uint32_t g_mask = r.swv >= 32 ? 0xffffffffu : ((1u << r.swv) - 1u);
-          for (int yo = r.y0; yo < r.y_end && ok; ++yo, ++i) {
-            const int rs = i % RG, sa = i & (p.DA - 1);
-            ok = wait_bar(bar_gf + 8 * rs, (i / RG) & 1, status, 39, abort_flag);
-            if (ok && i >= p.DA) ok = wait_bar(bar_ae + 8 * sa, ((i >> p.da_shift) - 1) & 1, status, 40, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            const int off = (yo * p.Wo + r.c0) & 3;
-            const float* rr = reinterpret_cast<const float*>(smem + (uint32_t)rs * p.raw_g_bytes) + co_l * p.BWg;
-            const uint32_t taddr = tmem_base + t_lane + a_col0 + (uint32_t)(sa * P);
-            float sum;
-            switch (off) {
-              case 0: sum = convert_g_row<P, 0>(rr, g_mask, part, taddr); break;
-              case 1: sum = convert_g_row<P, 1>(rr, g_mask, part, taddr); break;
-              case 2: sum = convert_g_row<P, 2>(rr, g_mask, part, taddr); break;
-              default: sum = convert_g_row<P, 3>(rr, g_mask, part, taddr); break;
+          for (int yo = r.y0; yo < r.y_end && ok;) {
+            const int rn = min(p.R, r.y_end - yo);
+            for (int k0 = 0; k0 < rn && ok; k0 += p.GL, ++e) {  // one g box = the rows of up to GL units (e counts g boxes here)
+              const int rs = e % RG, nu = min(p.GL, rn - k0);
+              ok = wait_bar(bar_gf + 8 * rs, (e / RG) & 1, status, 39, abort_flag);
+              if (!ok) break;
+              const float* raw = reinterpret_cast<const float*>(smem + (uint32_t)rs * p.raw_g_bytes) + co_l * p.BWg;
+              const int off0 = ((yo + k0) * p.Wo + r.c0) & 3;
+              for (int k = 0; k < nu && ok; ++k, ++i) {
+                const int sa = i & (p.DA - 1);
+                if (i >= p.DA) ok = wait_bar(bar_ae + 8 * sa, ((i >> p.da_shift) - 1) & 1, status, 40, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const int el = off0 + k * p.Wo, off = el & 3;
+                const float* rr = raw + (el & ~3);
+                const uint32_t taddr = tmem_base + t_lane + a_col0 + (uint32_t)(sa * P);
+                float sum;
+                switch (off) {
+                  case 0: sum = convert_g_row<P, 0>(rr, g_mask, part, taddr); break;
+                  case 1: sum = convert_g_row<P, 1>(rr, g_mask, part, taddr); break;
+                  case 2: sum = convert_g_row<P, 2>(rr, g_mask, part, taddr); break;
+                  default: sum = convert_g_row<P, 3>(rr, g_mask, part, taddr); break;
+                }
+                db_acc += sum;
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_af + 8 * sa);
+              }
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar_ge + 8 * rs);
             }
-            db_acc += sum;
-            tmem_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-              mbar_arrive(bar_af + 8 * sa);
-              mbar_arrive(bar_ge + 8 * rs);
-            }
+            yo += rn;
           }
         }
         u += r.y_end - r.y0;
@@ -498,14 +524,15 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
 }
 
 // dw[co, ci, ky, kx] = sum of the partials in a fixed order.  A block covers 32 consecutive elements of a partial tile
-// ([64 channels][ky][kx][ci], the accumulators' own order) times 32 groups of partials: every thread adds its few
-// partials, then the 32 group sums of an element are added in order and written to the element's place in dw.  The
+// ([64 channels][ky][kx][ci], the accumulators' own order) times 8 groups of partials: every thread adds its few
+// partials, then the 8 group sums of an element are added in order and written to the element's place in dw.  The
 // bias-gradient partials ([channel tile][CTA][64]) are further "elements" behind the last tile.
-__global__ void __launch_bounds__(1024) conv_dw_finish_kernel(const float* __restrict__ ws, const float* __restrict__ ws_db,
+template <int GROUPS>
+__global__ void __launch_bounds__(32 * GROUPS) conv_dw_finish_kernel(const float* __restrict__ ws, const float* __restrict__ ws_db,
                                                                float* __restrict__ dw, float* __restrict__ db, int Cout, int Cin,
                                                                int kh, int kw, int CIT, int n_cit, int NP, int cpc, int tile_elems,
                                                                int dw_elems, int db_elems) {
-  __shared__ float red[32][33];
+  __shared__ float red[GROUPS][33];
   const int lane_o = threadIdx.x & 31, grp = threadIdx.x >> 5;
   const int o = (int)blockIdx.x * 32 + lane_o;
   const float* src = nullptr;
@@ -533,12 +560,14 @@ __global__ void __launch_bounds__(1024) conv_dw_finish_kernel(const float* __res
   }
   float acc = 0.f;
   if (out) {
-    const int per = (n_part + 31) / 32, p0 = grp * per, p1 = min(n_part, p0 + per);
+    const int per = (n_part + GROUPS - 1) / GROUPS, p0 = grp * per, p1 = min(n_part, p0 + per);
     int pp = p0;
-    for (; pp + 4 <= p1; pp += 4) {
-      const float a = __ldg(src + pp * stride), b = __ldg(src + (pp + 1) * stride), c = __ldg(src + (pp + 2) * stride),
-                  d = __ldg(src + (pp + 3) * stride);
-      acc += a; acc += b; acc += c; acc += d;
+    for (; pp + 8 <= p1; pp += 8) {  // eight loads in flight per thread
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __ldg(src + (pp + j) * stride);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += v[j];
     }
     for (; pp < p1; ++pp) acc += __ldg(src + pp * stride);
   }
@@ -547,7 +576,7 @@ __global__ void __launch_bounds__(1024) conv_dw_finish_kernel(const float* __res
   if (grp == 0 && out) {
     float s = red[0][lane_o];
 #pragma unroll
-    for (int g2 = 1; g2 < 32; ++g2) s += red[g2][lane_o];
+    for (int g2 = 1; g2 < GROUPS; ++g2) s += red[g2][lane_o];
     *out = s;
   }
 }
@@ -630,8 +659,14 @@ rt_status rt_conv_dw_tma_internal(rt_ctx* ctx, const float* x, const float* y, c
   const int seg_units = max(1, 1024 / (2 * (P / 8)));
   p.SEG = (per + seg_units - 1) / seg_units;
   p.row_len = cit * g.kh * g.kw;
-  p.BWg = odd_quads(P + 4);
-  p.BWx = odd_quads(P + 8);
+  p.GL = p.RB = p.nseg == 1 ? p.R : 1;
+  p.BWg = odd_quads(3 + (p.GL - 1) * p.Wo + P + 4);   // what convert_g_row reads of the last row of a box
+  p.BWx = odd_quads(3 + (p.RB - 1) * p.W + P + 8);    // ... and convert_x_item
+  if (p.BWg > 256 || p.BWx > 256) {  // a TMA box is at most 256 elements wide
+    p.GL = p.RB = 1;
+    p.BWg = odd_quads(P + 4);
+    p.BWx = odd_quads(P + 8);
+  }
   p.raw_g_bytes = (uint32_t)(kCoTile * p.BWg * 4);
   p.raw_x_bytes = (uint32_t)(cit * p.BWx * 4);
   p.b_img_bytes = (uint32_t)(p.N * P * 4);
@@ -667,7 +702,7 @@ rt_status rt_conv_dw_tma_internal(rt_ctx* ctx, const float* x, const float* y, c
   st = P == 8 ? launch(conv_dw_kernel<8>) : (P == 16 ? launch(conv_dw_kernel<16>) : launch(conv_dw_kernel<32>));
   if (st != RT_OK) return st;
   const int tile_elems = kCoTile * p.row_len, dw_elems = p.n_combo * tile_elems, db_elems = db ? p.n_cot * kCoTile : 0;
-  conv_dw_finish_kernel<<<(dw_elems + db_elems + 31) / 32, 1024, 0, ctx->stream>>>(p.ws, p.ws_db, dw, db, g.Cy, g.Cx, g.kh, g.kw, cit, p.n_cit,
+  conv_dw_finish_kernel<8><<<(dw_elems + db_elems + 31) / 32, 256, 0, ctx->stream>>>(p.ws, p.ws_db, dw, db, g.Cy, g.Cx, g.kh, g.kw, cit, p.n_cit,
                                                                                 NP, p.cpc, tile_elems, dw_elems, db_elems);
   RT_LAUNCHED(ctx);
   return RT_OK;
