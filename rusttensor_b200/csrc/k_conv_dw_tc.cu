@@ -406,19 +406,14 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
               if (!ok) break;
               const float* raw = reinterpret_cast<const float*>(smem + p.off_raw_x + (uint32_t)rs * p.raw_x_bytes);
               const int off0 = (next_row * p.W + r.c0 - p.pw) & 3;  // distance of the box's first element to the 16-byte boundary below
-              // Every row of the box goes into its own ring slot; the slots are claimed first (their previous contents
-              // must have been consumed), then all rows are converted back to back and published with one fence.
-              int slots[4];
               for (int k = 0; k < nb && ok; ++k) {
-                slots[k] = ring.pos;
-                if (ring.wrapped) ok = wait_bar(bar_be + 8 * ring.pos, ring.par ^ 1u, status, 38, abort_flag);
+                const int bs = ring.pos;
+                if (ring.wrapped) ok = wait_bar(bar_be + 8 * bs, ring.par ^ 1u, status, 38, abort_flag);
                 ring.advance(p.DB);
-              }
-              if (!ok) break;
-              for (int k = 0; k < nb; ++k) {
+                if (!ok) break;
                 const int el = off0 + k * p.W, off = el & 3;
                 const float* row = raw + (el & ~3);
-                char* slot = smem + p.off_b + (uint32_t)slots[k] * 2u * p.b_img_bytes;
+                char* slot = smem + p.off_b + (uint32_t)bs * 2u * p.b_img_bytes;
 #pragma unroll
                 for (int k2 = 0; k2 < 2; ++k2) {
                   if (it_c4[k2] >= 0) {
@@ -432,13 +427,12 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
                     }
                   }
                 }
+                fence_async_smem();  // the tensor core reads these stores through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_bf + 8 * bs);
               }
-              fence_async_smem();  // the tensor core reads these stores through the async proxy
               __syncwarp();
-              if (lane == 0) {
-                for (int k = 0; k < nb; ++k) mbar_arrive(bar_bf + 8 * slots[k]);
-                mbar_arrive(bar_xe + 8 * rs);
-              }
+              if (lane == 0) mbar_arrive(bar_xe + 8 * rs);
               next_row += nb;
               ++e;
             }
@@ -455,15 +449,11 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
               if (!ok) break;
               const float* raw = reinterpret_cast<const float*>(smem + (uint32_t)rs * p.raw_g_bytes) + co_l * p.BWg;
               const int off0 = ((yo + k0) * p.Wo + r.c0) & 3;
-              // claim the A slots of the box's units, convert all of them, then one wait for the tensor-memory stores
-              for (int k = 0; k < nu && ok; ++k) {
-                const int iu = i + k, sa = iu & (p.DA - 1);
-                if (iu >= p.DA) ok = wait_bar(bar_ae + 8 * sa, ((iu >> p.da_shift) - 1) & 1, status, 40, abort_flag);
-              }
-              if (!ok) break;
-              tc_fence_after();
-              for (int k = 0; k < nu; ++k) {
-                const int sa = (i + k) & (p.DA - 1);
+              for (int k = 0; k < nu && ok; ++k, ++i) {
+                const int sa = i & (p.DA - 1);
+                if (i >= p.DA) ok = wait_bar(bar_ae + 8 * sa, ((i >> p.da_shift) - 1) & 1, status, 40, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
                 const int el = off0 + k * p.Wo, off = el & 3;
                 const float* rr = raw + (el & ~3);
                 const uint32_t taddr = tmem_base + t_lane + a_col0 + (uint32_t)(sa * P);
@@ -475,15 +465,13 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
                   default: sum = convert_g_row<P, 3>(rr, g_mask, part, taddr); break;
                 }
                 db_acc += sum;
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_af + 8 * sa);
               }
-              tmem_wait_st();
-              tc_fence_before();
               __syncwarp();
-              if (lane == 0) {
-                for (int k = 0; k < nu; ++k) mbar_arrive(bar_af + 8 * ((i + k) & (p.DA - 1)));
-                mbar_arrive(bar_ge + 8 * rs);
-              }
-              i += nu;
+              if (lane == 0) mbar_arrive(bar_ge + 8 * rs);
             }
             yo += rn;
           }
