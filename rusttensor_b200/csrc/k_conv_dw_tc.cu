@@ -34,8 +34,8 @@
 namespace tc {
 namespace dw {
 
-constexpr int kConvWarps = 8;                      // converter / epilogue warps
-constexpr int kGroupWarps = 4, kGroupThreads = kGroupWarps * 32;  // warps 0..3 convert x rows, warps 4..7 convert g rows
+constexpr int kConvWarps = 16;                     // converter / epilogue warps
+constexpr int kGroupWarps = 8, kGroupThreads = kGroupWarps * 32;  // warps 0..7 convert x rows, warps 8..15 convert g rows
 constexpr int kThreads = (kConvWarps + 2) * 32;    // + TMA warp + MMA warp
 constexpr int kCoTile = 64;
 constexpr int RG = 3, RX = 3;                      // ring depths: raw g boxes, raw x boxes
@@ -92,12 +92,13 @@ __device__ __forceinline__ void umma_ts_elect(uint32_t d, uint32_t a_tmem, uint3
 // Bounded wait that also gives up when another role of the CTA has already failed.
 // Bounded wait that also gives up when another role of the CTA has already failed.
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, int* status, int code, volatile int* abort_flag) {
+  // try_wait suspends the thread in hardware for a bounded time, so the loop polls without sleeping for a long while
+  // (a sleeping waiter adds its wake-up latency to every hand-over of the pipeline) and backs off only when something
+  // is clearly stuck.
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try(bar, parity)) return true;
-    if (i > 64) {
-      if (*abort_flag) return false;
-      __nanosleep(64);
-    }
+    if ((i & 63) == 63 && *abort_flag) return false;
+    if (i > 8192) __nanosleep(256);
   }
   record_status(status, code);
   *abort_flag = 1;
@@ -132,21 +133,21 @@ struct RingPos {
 // a = hi + lo with hi = a with the low 13 mantissa bits cleared
 __device__ __forceinline__ float hi_part(float v) { return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
 
-// One row of g (P pixels of one output channel, from the TMA-staged copy) -> one lane of the A slot in tensor memory:
+// NC pixels of one row of g (one output channel, from the TMA-staged copy) -> one lane of the A slot in tensor memory:
 // hi rows get the value with the low mantissa bits cleared, lo rows the remainder.  `mask` bit c = pixel c belongs to
 // the segment.  Returns the sum of the row (for the bias gradient).
-template <int P, int OFF>
+template <int NC, int OFF>
 __device__ __forceinline__ float convert_g_row(const float* raw_row, uint32_t mask, int part, uint32_t taddr) {
-  float c[P + 4];
+  float c[NC + 4];
   const float4* src = reinterpret_cast<const float4*>(raw_row);
 #pragma unroll
-  for (int m = 0; m < P / 4 + 1; ++m) {
+  for (int m = 0; m < NC / 4 + 1; ++m) {
     const float4 t = src[m];
     c[4 * m] = t.x; c[4 * m + 1] = t.y; c[4 * m + 2] = t.z; c[4 * m + 3] = t.w;
   }
   float sum = 0.f;
 #pragma unroll
-  for (int j0 = 0; j0 < P; j0 += 4) {
+  for (int j0 = 0; j0 < NC; j0 += 4) {
     uint32_t out[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -225,6 +226,10 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + p.off_bar + kNumBars * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile uint32_t* started_word = reinterpret_cast<volatile uint32_t*>(tmem_slot + 2);
+  float* db_scratch = reinterpret_cast<float*>(tmem_slot + 4);  // 64 floats: bias-gradient sums of the second pixel half
+  bool db_half0 = false;
+  float db_value = 0.f;
+  int db_channel = 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < RG; ++s) { mbar_init(bar_gf + 8 * s, 1); mbar_init(bar_ge + 8 * s, kGroupWarps); }
@@ -360,7 +365,9 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
     // ------------------- converters: warps 0..3 window rows of x, warps 4..7 rows of g; all eight: epilogue ---------
     const int tid = threadIdx.x;
     const bool x_group = warp < kGroupWarps;
-    const int q = warp & 3, half = warp >> 2;
+    // q: quarter of the tensor-memory lanes this warp may touch; half: which half of a row's pixels a g converter takes;
+    // cgrp: which of four interleaved sets of accumulator chunks the warp stores in the epilogue
+    const int q = warp & 3, half = (warp >> 2) & 1, cgrp = warp >> 2;
     // A rows are interleaved: tensor-memory lane 2c holds the hi part of channel c, lane 2c+1 its lo part
     const int part = lane & 1;
     const int co_l = q * 16 + (lane >> 1);           // output channel within the tile
@@ -369,7 +376,7 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
     bool ok = true;
     int i = 0, e = 0;
     RingPos ring;
-    // per-thread constants of the x items (at most two per thread: CIT <= 32, P <= 32, 128 threads)
+    // per-thread constants of the x items (at most two per thread: CIT <= 32, P <= 32, 256 threads)
     const uint32_t sbo = (uint32_t)P * 32, kx_step = (uint32_t)(p.CIT >> 3) * sbo;
     int it_c4[2], it_src[2];
     uint32_t it_dst[2], it_mask[2] = {0u, 0u};
@@ -440,7 +447,9 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
           }
         } else {
           // the g row of every unit -> an A slot in tensor memory (this thread: one output channel, hi or lo part)
-          const uint32_t g_mask = r.swv >= 32 ? 0xffffffffu : ((1u << r.swv) - 1u);
+          constexpr int NC = P / 2;               // this warp's pixels of a row: [col0, col0 + NC)
+          const int col0 = half * NC;
+          const uint32_t g_mask = (r.swv >= 32 ? 0xffffffffu : ((1u << r.swv) - 1u)) >> col0;
           for (int yo = r.y0; yo < r.y_end && ok;) {
             const int rn = min(p.R, r.y_end - yo);
             for (int k0 = 0; k0 < rn && ok; k0 += p.GL, ++e) {  // one g box = the rows of up to GL units (e counts g boxes here)
@@ -454,15 +463,15 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
                 if (i >= p.DA) ok = wait_bar(bar_ae + 8 * sa, ((i >> p.da_shift) - 1) & 1, status, 40, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const int el = off0 + k * p.Wo, off = el & 3;
+                const int el = off0 + k * p.Wo + col0, off = el & 3;
                 const float* rr = raw + (el & ~3);
-                const uint32_t taddr = tmem_base + t_lane + a_col0 + (uint32_t)(sa * P);
+                const uint32_t taddr = tmem_base + t_lane + a_col0 + (uint32_t)(sa * P + col0);
                 float sum;
                 switch (off) {
-                  case 0: sum = convert_g_row<P, 0>(rr, g_mask, part, taddr); break;
-                  case 1: sum = convert_g_row<P, 1>(rr, g_mask, part, taddr); break;
-                  case 2: sum = convert_g_row<P, 2>(rr, g_mask, part, taddr); break;
-                  default: sum = convert_g_row<P, 3>(rr, g_mask, part, taddr); break;
+                  case 0: sum = convert_g_row<NC, 0>(rr, g_mask, part, taddr); break;
+                  case 1: sum = convert_g_row<NC, 1>(rr, g_mask, part, taddr); break;
+                  case 2: sum = convert_g_row<NC, 2>(rr, g_mask, part, taddr); break;
+                  default: sum = convert_g_row<NC, 3>(rr, g_mask, part, taddr); break;
                 }
                 db_acc += sum;
                 tmem_wait_st();
@@ -486,8 +495,8 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
       const uint32_t started = *started_word;
       float* dst = p.ws + (((size_t)(combo * p.cpc + slot_id) * p.SEG + sg) * kCoTile + co_l) * (size_t)p.row_len;
       const int chunks = p.row_len / 16;   // row_len = kh * N, N a multiple of 16
-      int col = half * 16, ky = 0, ky_end = p.N;   // columns [ky * N, ky_end) belong to kernel row ky
-      for (int cc = half; cc < chunks; cc += 2, col += 32) {
+      int col = cgrp * 16, ky = 0, ky_end = p.N;   // columns [ky * N, ky_end) belong to kernel row ky
+      for (int cc = cgrp; cc < chunks; cc += 4, col += 64) {
         while (col >= ky_end) { ++ky; ky_end += p.N; }
         uint32_t v[16];
         if ((started >> ky) & 1u) {
@@ -513,10 +522,14 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
       if (lane == 0) mbar_arrive(bar_de);  // the accumulators may be overwritten
     }
     // bias gradient partial: the hi lanes of the g converters hold the row sums of their channel
-    if (ok && p.ws_db && cit == 0 && !x_group && part == 0) p.ws_db[(size_t)(cot * p.cpc + slot_id) * kCoTile + co_l] = db_acc;
+    if (ok && p.ws_db && cit == 0 && !x_group && part == 0 && half == 1) db_scratch[co_l] = db_acc;  // second half of the pixels
+    db_half0 = ok && p.ws_db && cit == 0 && !x_group && part == 0 && half == 0;
+    db_value = db_acc;
+    db_channel = co_l;
   }
   tc_fence_before();
   __syncthreads();
+  if (db_half0) p.ws_db[(size_t)(cot * p.cpc + slot_id) * kCoTile + db_channel] = db_value + db_scratch[db_channel];
   if (warp == kConvWarps + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -674,7 +687,7 @@ rt_status rt_conv_dw_tma_internal(rt_ctx* ctx, const float* x, const float* y, c
   p.off_raw_x = RG * p.raw_g_bytes;
   p.off_b = p.off_raw_x + RX * p.raw_x_bytes;
   p.off_bar = (p.off_b + (uint32_t)p.DB * 2u * p.b_img_bytes + 127u) & ~127u;
-  const uint32_t smem_bytes = p.off_bar + kNumBars * 8 + 16;
+  const uint32_t smem_bytes = p.off_bar + kNumBars * 8 + 16 + kCoTile * 4;
   if (smem_bytes > 227u * 1024u) return RT_ERR_UNIMPLEMENTED;
   p.d_Ho.init(p.Ho);
   p.d_nseg.init(p.nseg);
