@@ -348,72 +348,98 @@ def data_parallel_check(rt, dist, config, dims, rank, world, local_rank, nccl_id
 
 def kernel_bandwidth_table(capi, pk, rows=4096, cols=4096):
     """Times the HBM-bound kernels of the path one by one at the shapes of the element-wise / reduction
-    micro-benchmark (X [4096,4096], b [4096]): CUDA events on the library's stream, an L2 flush (256 MB fill)
-    before every timed launch, mean of 10.  Bytes are the algorithmic ones: 4 x (elements of each distinct operand
-    read at its un-broadcast size + elements written)."""
+    micro-benchmark (X [rows,cols], b [cols]).  Bytes are the algorithmic ones: 4 x (elements of each distinct operand
+    read at its un-broadcast size + elements written).
+
+    `ms`: every kernel is given `sets` distinct sets of operands (together several times the 126 MB L2, so each launch
+    finds its inputs in HBM only); one launch per set is captured into a CUDA graph - the way the training step issues
+    its kernels - and the graph is replayed three times between two CUDA events on the library's stream; the time is divided
+    by the number of launches.  `ms_single_launch`: one eager launch between two events after a 256 MB L2 flush; this
+    includes the event pair's own cost, which the row "tiny launch" shows (a one-element fill measured the same two ways)."""
     from rusttensor_b200.capi import BINARY, REDUCE, UNARY
 
     r = np.random.default_rng(0)
     n = rows * cols
-    X = capi.to_device(r.standard_normal((rows, cols)).astype(np.float32))
-    G = capi.to_device(r.standard_normal((rows, cols)).astype(np.float32))
-    A = capi.to_device(r.standard_normal((rows, cols)).astype(np.float32))
-    bvec = capi.to_device(r.standard_normal((cols,)).astype(np.float32))
-    grow = capi.to_device(r.standard_normal((rows,)).astype(np.float32))
-    D1, D2 = capi.empty((rows, cols)), capi.empty((rows, cols))
+    sets = 8 if n <= 4096 * 4096 else 4
+    host = lambda *shape: r.standard_normal(shape).astype(np.float32)
+    hx, hg, ha = host(rows, cols), host(rows, cols), host(rows, cols)
+    S = []
+    for _ in range(sets):
+        S.append(dict(X=capi.to_device(hx), G=capi.to_device(hg), A=capi.to_device(ha), D1=capi.empty((rows, cols)), D2=capi.empty((rows, cols)),
+                      m=capi.to_device(np.zeros((rows, cols), np.float32)), v=capi.to_device(np.zeros((rows, cols), np.float32))))
+    bvec = capi.to_device(host(cols))
+    grow = capi.to_device(host(rows))
     dcol, drow = capi.empty((cols,)), capi.empty((rows,))
-    m, v = capi.to_device(np.zeros((rows, cols), np.float32)), capi.to_device(np.zeros((rows, cols), np.float32))
     pn, pc, ph = 256, 32, 28
-    pool_g = capi.to_device(r.standard_normal((pn, pc, ph // 2, ph // 2)).astype(np.float32))
-    pool_idx = capi.to_device(r.integers(0, 4, (pn, pc, ph // 2, ph // 2)).astype(np.float32))
-    pool_dx = capi.empty((pn, pc, ph, ph))
+    hpg, hpi = host(pn, pc, ph // 2, ph // 2), r.integers(0, 4, (pn, pc, ph // 2, ph // 2)).astype(np.float32)
+    P = [dict(g=capi.to_device(hpg), idx=capi.to_device(hpi), dx=capi.empty((pn, pc, ph, ph))) for _ in range(sets)]
+    one = capi.empty((4,))
     i64, f32, i32 = C.c_int64, C.c_float, C.c_int
     sh2, sh1 = capi.i64([rows, cols]), capi.i64([cols])
     cases = [
+        ("tiny launch (fill of one element)", 0.0, lambda b: capi.call("fill", one.ptr, f32(1.0), i64(1))),
         ("unary_backward tanh", 12.0 * n,
-         lambda: capi.call("unary_backward", i32(UNARY["tanh"]), X.ptr, G.ptr, D1.ptr, i64(n), f32(0), f32(0))),
-        ("unary exp (forward)", 8.0 * n, lambda: capi.call("unary", i32(UNARY["exp"]), X.ptr, D1.ptr, i64(n), f32(0), f32(0))),
+         lambda b: capi.call("unary_backward", i32(UNARY["tanh"]), S[b]["X"].ptr, S[b]["G"].ptr, S[b]["D1"].ptr, i64(n), f32(0), f32(0))),
+        ("unary exp (forward)", 8.0 * n, lambda b: capi.call("unary", i32(UNARY["exp"]), S[b]["X"].ptr, S[b]["D1"].ptr, i64(n), f32(0), f32(0))),
         ("binary_backward mul [R,C]*[C] (fused column sum)", 4.0 * (3 * n + 2 * cols),
-         lambda: capi.call("binary_backward", i32(BINARY["mul"]), X.ptr, sh2, i32(2), bvec.ptr, sh1, i32(1), G.ptr, D1.ptr, dcol.ptr)),
+         lambda b: capi.call("binary_backward", i32(BINARY["mul"]), S[b]["X"].ptr, sh2, i32(2), bvec.ptr, sh1, i32(1), S[b]["G"].ptr, S[b]["D1"].ptr,
+                             dcol.ptr)),
         ("binary_backward mul same shape", 20.0 * n,
-         lambda: capi.call("binary_backward", i32(BINARY["mul"]), X.ptr, sh2, i32(2), A.ptr, sh2, i32(2), G.ptr, D1.ptr, D2.ptr)),
+         lambda b: capi.call("binary_backward", i32(BINARY["mul"]), S[b]["X"].ptr, sh2, i32(2), S[b]["A"].ptr, sh2, i32(2), S[b]["G"].ptr,
+                             S[b]["D1"].ptr, S[b]["D2"].ptr)),
         ("reduce sum along rows' axis 1", 4.0 * (n + rows),
-         lambda: capi.call("reduce", i32(REDUCE["sum"]), X.ptr, i64(rows), i64(cols), i64(1), drow.ptr)),
+         lambda b: capi.call("reduce", i32(REDUCE["sum"]), S[b]["X"].ptr, i64(rows), i64(cols), i64(1), drow.ptr)),
         ("reduce sum along axis 0", 4.0 * (n + cols),
-         lambda: capi.call("reduce", i32(REDUCE["sum"]), X.ptr, i64(1), i64(rows), i64(cols), dcol.ptr)),
+         lambda b: capi.call("reduce", i32(REDUCE["sum"]), S[b]["X"].ptr, i64(1), i64(rows), i64(cols), dcol.ptr)),
         ("logsumexp axis 1 (forward)", 4.0 * (n + rows),
-         lambda: capi.call("reduce", i32(REDUCE["logsumexp"]), X.ptr, i64(rows), i64(cols), i64(1), drow.ptr)),
+         lambda b: capi.call("reduce", i32(REDUCE["logsumexp"]), S[b]["X"].ptr, i64(rows), i64(cols), i64(1), drow.ptr)),
         ("logsumexp backward", 4.0 * (2 * n + rows),
-         lambda: capi.call("reduce_backward", i32(REDUCE["logsumexp"]), X.ptr, grow.ptr, i64(rows), i64(cols), i64(1), D1.ptr)),
+         lambda b: capi.call("reduce_backward", i32(REDUCE["logsumexp"]), S[b]["X"].ptr, grow.ptr, i64(rows), i64(cols), i64(1), S[b]["D1"].ptr)),
         ("log_softmax backward", 12.0 * n,
-         lambda: capi.call("log_softmax_backward", X.ptr, G.ptr, i64(rows), i64(cols), i64(1), D1.ptr)),
-        ("max_pool2d backward 2x2 [256,32,28,28]", 4.0 * (2 * pool_g.size + pool_dx.size),
-         lambda: capi.call("max_pool2d_backward", pool_g.ptr, pool_idx.ptr, i64(pn), i64(pc), i64(ph), i64(ph), i32(2), i32(2), i32(2),
-                           i32(2), i32(0), i32(0), pool_dx.ptr)),
-        ("adam step, 16.8 M parameters", 28.0 * n,
-         lambda: capi.call("adam_step", A.ptr, G.ptr, m.ptr, v.ptr, i64(n), f32(1e-3), f32(0.9), f32(0.999), f32(1e-8), i64(1))),
+         lambda b: capi.call("log_softmax_backward", S[b]["X"].ptr, S[b]["G"].ptr, i64(rows), i64(cols), i64(1), S[b]["D1"].ptr)),
+        ("max_pool2d backward 2x2 [256,32,28,28]", 4.0 * (2 * hpg.size + pn * pc * ph * ph),
+         lambda b: capi.call("max_pool2d_backward", P[b]["g"].ptr, P[b]["idx"].ptr, i64(pn), i64(pc), i64(ph), i64(ph), i32(2), i32(2), i32(2),
+                             i32(2), i32(0), i32(0), P[b]["dx"].ptr)),
+        ("adam step, %.1f M parameters" % (n / 1e6), 28.0 * n,
+         lambda b: capi.call("adam_step", S[b]["A"].ptr, S[b]["G"].ptr, S[b]["m"].ptr, S[b]["v"].ptr, i64(n), f32(1e-3), f32(0.9), f32(0.999),
+                             f32(1e-8), i64(1))),
     ]
     flush = capi.empty((64 * 1024 * 1024,))
     flush_sum = capi.empty((1,))
     ms = C.c_float(0)
+    replays = 3
     out = []
     for name, nbytes, call in cases:
-        for _ in range(3):
-            call()
-        ts = []
-        for _ in range(10):
+        for b in range(sets):
+            call(b)
+        graph = C.c_void_p()
+        capi.call("graph_begin")
+        for b in range(sets):
+            call(b)
+        capi.call("graph_end", C.byref(graph))
+        capi.call("graph_launch", graph)
+        rounds = []
+        for _ in range(5):
+            capi.call("timer_start")
+            for _ in range(replays):
+                capi.call("graph_launch", graph)
+            capi.call("timer_stop", C.byref(ms))
+            rounds.append(ms.value / (replays * sets))
+        capi.call("graph_destroy", graph)
+        singles = []
+        for i in range(10):
             # L2 flush: write 256 MB, then read it back so that the dirty lines are written out before the timed
             # launch instead of during it
             capi.call("fill", flush.ptr, C.c_float(1.0), C.c_int64(flush.size))
             capi.call("reduce", i32(REDUCE["sum"]), flush.ptr, i64(1), i64(flush.size), i64(1), flush_sum.ptr)
             capi.call("timer_start")
-            call()
+            call(i % sets)
             capi.call("timer_stop", C.byref(ms))
-            ts.append(ms.value)
-        t = float(np.mean(ts)) * 1e-3
+            singles.append(ms.value)
+        t = float(np.median(rounds)) * 1e-3
         gbs = nbytes / t / 1e9
-        out.append({"kernel": name, "ms": t * 1e3, "algorithmic_MB": nbytes / 1e6, "GB/s": gbs, "frac_of_measured_hbm": gbs / pk["hbm"],
-                    "frac_of_8TBs": gbs / 8000.0})
+        out.append({"kernel": name, "ms": t * 1e3, "ms_single_launch": float(np.mean(singles)), "algorithmic_MB": nbytes / 1e6, "GB/s": gbs,
+                    "frac_of_measured_hbm": gbs / pk["hbm"], "frac_of_8TBs": gbs / 8000.0, "operand_sets": sets})
     return out
 
 
@@ -478,7 +504,8 @@ def main():
             pk = peaks()
             table = kernel_bandwidth_table(rt.CApi(ctx=rt.context_handle()), pk, args.kernels_size, args.kernels_size)
             print(json.dumps({"kernel_bandwidth": table, "hbm_peak_GBs": pk["hbm"], "peak_source": pk["source"],
-                              "l2": "256 MB fill, then a read of the same 256 MB, before every timed launch",
+                              "l2": "ms: launches cycle over distinct operand sets several times the L2 in total; ms_single_launch: 256 MB fill, then a "
+                                    "read of the same 256 MB, before every timed launch",
                               "rows": args.kernels_size, "cols": args.kernels_size}))
         return
     config, dims, per_gpu, desc = WORKLOADS[args.workload]

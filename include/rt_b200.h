@@ -315,8 +315,23 @@ rt_status rt_pack_flat(rt_ctx* ctx, int n_tensors, const float* const* srcs, con
                        int clip, float clip_lo, float clip_hi);
 #define RT_DP_ID_BYTES 128
 rt_status rt_dp_unique_id(uint8_t id[RT_DP_ID_BYTES]);                /* rank 0 creates, every rank receives a copy */
+/* Joins the communicator.  The communicator is created in NCCL's non-blocking mode and the call polls
+ * ncclCommGetAsyncError until every rank has joined or `timeout_ms` has passed; a rank that never joins therefore ends the
+ * call with RT_ERR_TIMEOUT (the half-built communicator is aborted and the context stays usable) instead of blocking for
+ * ever.  timeout_ms <= 0, RT_B200_NCCL_BLOCKING=1, or an NCCL without the non-blocking API: the plain blocking
+ * ncclCommInitRank.  rt_dp_init uses RT_B200_DP_TIMEOUT_MS from the environment (default 120000).  The same deadline
+ * bounds every later wait of this context on the communicator (rt_dp_allreduce_sum's enqueue, rt_dp_wait_event). */
 rt_status rt_dp_init(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID_BYTES]);
+rt_status rt_dp_init_deadline(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID_BYTES], int64_t timeout_ms);
 rt_status rt_dp_allreduce_sum(rt_ctx* ctx, float* buf, int64_t n);    /* in place, on the context's stream */
+/* One poll of ncclCommGetAsyncError: RT_OK while the communicator is healthy (or there is none); an asynchronous error
+ * (a peer that died, a failed transport) aborts the communicator and returns RT_ERR_NCCL; *nccl_code gets NCCL's code. */
+rt_status rt_dp_async_error(rt_ctx* ctx, int* nccl_code);
+/* Waits for an event recorded behind a step like rt_event_synchronize, but as a watchdog: the host polls the event and
+ * the communicator's asynchronous error together; on an error, or when the context's deadline passes first, the
+ * communicator is aborted (which ends a collective kernel stuck on a missing peer) and RT_ERR_NCCL / RT_ERR_TIMEOUT is
+ * returned.  Without a communicator it is rt_event_synchronize. */
+rt_status rt_dp_wait_event(rt_ctx* ctx, rt_event* ev);
 rt_status rt_dp_finalize(rt_ctx* ctx);
 
 /* ---- gradient exchange fused into the optimizer step over peer memory (new) ----------------------------------

@@ -521,7 +521,7 @@ struct DpTrainer {
     B200Backend::check(rt_event_record(c, pipe_done[k]));
     const bool have_prev = pipe_steps > 0;
     if (have_prev) {
-      B200Backend::check(rt_event_synchronize(c, pipe_done[k ^ 1]));
+      B200Backend::check(rt_dp_wait_event(c, pipe_done[k ^ 1]));
       *prev_loss = *pipe_loss[k ^ 1];
     }
     ++pipe_steps;
@@ -576,7 +576,7 @@ struct DpTrainer {
     B200Backend::check(rt_event_record(c, pipe_done[k]));
     const bool have_prev = pipe_steps > 0;
     if (have_prev) {
-      B200Backend::check(rt_event_synchronize(c, pipe_done[k ^ 1]));
+      B200Backend::check(rt_dp_wait_event(c, pipe_done[k ^ 1]));
       *prev_loss = *pipe_loss[k ^ 1];
     }
     ++pipe_steps;
@@ -585,7 +585,7 @@ struct DpTrainer {
   float pipe_flush() {
     if (pipe_steps == 0) throw Error::invalid_op("no pipelined step has run yet");
     const int k = (int)((pipe_steps - 1) & 1);
-    B200Backend::check(rt_event_synchronize(B200Backend::ctx(), pipe_done[k]));
+    B200Backend::check(rt_dp_wait_event(B200Backend::ctx(), pipe_done[k]));
     return *pipe_loss[k];
   }
 };
@@ -692,6 +692,10 @@ int rth_dp_set_state(int64_t h, int which, int i, const float* data, int64_t n) 
     auto& st = which == 0 ? d.state1.at(i) : d.state2.at(i);
     B200Backend::update_from_host(st, std::vector<float>(data, data + n));
   });
+}
+// Number of floats of the flat gradient buffer: what every rank must agree on before the first exchange.
+int rth_dp_flat_len(int64_t h, int64_t* n) {
+  return rt::capi::guarded<B200Backend>([&](auto&) { *n = dp_get(h).flat_len; });
 }
 int rth_dp_optimizer_kind(int64_t h, int* kind) {  // 0 none, 1 Adam, 2 MomentumSGD
   return rt::capi::guarded<B200Backend>([&](auto&) { *kind = dp_get(h).tr->w.optimizer; });

@@ -143,6 +143,183 @@ __global__ void __launch_bounds__(kThreads) thin_conv_dw_kernel(const ThinParams
   }
 }
 
+// ---- weight and bias gradient of a single-channel, unit-stride convolution, whole images per block ----------------
+// dw[n, ky, kx] = sum_{b, yo, xo} g[b, n, yo, xo] * x[b, yo - ph + ky, xo - pw + kx],  db[n] = sum g[b, n, :, :].
+// A block walks over images b = blockIdx.x, blockIdx.x + gridDim.x, ...: the image, with its zero halo, sits in shared
+// memory (the next one is fetched into registers meanwhile); warps w and w + 8 own output channels 4w .. 4w+3 of the current
+// group of 32 and take alternate blocks of 128 output pixels, their lanes stride over the pixels with coalesced loads of g
+// (the next block's loads in flight while the current one is accumulated), and the 4 x (KH*KW + 1) running sums stay in
+// registers across all images of the block.  One pass over g yields dw and db.  The per-block sums are added in a fixed
+// order by a two-level hand-over: the block that arrives last in its group of eight adds the group's partial sums, the
+// group that arrives last adds the groups' - whichever blocks these happen to be, the order of the additions is the same.
+struct ImageDwParams {
+  const float* x;  // [Nb, 1, H, W]
+  const float* g;  // [Nb, N, Ho, Wo]
+  float* part1;    // [gridDim.x][N * (T + 1)]
+  float* part2;    // [groups][N * (T + 1)]
+  float* dw;       // [N, T]
+  float* db;       // [N] or null
+  unsigned* tickets;  // [1 + groups], zero between launches
+  int Nb, H, W, N, Ho, Wo, ph, pw, Hp, Wp;
+  FastDiv d_Wo, d_Wp;
+};
+constexpr int kGroupBlocks = 8;
+
+constexpr int kImgThreads = 512;
+
+template <int KH, int KW>
+__global__ void __launch_bounds__(kImgThreads) thin_dw_image_kernel(const ImageDwParams p) {
+  constexpr int T = KH * KW;
+  extern __shared__ __align__(16) float tile[];  // Hp x Wp: the image with its halo
+  __shared__ float phase1[8][4][T + 1];          // sums of the warps that took the odd pixel blocks
+  __shared__ int is_last;
+  // warp = (pixel phase, channel quad): warps w and w + 8 share four output channels and take alternate blocks of 128 pixels
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, quad = warp & 7, phase = warp >> 3;
+  const int howo = p.Ho * p.Wo, tile_n = p.Hp * p.Wp, outs = p.N * (T + 1);
+  constexpr int kPre = 2;  // halo tile elements a thread carries for the next image (more: a second round after the swap)
+  auto fetch = [&](int b, int i) -> float {
+    uint32_t ty, tx;
+    p.d_Wp.divmod((uint32_t)i, ty, tx);
+    const int iy = (int)ty - p.ph, ix = (int)tx - p.pw;
+    return ((unsigned)iy < (unsigned)p.H && (unsigned)ix < (unsigned)p.W) ? __ldg(p.x + ((int64_t)b * p.H + iy) * p.W + ix) : 0.f;
+  };
+  for (int c0 = 0; c0 < p.N; c0 += 32) {
+    const int n0 = c0 + quad * 4;
+    float acc[4][T + 1];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int t = 0; t <= T; ++t) acc[i][t] = 0.f;
+    __syncthreads();  // the tile of the previous channel group is no longer read
+    for (int i = threadIdx.x; i < tile_n; i += kImgThreads) tile[i] = fetch(blockIdx.x, i);
+    __syncthreads();
+    for (int b = blockIdx.x; b < p.Nb; b += gridDim.x) {
+      const int nb = b + gridDim.x;
+      float pre[kPre];
+#pragma unroll
+      for (int u = 0; u < kPre; ++u) {
+        const int i = threadIdx.x + u * kImgThreads;
+        pre[u] = (nb < p.Nb && i < tile_n) ? fetch(nb, i) : 0.f;
+      }
+      const float* gb = p.g + ((int64_t)b * p.N + n0) * howo;
+      // the gradients of the next block of pixels are in flight while the current one is accumulated
+      float gv[4][4], gn[4][4];
+      auto load_g = [&](int q0, float (&dst)[4][4]) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int q = q0 + u * 32 + lane;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) dst[u][i] = (q < howo && n0 + i < p.N) ? __ldg(gb + (int64_t)i * howo + q) : 0.f;
+        }
+      };
+      load_g(phase * 128, gv);
+      for (int q0 = phase * 128; q0 < howo; q0 += 256) {
+        load_g(q0 + 256, gn);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int q = q0 + u * 32 + lane;
+          uint32_t yo, xo;
+          p.d_Wo.divmod(q < howo ? (uint32_t)q : 0u, yo, xo);
+          const float* tp = tile + (int)yo * p.Wp + (int)xo;
+#pragma unroll
+          for (int ky = 0; ky < KH; ++ky)
+#pragma unroll
+            for (int kx = 0; kx < KW; ++kx) {
+              const float tv = tp[ky * p.Wp + kx];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) acc[i][ky * KW + kx] = fmaf(gv[u][i], tv, acc[i][ky * KW + kx]);
+            }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[i][T] += gv[u][i];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) gv[u][i] = gn[u][i];
+      }
+      __syncthreads();  // every warp is done with this image
+      if (nb < p.Nb) {
+#pragma unroll
+        for (int u = 0; u < kPre; ++u) {
+          const int i = threadIdx.x + u * kImgThreads;
+          if (i < tile_n) tile[i] = pre[u];
+        }
+        for (int i = threadIdx.x + kPre * kImgThreads; i < tile_n; i += kImgThreads) tile[i] = fetch(nb, i);
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int t = 0; t <= T; ++t) {
+        float v = acc[i][t];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        acc[i][t] = v;
+      }
+    if (phase == 1 && lane == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int t = 0; t <= T; ++t) phase1[quad][i][t] = acc[i][t];
+    }
+    __syncthreads();
+    if (phase == 0 && lane == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int t = 0; t <= T; ++t)
+          if (n0 + i < p.N) p.part1[(int64_t)blockIdx.x * outs + (n0 + i) * (T + 1) + t] = acc[i][t] + phase1[quad][i][t];
+    }
+  }
+  // level 1: the last block of each group of eight adds the group's partial sums
+  const int grp = blockIdx.x / kGroupBlocks, groups = (gridDim.x + kGroupBlocks - 1) / kGroupBlocks;
+  const int gsize = min(kGroupBlocks, (int)gridDim.x - grp * kGroupBlocks);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    is_last = atomicAdd(p.tickets + 1 + grp, 1u) == (unsigned)gsize - 1;
+    if (is_last) p.tickets[1 + grp] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int o = threadIdx.x; o < outs; o += kImgThreads) {
+    float v[kGroupBlocks];
+#pragma unroll
+    for (int j = 0; j < kGroupBlocks; ++j) v[j] = j < gsize ? __ldcg(p.part1 + (int64_t)(grp * kGroupBlocks + j) * outs + o) : 0.f;
+    float sum = v[0];
+#pragma unroll
+    for (int j = 1; j < kGroupBlocks; ++j) sum += v[j];
+    p.part2[(int64_t)grp * outs + o] = sum;
+  }
+  // level 2: the last group adds the groups' sums and writes the result
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    is_last = atomicAdd(p.tickets, 1u) == (unsigned)groups - 1;
+    if (is_last) p.tickets[0] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int o = threadIdx.x; o < outs; o += kImgThreads) {
+    float sum = 0.f;
+    int j = 0;
+    for (; j + 8 <= groups; j += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(p.part2 + (int64_t)(j + u) * outs + o);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) sum += v[u];
+    }
+    for (; j < groups; ++j) sum += __ldcg(p.part2 + (int64_t)j * outs + o);
+    const int n = o / (T + 1), t = o - n * (T + 1);
+    if (t < T) p.dw[n * T + t] = sum;
+    else if (p.db) p.db[n] = sum;
+  }
+}
+
 bool make_params(const ConvGeom& g, const float* x, ThinParams* p) {
   const int T = g.Cx * g.kh * g.kw;
   const int64_t pixels = (int64_t)g.Nb * g.Hy * g.Wy;
@@ -185,8 +362,44 @@ rt_status rt_conv_forward_thin_internal(rt_ctx* ctx, const float* x, const float
   return RT_OK;
 }
 
-// dw[Cy, Cx*kh*kw] = sum over pixels of g * im2col(x) for Cx*kh*kw <= 16; RT_ERR_UNIMPLEMENTED otherwise.
-rt_status rt_conv_weight_grad_thin_internal(rt_ctx* ctx, const float* x, const float* gy, const ConvGeom& g, float* dw) {
+// The single-channel whole-image kernel: unit stride, 3x3 window, the image with its halo within 48 KB of shared memory.
+static rt_status weight_grad_image(rt_ctx* ctx, const float* x, const float* gy, const ConvGeom& g, float* dw, float* db) {
+  if (g.Cx != 1 || g.sh != 1 || g.sw != 1 || g.kh != 3 || g.kw != 3 || g.Cy < 1 || g.Nb < 1 || !ctx->reduce_counters)
+    return RT_ERR_UNIMPLEMENTED;
+  ImageDwParams p;
+  p.Hp = g.Hy + g.kh - 1;
+  p.Wp = g.Wy + g.kw - 1;
+  const size_t smem = sizeof(float) * (size_t)p.Hp * p.Wp;
+  if (g.Hy < 1 || g.Wy < 1 || smem > 48 * 1024 || (int64_t)g.Nb * g.Cy * g.Hy * g.Wy >= (1ll << 31)) return RT_ERR_UNIMPLEMENTED;
+  const int T = g.kh * g.kw, outs = g.Cy * (T + 1);
+  const int grid = g.Nb < ctx->sm_count ? g.Nb : ctx->sm_count;
+  const int groups = (grid + kGroupBlocks - 1) / kGroupBlocks;
+  if (1 + groups > kAuxCounterSlots) return RT_ERR_UNIMPLEMENTED;
+  RtScratch part(ctx);
+  rt_status st = part.alloc(sizeof(float) * (size_t)(grid + groups) * outs);
+  if (st != RT_OK) return st;
+  p.x = x; p.g = gy; p.dw = dw; p.db = db;
+  p.part1 = part.as<float>();
+  p.part2 = p.part1 + (size_t)grid * outs;
+  p.tickets = ctx->reduce_counters + 2 * kReduceCounterSlots + (ctx->on_side ? kAuxCounterSlots : 0);
+  p.Nb = g.Nb; p.H = g.Hx; p.W = g.Wx; p.N = g.Cy; p.Ho = g.Hy; p.Wo = g.Wy; p.ph = g.ph; p.pw = g.pw;
+  p.d_Wo.init(g.Wy);
+  p.d_Wp.init(p.Wp);
+  thin_dw_image_kernel<3, 3><<<grid, kImgThreads, smem, ctx->stream>>>(p);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+// dw[Cy, Cx*kh*kw] = sum over pixels of g * im2col(x) for Cx*kh*kw <= 16; RT_ERR_UNIMPLEMENTED otherwise.  With `db` not null
+// the bias gradient db[Cy] may come out of the same pass; *db_done tells whether it did.
+rt_status rt_conv_weight_grad_thin_internal(rt_ctx* ctx, const float* x, const float* gy, const ConvGeom& g, float* dw, float* db,
+                                            bool* db_done) {
+  if (db_done) *db_done = false;
+  {
+    const rt_status st = weight_grad_image(ctx, x, gy, g, dw, db_done ? db : nullptr);
+    if (st == RT_OK && db && db_done) *db_done = true;
+    if (st != RT_ERR_UNIMPLEMENTED) return st;
+  }
   ThinParams p;
   if (g.Cy < 1 || !make_params(g, x, &p)) return RT_ERR_UNIMPLEMENTED;
   const int TP = (p.T + 3) / 4 * 4;

@@ -27,7 +27,8 @@ rt_status rt_conv_weight_grad_tc_internal(rt_ctx* ctx, const float* x, const flo
 rt_status rt_conv_dw_tma_internal(rt_ctx* ctx, const float* x, const float* y, const ConvGeom& g, float* dw, float* db);
 rt_status rt_conv_forward_thin_internal(rt_ctx* ctx, const float* x, const float* w, const float* bias, const ConvGeom& g,
                                         float* y);
-rt_status rt_conv_weight_grad_thin_internal(rt_ctx* ctx, const float* x, const float* gy, const ConvGeom& g, float* dw);
+rt_status rt_conv_weight_grad_thin_internal(rt_ctx* ctx, const float* x, const float* gy, const ConvGeom& g, float* dw, float* db,
+                                            bool* db_done);
 rt_status rt_conv_window_tc_internal(rt_ctx* ctx, const float* src, int Nb, int C, int H, int W, int ph, int pw, const float* w,
                                      int N, int kh, int kw, int sn, int sc, int sky, int skx, int off0, const float* bias,
                                      float* out);
@@ -520,7 +521,7 @@ rt_status conv_weight_grad_like(rt_ctx* ctx, const float* x, const float* y, con
     if (st != RT_ERR_UNIMPLEMENTED) return st;
   }
   if (ctx->use_tensor_cores && M > 0 && N > 0 && K > 0) {  // tiny reductions: direct FP32 kernel
-    rt_status st = rt_conv_weight_grad_thin_internal(ctx, x, y, g, dw);
+    rt_status st = rt_conv_weight_grad_thin_internal(ctx, x, y, g, dw, db, db_done);
     if (st != RT_ERR_UNIMPLEMENTED) return st;
   }
   if (ctx->use_tensor_cores && M > 0 && N > 0) {

@@ -1,8 +1,9 @@
 // Issue-rate probe for tcgen05.mma.kind::tf32: how many SM cycles one MMA of a given shape occupies
 // the tensor pipe when MMAs are issued back to back.  The convolution and GEMM kernels of this
-// library choose their tile shapes from these numbers (an MMA with a small N costs as much as one
-// with N = 128; N = 256 runs at the full rate), so the measurement ships with the library and
-// `bench.py --mma-rate` prints it.
+// library choose their tile shapes from these numbers (measured on a B200, K = 8: with A in shared
+// memory an M = 128 MMA costs about 32 + N/4 cycles up to N = 128 and N/2 beyond, the shared-memory
+// read of A being the floor; with A in tensor memory it costs N/2 for every N; M = 64 runs at half
+// the rate), so the measurement ships with the library and `bench.py --mma-rate` prints it.
 //
 // One CTA, one warp issues `iters` MMAs (one elected lane), then one tcgen05.commit; the time from the
 // first issue to the completion of the commit is divided by `iters`.  Operands are zeros in shared

@@ -2,8 +2,19 @@
 // gradient all-reduce of librt_b200.so.
 #include <dlfcn.h>
 
+#include <chrono>
 #include <cstdlib>
 #include <cstring>
+#include <thread>
+
+// NCCL's header is only needed for the communicator configuration of the non-blocking mode (NCCL_CONFIG_INITIALIZER); the
+// library itself is resolved with dlopen at run time.
+#if defined(__has_include)
+#if __has_include(<nccl.h>)
+#include <nccl.h>
+#define RT_HAVE_NCCL_HEADER 1
+#endif
+#endif
 
 #include "rt_internal.cuh"
 
@@ -63,6 +74,12 @@ rt_status rt_ctx_create(int device, rt_ctx** out) {
     return RT_ERR_CUDA;
   }
   ctx->device_status = static_cast<int*>(status_dev);
+  if (cudaMalloc(&ctx->reduce_counters, 2 * (kReduceCounterSlots + kAuxCounterSlots) * sizeof(unsigned)) != cudaSuccess ||
+      cudaMemset(ctx->reduce_counters, 0, 2 * (kReduceCounterSlots + kAuxCounterSlots) * sizeof(unsigned)) != cudaSuccess) {
+    cudaGetLastError();
+    if (ctx->reduce_counters) cudaFree(ctx->reduce_counters);
+    ctx->reduce_counters = nullptr;  // the reductions then keep to their two-launch form
+  }
   const char* no_tc = getenv("RT_B200_DISABLE_TENSOR_CORES");
   if (no_tc && no_tc[0] == '1') ctx->use_tensor_cores = false;
   const char* dw_tma = getenv("RT_B200_CONV_DW_TMA");
@@ -90,6 +107,7 @@ rt_status rt_ctx_destroy(rt_ctx* ctx) {
   for (auto& kv : ctx->side_deferred) cudaFree(kv.second);
   for (auto& kv : ctx->live_blocks) cudaFree(kv.first);
   if (ctx->host_status) cudaFreeHost(const_cast<int*>(ctx->host_status));
+  if (ctx->reduce_counters) cudaFree(ctx->reduce_counters);
   if (ctx->ev_start) cudaEventDestroy(ctx->ev_start);
   if (ctx->ev_stop) cudaEventDestroy(ctx->ev_stop);
   cudaStreamDestroy(ctx->stream);
@@ -519,27 +537,42 @@ rt_status rt_timer_stop(rt_ctx* ctx, float* ms) {
 }
 
 // ---- NCCL, resolved at run time so that the library loads on machines without it ---
+// RT_B200_NCCL_LIBRARY names the shared object to load instead of libnccl.so.2 (the failure-handling tests load a
+// scripted stand-in through it).
 namespace {
 struct NcclId {
   char internal[128];
 };
+constexpr int kNcclSuccess = 0, kNcclInProgress = 7;
 struct NcclApi {
   void* handle = nullptr;
   int (*GetUniqueId)(NcclId*) = nullptr;
   int (*CommInitRank)(void**, int, NcclId, int) = nullptr;
+  int (*CommInitRankConfig)(void**, int, NcclId, int, void*) = nullptr;
+  int (*CommGetAsyncError)(void*, int*) = nullptr;
+  int (*CommAbort)(void*) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
   int (*CommDestroy)(void*) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
   bool ok = false;
+  const char* text(int rc) const { return GetErrorString ? GetErrorString(rc) : "?"; }
 };
 NcclApi& nccl() {
   static NcclApi api;
   if (!api.handle) {
-    api.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
-    if (!api.handle) api.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    const char* custom = getenv("RT_B200_NCCL_LIBRARY");
+    if (custom && custom[0]) {
+      api.handle = dlopen(custom, RTLD_NOW | RTLD_GLOBAL);
+    } else {
+      api.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+      if (!api.handle) api.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    }
     if (api.handle) {
       api.GetUniqueId = (int (*)(NcclId*))dlsym(api.handle, "ncclGetUniqueId");
       api.CommInitRank = (int (*)(void**, int, NcclId, int))dlsym(api.handle, "ncclCommInitRank");
+      api.CommInitRankConfig = (int (*)(void**, int, NcclId, int, void*))dlsym(api.handle, "ncclCommInitRankConfig");
+      api.CommGetAsyncError = (int (*)(void*, int*))dlsym(api.handle, "ncclCommGetAsyncError");
+      api.CommAbort = (int (*)(void*))dlsym(api.handle, "ncclCommAbort");
       api.AllReduce = (int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t))dlsym(api.handle, "ncclAllReduce");
       api.CommDestroy = (int (*)(void*))dlsym(api.handle, "ncclCommDestroy");
       api.GetErrorString = (const char* (*)(int))dlsym(api.handle, "ncclGetErrorString");
@@ -547,6 +580,46 @@ NcclApi& nccl() {
     }
   }
   return api;
+}
+
+int64_t now_ms() {
+  return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+// Gives the communicator up after a failure: ncclCommAbort also ends collective kernels that are stuck on a missing peer.
+void abandon_comm(rt_ctx* ctx, void* comm) {
+  NcclApi& n = nccl();
+  if (comm) {
+    if (n.CommAbort) n.CommAbort(comm);
+    else n.CommDestroy(comm);
+  }
+  if (ctx->nccl_comm == comm) ctx->nccl_comm = nullptr;
+}
+
+// Polls the communicator until its pending call has finished.  RT_OK, RT_ERR_NCCL (the communicator reported an error) or
+// RT_ERR_TIMEOUT (the deadline passed first); after either error the communicator has been aborted.
+rt_status settle_comm(rt_ctx* ctx, void* comm, const char* what) {
+  NcclApi& n = nccl();
+  const int64_t deadline = now_ms() + ctx->dp_timeout_ms;
+  for (int spins = 0;; ++spins) {
+    int state = kNcclSuccess;
+    const int rc = n.CommGetAsyncError(comm, &state);
+    if (rc != kNcclSuccess) {
+      abandon_comm(ctx, comm);
+      RT_FAIL(ctx, RT_ERR_NCCL, "%s: ncclCommGetAsyncError failed: %s", what, n.text(rc));
+    }
+    if (state == kNcclSuccess) return RT_OK;
+    if (state != kNcclInProgress) {
+      abandon_comm(ctx, comm);
+      RT_FAIL(ctx, RT_ERR_NCCL, "%s: the communicator reported: %s", what, n.text(state));
+    }
+    if (now_ms() > deadline) {
+      abandon_comm(ctx, comm);
+      RT_FAIL(ctx, RT_ERR_TIMEOUT, "%s: not finished after %lld ms (a rank that never joined?); communicator aborted", what,
+              (long long)ctx->dp_timeout_ms);
+    }
+    if (spins > 1000) std::this_thread::sleep_for(std::chrono::microseconds(200));
+  }
 }
 }  // namespace
 
@@ -561,7 +634,7 @@ rt_status rt_dp_unique_id(uint8_t id[RT_DP_ID_BYTES]) {
   return RT_OK;
 }
 
-rt_status rt_dp_init(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID_BYTES]) {
+rt_status rt_dp_init_deadline(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID_BYTES], int64_t timeout_ms) {
   RT_CHECK_CTX(ctx);
   if (world < 1 || rank < 0 || rank >= world) RT_FAIL(ctx, RT_ERR_INVALID_INDEX, "rt_dp_init: rank %d of %d", rank, world);
   ctx->dp_rank = rank;
@@ -570,25 +643,98 @@ rt_status rt_dp_init(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID
   if (ctx->nccl_comm) return RT_OK;  // already joined (a second trainer on the same context reuses the communicator)
   RT_CHECK_PTR(ctx, id);
   NcclApi& n = nccl();
-  if (!n.ok) RT_FAIL(ctx, RT_ERR_NCCL, "libnccl.so.2 could not be loaded");
+  if (!n.ok) RT_FAIL(ctx, RT_ERR_NCCL, "the NCCL library could not be loaded");
   NcclId nid;
   memcpy(&nid, id, sizeof(nid));
   RT_CUDA(ctx, cudaSetDevice(ctx->device));
-  int rc = n.CommInitRank(&ctx->nccl_comm, world, nid, rank);
-  if (rc != 0) RT_FAIL(ctx, RT_ERR_NCCL, "ncclCommInitRank failed: %s", n.GetErrorString ? n.GetErrorString(rc) : "?");
+  const char* blocking_env = getenv("RT_B200_NCCL_BLOCKING");
+  bool nonblocking = timeout_ms > 0 && !(blocking_env && blocking_env[0] == '1') && n.CommInitRankConfig && n.CommGetAsyncError &&
+                     n.CommAbort;
+#ifndef RT_HAVE_NCCL_HEADER
+  nonblocking = false;  // the configuration structure comes from NCCL's own header
+#endif
+  if (!nonblocking) {
+    const int rc = n.CommInitRank(&ctx->nccl_comm, world, nid, rank);
+    if (rc != kNcclSuccess) {
+      ctx->nccl_comm = nullptr;
+      RT_FAIL(ctx, RT_ERR_NCCL, "ncclCommInitRank failed: %s", n.text(rc));
+    }
+    ctx->nccl_nonblocking = false;
+    return RT_OK;
+  }
+#ifdef RT_HAVE_NCCL_HEADER
+  ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+  config.blocking = 0;
+  void* comm = nullptr;
+  const int rc = n.CommInitRankConfig(&comm, world, nid, rank, &config);
+  if (rc != kNcclSuccess && rc != kNcclInProgress) {
+    if (comm) abandon_comm(ctx, comm);
+    RT_FAIL(ctx, RT_ERR_NCCL, "ncclCommInitRankConfig failed: %s", n.text(rc));
+  }
+  if (!comm) RT_FAIL(ctx, RT_ERR_NCCL, "ncclCommInitRankConfig returned no communicator");
+  ctx->dp_timeout_ms = timeout_ms;
+  const rt_status st = settle_comm(ctx, comm, "rt_dp_init");
+  if (st != RT_OK) return st;
+  ctx->nccl_comm = comm;
+  ctx->nccl_nonblocking = true;
+#endif
   return RT_OK;
+}
+
+rt_status rt_dp_init(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID_BYTES]) {
+  int64_t timeout_ms = 120000;
+  const char* env = getenv("RT_B200_DP_TIMEOUT_MS");
+  if (env && env[0]) timeout_ms = atoll(env);
+  return rt_dp_init_deadline(ctx, rank, world, id, timeout_ms);
 }
 
 rt_status rt_dp_allreduce_sum(rt_ctx* ctx, float* buf, int64_t count) {
   RT_CHECK_CTX(ctx);
   if (ctx->dp_world == 1 || count == 0) return RT_OK;
   RT_CHECK_PTR(ctx, buf);
-  if (!ctx->nccl_comm) RT_FAIL(ctx, RT_ERR_NCCL, "rt_dp_allreduce_sum: rt_dp_init was not called");
+  if (!ctx->nccl_comm) RT_FAIL(ctx, RT_ERR_NCCL, "rt_dp_allreduce_sum: no communicator (rt_dp_init was not called, or it was aborted)");
   NcclApi& n = nccl();
   const int nccl_float32 = 7, nccl_sum = 0;
-  int rc = n.AllReduce(buf, buf, (size_t)count, nccl_float32, nccl_sum, ctx->nccl_comm, ctx->stream);
-  if (rc != 0) RT_FAIL(ctx, RT_ERR_NCCL, "ncclAllReduce failed: %s", n.GetErrorString ? n.GetErrorString(rc) : "?");
+  const int rc = n.AllReduce(buf, buf, (size_t)count, nccl_float32, nccl_sum, ctx->nccl_comm, ctx->stream);
+  if (rc == kNcclInProgress && ctx->nccl_nonblocking) return settle_comm(ctx, ctx->nccl_comm, "rt_dp_allreduce_sum");
+  if (rc != kNcclSuccess) RT_FAIL(ctx, RT_ERR_NCCL, "ncclAllReduce failed: %s", n.text(rc));
   return RT_OK;
+}
+
+rt_status rt_dp_async_error(rt_ctx* ctx, int* nccl_code) {
+  RT_CHECK_CTX(ctx);
+  if (nccl_code) *nccl_code = 0;
+  NcclApi& n = nccl();
+  if (!ctx->nccl_comm || !n.CommGetAsyncError) return RT_OK;
+  int state = kNcclSuccess;
+  const int rc = n.CommGetAsyncError(ctx->nccl_comm, &state);
+  if (rc != kNcclSuccess) state = rc;
+  if (nccl_code) *nccl_code = state;
+  if (state == kNcclSuccess || state == kNcclInProgress) return RT_OK;
+  abandon_comm(ctx, ctx->nccl_comm);
+  RT_FAIL(ctx, RT_ERR_NCCL, "the communicator reported an asynchronous error: %s; communicator aborted", n.text(state));
+}
+
+rt_status rt_dp_wait_event(rt_ctx* ctx, rt_event* ev) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, ev);
+  if (!ctx->nccl_comm) return rt_event_synchronize(ctx, ev);
+  const int64_t deadline = now_ms() + ctx->dp_timeout_ms;
+  for (int spins = 0;; ++spins) {
+    const cudaError_t q = cudaEventQuery(ev->ev);
+    if (q == cudaSuccess) return rt_take_status(ctx, nullptr);
+    if (q != cudaErrorNotReady) RT_FAIL(ctx, RT_ERR_CUDA, "rt_dp_wait_event: %s", cudaGetErrorString(q));
+    if ((spins & 63) == 63) {
+      const rt_status st = rt_dp_async_error(ctx, nullptr);
+      if (st != RT_OK) return st;
+      if (now_ms() > deadline) {
+        abandon_comm(ctx, ctx->nccl_comm);
+        RT_FAIL(ctx, RT_ERR_TIMEOUT, "rt_dp_wait_event: the step did not finish within %lld ms; communicator aborted",
+                (long long)ctx->dp_timeout_ms);
+      }
+    }
+    if (spins > 20000) std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
 }
 
 rt_status rt_ipc_export(rt_ctx* ctx, void* device_ptr, uint8_t handle[RT_IPC_HANDLE_BYTES]) {
@@ -619,8 +765,10 @@ rt_status rt_ipc_close(rt_ctx* ctx, void* peer_ptr) {
 rt_status rt_dp_finalize(rt_ctx* ctx) {
   RT_CHECK_CTX(ctx);
   if (ctx->nccl_comm) {
+    cudaStreamSynchronize(ctx->stream);  // no collective of this communicator is still queued
     nccl().CommDestroy(ctx->nccl_comm);
     ctx->nccl_comm = nullptr;
+    ctx->nccl_nonblocking = false;
   }
   ctx->dp_world = 1;
   ctx->dp_rank = 0;

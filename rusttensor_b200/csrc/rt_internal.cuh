@@ -46,6 +46,10 @@ struct rt_ctx {
   // device's address space.  device_status is what kernels get, host_status the same word as the host reads it.
   int* device_status = nullptr;
   volatile int* host_status = nullptr;
+  // Tickets of the kernels that finish a split sum in their last block (k_reduce.cu, k_conv_thin.cu): zero between launches.
+  // 2 x kReduceCounterSlots for the column reductions, then 2 x kAuxCounterSlots; of each pair one half serves work queued on
+  // the main stream and one the side stream, which may run such a kernel at the same time.
+  unsigned* reduce_counters = nullptr;
   // Route large contractions to the tcgen05 3xTF32 kernels (k_gemm_tc.cu).
   bool use_tensor_cores = true;
   // Unit-stride convolution weight gradients through the TMA-fed kernel with the pixels as the reduction index
@@ -53,8 +57,13 @@ struct rt_ctx {
   bool use_tma_weight_grad = true;
   // NCCL (loaded at run time on first use)
   void* nccl_comm = nullptr;
+  bool nccl_nonblocking = false;  // the communicator was created in NCCL's non-blocking mode: calls may answer "in progress"
+  int64_t dp_timeout_ms = 120000; // host deadline of every wait on the communicator
   int dp_rank = 0, dp_world = 1;
 };
+
+constexpr int kReduceCounterSlots = 4096;  // per stream half: tickets of the column reductions
+constexpr int kAuxCounterSlots = 128;      // per stream half, behind them: tickets of other kernels that hand partial sums over
 
 #define RT_FAIL(ctx, code, ...)                         \
   do {                                                  \

@@ -78,6 +78,13 @@ class DataParallelTrainer:
         return k.value
 
     @property
+    def flat_len(self):
+        """Floats in the flat gradient buffer (every tensor's start padded to 16 bytes): equal on all ranks of a job."""
+        n = C.c_int64(0)
+        self._call("dp_flat_len", C.c_int64(self.handle), C.byref(n))
+        return n.value
+
+    @property
     def step_count(self):
         """Number of optimizer steps taken (Adam's ``t``)."""
         t = C.c_int64(0)

@@ -17,6 +17,9 @@ CONV = [
     (1, 4, 6, 6, 5, 5, (1, 1), (2, 2)), (4, 1, 28, 28, 32, 3, (1, 1), (1, 1)), (3, 32, 14, 14, 64, 3, (1, 1), (1, 1)),
     (2, 5, 11, 13, 7, 3, (2, 1), (0, 1)), (1, 64, 12, 12, 128, 3, (1, 1), (1, 1)), (16, 32, 14, 14, 64, 3, (1, 1), (1, 1)),
     (8, 1, 28, 28, 32, 3, (1, 1), (1, 1)), (2, 64, 20, 20, 128, 3, (1, 1), (1, 1)), (3, 8, 10, 9, 16, 5, (1, 1), (2, 2)),
+    # single-channel 3x3 inputs (the whole-image weight/bias gradient kernel): more images than SMs, more than 32 output
+    # channels (two channel groups), a channel count that is no multiple of four, no padding, one image
+    (301, 1, 12, 10, 5, 3, (1, 1), (1, 1)), (5, 1, 9, 11, 70, 3, (1, 1), (0, 0)), (1, 1, 28, 28, 33, 3, (1, 1), (1, 1)),
 ]
 
 
@@ -47,10 +50,11 @@ def test_conv2d_forward_backward(oracle_engine, gpu_engine, contraction_path, n,
     assert_close(res["gpu"][2], dw64, TOL, "conv2d dW vs float64")
 
 
-def test_conv2d_without_bias_and_frozen_input(oracle_engine, gpu_engine, contraction_path):
+@pytest.mark.parametrize("cin", [3, 1])
+def test_conv2d_without_bias_and_frozen_input(oracle_engine, gpu_engine, contraction_path, cin):
     r = rng(43)
-    x = r.standard_normal((2, 3, 6, 6)).astype(np.float32)
-    w = r.standard_normal((4, 3, 3, 3)).astype(np.float32)
+    x = r.standard_normal((2, cin, 6, 6)).astype(np.float32)
+    w = r.standard_normal((4, cin, 3, 3)).astype(np.float32)
     res = []
     for e in (oracle_engine, gpu_engine):
         xt, wt = e.tensor(x, requires_grad=False), e.tensor(w, requires_grad=True)
