@@ -289,7 +289,7 @@ def data_parallel_check(rt, dist, config, dims, rank, world, local_rank, nccl_id
     from rusttensor_b200.workloads import workload_data
 
     flat = np.concatenate([t.numpy().ravel() for t in trained.params]).view(np.int32)
-    hi = torch.from_numpy(flat.copy()).cuda()
+    hi = torch.from_numpy(flat.copy()).to("cuda" if dist.get_backend() == "nccl" else "cpu")
     lo = hi.clone()
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
@@ -306,7 +306,7 @@ def data_parallel_check(rt, dist, config, dims, rank, world, local_rank, nccl_id
     small = list(dims)
     small[0] = max(4, small[0] // 8)
     dp = rt.DataParallelTrainer(trainer_config, small, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
-    if os.environ.get("RT_B200_DP_FUSED", "1") == "1":
+    if os.environ.get("RT_B200_DP_FUSED", "0") == "1":
         if not dp.connect_peers(dist):
             dp = rt.DataParallelTrainer(trainer_config, small, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
     params, _ = workload_data(config, small, seed=0)
@@ -337,7 +337,7 @@ def data_parallel_check(rt, dist, config, dims, rank, world, local_rank, nccl_id
                 ok2 = ok2 and bool(np.all(err <= bound))
                 if key != "p" and err.size:
                     worst = max(worst, float(np.max(err / np.maximum(bound, 1e-30))))
-    flag = torch.tensor([1 if ok2 else 0], dtype=torch.int32, device="cuda")
+    flag = torch.tensor([1 if ok2 else 0], dtype=torch.int32, device="cuda" if dist.get_backend() == "nccl" else "cpu")
     dist.broadcast(flag, 0)
     return {"ok": bool(identical and flag.item() == 1), "replicas_bit_identical": identical, "joint_batch_within_tolerance": bool(flag.item() == 1),
             "worst_moment_error_over_bound": worst, "per_gpu_batch_of_check": small[0],
@@ -511,34 +511,53 @@ def main():
     config, dims, per_gpu, desc = WORKLOADS[args.workload]
     dist = None
     nccl_id = None
-    if world > 1:
+    if world > 1 or os.environ.get("RT_BENCH_FORCE_DIST") == "1":  # the second: a diagnostic (one rank with a process group)
         import torch
         import torch.distributed as dist
 
+        from rusttensor_b200 import dp_setup
+
+        # The process group only carries the set-up (communicator id, peer-memory handles, agreement checks), the barriers
+        # around the timed regions and the max over the ranks: gloo by default.  Measured on B200s: after a few NCCL barriers of
+        # torch's own communicator every later training step of the process ran 15 us slower (0.249 -> 0.264 ms, one rank, no
+        # exchange at all); gloo barriers leave the step alone.  The gradient exchange itself never goes through this group: it
+        # is the library's peer-memory kernels or its own NCCL communicator.  RT_BENCH_PG=nccl selects torch's NCCL group.
+        pg_backend = os.environ.get("RT_BENCH_PG", "gloo")
         torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        idt = torch.zeros(128, dtype=torch.uint8, device="cuda")
-        if rank == 0:
-            idt = torch.tensor(list(rt.DataParallelTrainer.unique_id()), dtype=torch.uint8, device="cuda")
-        dist.broadcast(idt, 0)
-        nccl_id = idt.cpu().tolist()
+        if pg_backend == "nccl":
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        else:
+            dist.init_process_group(pg_backend)
+        ddev = "cuda" if pg_backend == "nccl" else "cpu"
+        nccl_id = dp_setup.share_unique_id(dist, rt.DataParallelTrainer.unique_id, rank, device=ddev)
 
     trainer_config = config + (100 if args.fused_forward else 0)
     if args.fused_forward:
         desc += " [fused forward ops]"
-    tr = rt.DataParallelTrainer(trainer_config, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
+    uncoupled = world > 1 and os.environ.get("RT_BENCH_UNCOUPLED") == "1"
+    if uncoupled:
+        # diagnostic: the N processes train independent replicas (no gradient exchange); shows what the exchange costs
+        tr = rt.DataParallelTrainer(trainer_config, dims, rank=0, world=1, device=local_rank)
+    else:
+        tr = rt.DataParallelTrainer(trainer_config, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
     capi = rt.CApi(ctx=rt.context_handle())
     exchange = "one NCCL all-reduce of the flat gradients (N>1)"
-    if world > 1 and os.environ.get("RT_B200_DP_FUSED", "1") == "1":
-        # Default: the gradients are read from the peers' buffers inside the optimizer kernel and the whole step - exchange
-        # included - is one CUDA-graph launch; RT_B200_DP_FUSED=0 selects the NCCL all-reduce between the graph and an eager
-        # optimizer launch.  Every rank must agree on the mode, so a set-up failure on any rank sends all of them to NCCL
+    if uncoupled:
+        exchange = "NONE (RT_BENCH_UNCOUPLED=1: independent replicas, a diagnostic and not a data-parallel run)"
+    elif world > 1 and os.environ.get("RT_B200_DP_FUSED", "0") == "1":
+        # RT_B200_DP_FUSED=1: the gradients are read from the peers' buffers inside the optimizer kernel and the whole step -
+        # exchange included - is one CUDA-graph launch.  Default: one NCCL all-reduce between the graph and an eager optimizer
+        # launch, which measured faster on this model's 1.7 MB of gradients (eight B200s: 0.288 against 0.297 ms per step;
+        # two: 0.270 against 0.273).  Every rank must agree on the mode, so a set-up failure on any rank sends all of them to NCCL
         if tr.connect_peers(dist):
             exchange = "gradient exchange over peer memory fused into the optimizer kernel (N>1)"
         else:
             print(f"[rank {rank}] peer-memory exchange unavailable ({getattr(tr, 'peer_error', 'another rank failed')}); using NCCL",
                   file=sys.stderr)
             tr = rt.DataParallelTrainer(trainer_config, dims, rank=rank, world=world, nccl_id=nccl_id, device=local_rank)
+    if world > 1 and not uncoupled:
+        # every rank must have built the same model before the first exchange: raises on all ranks otherwise
+        dp_setup.agree(dist, "the model (flat gradient length, number of parameter tensors)", [tr.flat_len, len(tr.params)], device=ddev)
     params, inputs = workload_data(config, dims, seed=0, rank=rank)  # same weights on every rank, different data
     for t, p in zip(tr.params, params):
         t.update_from_host(p)
@@ -577,7 +596,7 @@ def main():
             if dist is not None:
                 import torch
 
-                tt = torch.tensor([v], device="cuda")
+                tt = torch.tensor([v], device=ddev)
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
                 v = float(tt.item())
             out.append(v)
@@ -587,7 +606,26 @@ def main():
     if rank == 0:
         sampler.start()
     lb = capi.launches()
+    fused_exchange = world > 1 and exchange.startswith("gradient exchange over peer memory")
+    wait0 = tr.peer_wait_ns if fused_exchange else 0
     regions = timed(lambda: tr.step(None), args.steps, repeats=args.repeats)  # each region is exactly --steps steps
+    trace = None
+    if os.environ.get("RT_B200_DP_TRACE") == "1":
+        ts = tr.trace()
+        names = ["begin->forward", "forward->backward", "backward->packed", "packed->peers complete", "peers complete->optimizer done"]
+        idx = [(0, 1), (1, 2), (2, 3), (3, 4), (4, 6)] if fused_exchange else [(0, 1), (1, 2), None, None, (2, 6)]
+        trace = {n: round((ts[b] - ts[a]) / 1e3, 2) for n, ab in zip(names, idx) if ab for a, b in [ab]}
+        trace["note"] = "last step of this rank, GPU nanosecond timer, microseconds; each stamp is a one-thread kernel of its own"
+    peer_wait = None
+    if fused_exchange:
+        # diagnostic: how long each rank's one-block wait kernel polled for its peers per step (device clock), all ranks
+        import torch
+
+        mine = torch.tensor([(tr.peer_wait_ns - wait0) / (args.steps * args.repeats) / 1e3], device=ddev)
+        allw = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allw, mine)
+        peer_wait = {"us_per_step_by_rank": [round(float(t.item()), 2) for t in allw],
+                     "what": "time the wait kernel of each rank polled for the peers' flags, per step"}
     gpu_launches = (capi.launches() - lb) // args.repeats + launches_per_replay * args.steps  # per region
     clocks = sampler.stop() if rank == 0 else None
     ms_resident = float(np.median(regions))
@@ -680,7 +718,7 @@ def main():
                      "optimizer kernel that reads every rank's gradients over NVLink (no all-reduce call)")
     else:
         step_text = f"CUDA-graph replay of forward+backward, {exchange}, one fused optimizer launch"
-    dp_check = data_parallel_check(rt, dist, config, dims, rank, world, local_rank, nccl_id, trainer_config, tr) if world > 1 else None
+    dp_check = data_parallel_check(rt, dist, config, dims, rank, world, local_rank, nccl_id, trainer_config, tr) if world > 1 and not uncoupled else None
 
     if rank == 0:
         pk = peaks()
@@ -705,6 +743,7 @@ def main():
             "e2e": {"value": total * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(gpu_launches), "final_loss": loss, "clocks": clocks,
+            "peer_wait": peer_wait, "step_trace": trace,
             "timed_regions": {"n": len(regions), "steps_each": args.steps, "ms_per_step_median": ms_resident / args.steps,
                               "ms_per_step_min": min(regions) / args.steps, "ms_per_step_max": max(regions) / args.steps},
         }

@@ -129,6 +129,9 @@ rt_status rt_graph_num_nodes(rt_ctx* ctx, rt_graph* g, int64_t* n);
 /* Device-side timing on the context's stream (CUDA events). */
 rt_status rt_timer_start(rt_ctx* ctx);
 rt_status rt_timer_stop(rt_ctx* ctx, float* elapsed_ms); /* synchronises */
+/* A one-thread kernel that stores the GPU's nanosecond timer (%globaltimer) into *dst (device memory) when it runs: a
+ * time stamp between two kernels of a stream, usable inside a captured graph, where events cannot be read back. */
+rt_status rt_stamp(rt_ctx* ctx, unsigned long long* dst);
 
 /* ---- unary elementwise: y = f(x) and dx = g * f'(x), f' recomputed from the INPUT x ---------- */
 enum {
@@ -315,12 +318,14 @@ rt_status rt_pack_flat(rt_ctx* ctx, int n_tensors, const float* const* srcs, con
                        int clip, float clip_lo, float clip_hi);
 #define RT_DP_ID_BYTES 128
 rt_status rt_dp_unique_id(uint8_t id[RT_DP_ID_BYTES]);                /* rank 0 creates, every rank receives a copy */
-/* Joins the communicator.  The communicator is created in NCCL's non-blocking mode and the call polls
- * ncclCommGetAsyncError until every rank has joined or `timeout_ms` has passed; a rank that never joins therefore ends the
- * call with RT_ERR_TIMEOUT (the half-built communicator is aborted and the context stays usable) instead of blocking for
- * ever.  timeout_ms <= 0, RT_B200_NCCL_BLOCKING=1, or an NCCL without the non-blocking API: the plain blocking
- * ncclCommInitRank.  rt_dp_init uses RT_B200_DP_TIMEOUT_MS from the environment (default 120000).  The same deadline
- * bounds every later wait of this context on the communicator (rt_dp_allreduce_sum's enqueue, rt_dp_wait_event). */
+/* Joins the communicator.  rt_dp_init_deadline with timeout_ms > 0 creates it in NCCL's non-blocking mode and polls
+ * ncclCommGetAsyncError until every rank has joined or the deadline has passed: a rank that never joins ends the call with
+ * RT_ERR_TIMEOUT (the half-built communicator is aborted and the context stays usable) instead of blocking for ever.  The
+ * same deadline then bounds every later wait of this context on the communicator (rt_dp_allreduce_sum's enqueue,
+ * rt_dp_wait_event).  timeout_ms <= 0, or an NCCL without the non-blocking API: the plain blocking ncclCommInitRank.
+ * rt_dp_init joins a BLOCKING communicator (on a non-blocking one every all-reduce has to be polled, which costs the host
+ * more than 0.1 ms per step) unless RT_B200_NCCL_NONBLOCKING=1 is set (deadline RT_B200_DP_TIMEOUT_MS, default 120000); make
+ * sure beforehand, on the host, that every rank is there (rusttensor_b200/dp_setup.py does that with a deadline). */
 rt_status rt_dp_init(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID_BYTES]);
 rt_status rt_dp_init_deadline(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID_BYTES], int64_t timeout_ms);
 rt_status rt_dp_allreduce_sum(rt_ctx* ctx, float* buf, int64_t n);    /* in place, on the context's stream */
@@ -353,7 +358,7 @@ rt_status rt_ipc_open(rt_ctx* ctx, const uint8_t handle[RT_IPC_HANDLE_BYTES], vo
 rt_status rt_ipc_close(rt_ctx* ctx, void* peer_ptr);
 /* Step state in device memory: RT_STEP_STATE_WORDS ints, zero before the first step.  word 0 = exchange step number,
  * word 1 = step for which the peers' gradients are complete (negative: the wait for that step ran out), word 2 = optimizer
- * step count t.  Keeping it on the device lets a whole training step - including the exchange and Adam's bias
+ * step count t, word 3 = time this rank has spent in rt_dp_wait_peers so far, in units of 64 ns (a diagnostic).  Keeping it on the device lets a whole training step - including the exchange and Adam's bias
  * corrections - be replayed from one CUDA graph.  rt_dp_step_begin adds one to words 0 and 2. */
 #define RT_STEP_STATE_WORDS 4
 rt_status rt_dp_step_begin(rt_ctx* ctx, int* step_state);
@@ -365,6 +370,11 @@ rt_status rt_optimizer_step_multi_device_t(rt_ctx* ctx, int kind, int n_tensors,
 /* rt_pack_flat into flat0 or flat1, whichever the step number selects (buffer = step & 1). */
 rt_status rt_pack_flat_alternating(rt_ctx* ctx, int n_tensors, const float* const* srcs, const int64_t* sizes, float* flat0,
                                    float* flat1, const int* step_state, int clip, float clip_lo, float clip_hi);
+/* rt_pack_flat_alternating and rt_dp_signal_peers in one launch: the block of the pack kernel that finishes last writes the
+ * flags.  Falls back to the two launches when the tensor list needs more than one pack launch. */
+rt_status rt_pack_flat_signal(rt_ctx* ctx, int n_tensors, const float* const* srcs, const int64_t* sizes, float* flat0, float* flat1,
+                              const int* step_state, int clip, float clip_lo, float clip_hi, int* const* peer_flags, int rank,
+                              int world);
 /* peer_flags[r] = rank r's flag array (world ints) as opened on this rank; the entry of this rank is ignored.  Writes the
  * current step number into slot `rank` of every peer's array, after everything queued before it on the stream. */
 rt_status rt_dp_signal_peers(rt_ctx* ctx, int* const* peer_flags, int rank, int world, const int* step_state);

@@ -64,6 +64,14 @@ struct DpTrainer {
   // its step numbers from here; the host's `t` is kept in step for checkpoints.
   Storage ctrl;
   int* ctrl_ptr() { return reinterpret_cast<int*>(ctrl.ptr()); }
+  // RT_B200_DP_TRACE=1: time stamps (GPU nanosecond timer) around the parts of the captured step, read with rth_dp_trace
+  rt::B200Backend::Storage trace;
+  bool tracing = std::getenv("RT_B200_DP_TRACE") && std::getenv("RT_B200_DP_TRACE")[0] == '1';
+  void stamp(int i) {
+    if (!tracing) return;
+    if (!trace.buf) trace = B200Backend::zeros(rt::Shape{32});
+    B200Backend::check(rt_stamp(B200Backend::ctx(), reinterpret_cast<unsigned long long*>(trace.ptr()) + i));
+  }
   bool update_in_stream() const { return tr->w.optimizer != 0 && (world == 1 || fused); }
   // pipelined steps: double-buffered uploads, two loss slots with completion events
   std::vector<rt_upload*> uploads;
@@ -156,6 +164,7 @@ struct DpTrainer {
     rt_ctx* cx = B200Backend::ctx();
     if (update_in_stream()) {
       own_buffers();  // the launches below (and the graph, when capturing) keep these pointers
+      stamp(0);
       B200Backend::check(rt_dp_step_begin(cx, ctrl_ptr()));
     }
     for (auto& p : w.params) p.zero_grad();
@@ -163,8 +172,11 @@ struct DpTrainer {
     Tensor loss = rt::models::forward_loss(w, inputs);
     early_lo = early_hi = 0;
     if (world == 1 || fused) {
+      stamp(1);
       loss.backward();
+      stamp(2);
       if (update_in_stream()) update_on_device();
+      stamp(6);
       return loss;
     }
     const int n = (int)w.params.size();
@@ -323,10 +335,14 @@ struct DpTrainer {
       if (!p.grad()) throw Error(ErrorKind::NoGradientError, "parameter received no gradient");
       srcs.push_back(p.grad()->ptr());
     }
-    B200Backend::check(rt_pack_flat_alternating(c, (int)srcs.size(), srcs.data(), sizes.data(), flat2[0].ptr(), flat2[1].ptr(), ctrl_ptr(),
-                                                w.clip_grads ? 1 : 0, w.clip_lo, w.clip_hi));
-    B200Backend::check(rt_dp_signal_peers(c, peer_flags.data(), rank, world, ctrl_ptr()));
+    // pack (its last block signals the peers) -> wait -> optimizer, all on one stream: a kernel that waits for a peer never
+    // runs beside work of this rank that the peer in turn waits for (two streams may share a hardware queue, and the pack
+    // could then sit behind the spinning wait).
+    B200Backend::check(rt_pack_flat_signal(c, (int)srcs.size(), srcs.data(), sizes.data(), flat2[0].ptr(), flat2[1].ptr(), ctrl_ptr(),
+                                           w.clip_grads ? 1 : 0, w.clip_lo, w.clip_hi, peer_flags.data(), rank, world));
+    stamp(3);
     B200Backend::check(rt_dp_wait_peers(c, reinterpret_cast<const int*>(flag_store.ptr()), rank, world, ctrl_ptr(), 0));
+    stamp(4);
     UpdatePointers u = update_pointers(flat2[0].ptr());
     B200Backend::check(rt_optimizer_step_multi_peers(c, kind, (int)u.ps.size(), u.ps.data(), u.gs.data(), u.s1.data(), u.s2.data(),
                                                      sizes.data(), w.lr, w.beta1, w.beta2, w.eps, w.momentum, 1.0f / (float)world,
@@ -691,6 +707,25 @@ int rth_dp_set_state(int64_t h, int which, int i, const float* data, int64_t n) 
     auto& d = dp_get(h);
     auto& st = which == 0 ? d.state1.at(i) : d.state2.at(i);
     B200Backend::update_from_host(st, std::vector<float>(data, data + n));
+  });
+}
+// Diagnostic of the exchange over peer memory: the time (ns) this rank has spent waiting for its peers' gradients so far.
+int rth_dp_peer_wait_ns(int64_t h, int64_t* ns) {
+  return rt::capi::guarded<B200Backend>([&](auto&) {
+    int words[4] = {0, 0, 0, 0};
+    B200Backend::check(rt_memcpy_d2h(B200Backend::ctx(), words, dp_get(h).ctrl_ptr(), sizeof(words)));
+    *ns = (int64_t)(unsigned)words[3] * 64;
+  });
+}
+// RT_B200_DP_TRACE=1: the time stamps of the last step (ns): 0 step start, 1 forward done, 2 backward done, 3 gradients packed
+// and signalled, 4 peers' gradients complete, 6 optimizer done.  Synchronises.
+int rth_dp_trace(int64_t h, int64_t* out, int n) {
+  return rt::capi::guarded<B200Backend>([&](auto&) {
+    auto& d = dp_get(h);
+    if (!d.trace.buf) throw Error::invalid_op("tracing is off (RT_B200_DP_TRACE=1 before the trainer is created)");
+    std::vector<float> raw = B200Backend::copy_to_host(d.trace);
+    const unsigned long long* t = reinterpret_cast<const unsigned long long*>(raw.data());
+    for (int i = 0; i < n && i < 16; ++i) out[i] = (int64_t)t[i];
   });
 }
 // Number of floats of the flat gradient buffer: what every rank must agree on before the first exchange.

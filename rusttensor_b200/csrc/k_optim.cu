@@ -48,7 +48,7 @@ struct OptArgs {
 };
 
 // Words of the step state.
-enum { kCtrlStep = 0, kCtrlReady = 1, kCtrlT = 2, kCtrlWords = 4 };
+enum { kCtrlStep = 0, kCtrlReady = 1, kCtrlT = 2, kCtrlWaited = 3, kCtrlWords = 4 };
 
 // compiler-rt __powisf2, the lowering of f32::powi used by the reference (cpu.rs:302-303)
 __host__ __device__ inline float powi_f32(float a, int b) {
@@ -190,11 +190,18 @@ __global__ void __launch_bounds__(kThreads) optimizer_peer_kernel(const __grid_c
   if (vec) {
     const int64_t end4 = base + ((end - base) & ~int64_t(3));
     for (int64_t i = base + threadIdx.x * 4; i < end4; i += kThreads * 4) {
+      // every rank's load is issued before the first one is used (a remote load takes a few microseconds); the sum
+      // then runs in rank order, the same on every rank
+      float4 t[kMaxPeers];
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r)
+        if (r < pa.world) t[r] = ld_peer4(pa.flat[buf][r] + goff + i);
       float4 gv = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int r = 0; r < pa.world; ++r) {  // rank order: the same sum on every rank
-        const float4 t = ld_peer4(pa.flat[buf][r] + goff + i);
-        gv.x += t.x; gv.y += t.y; gv.z += t.z; gv.w += t.w;
-      }
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r)
+        if (r < pa.world) {
+          gv.x += t[r].x; gv.y += t[r].y; gv.z += t[r].z; gv.w += t[r].w;
+        }
       float4 pv = *reinterpret_cast<float4*>(p + i);
       float4 m = make_float4(0, 0, 0, 0), v = make_float4(0, 0, 0, 0);
       if (KIND != 0) m = *reinterpret_cast<float4*>(s1 + i);
@@ -210,8 +217,14 @@ __global__ void __launch_bounds__(kThreads) optimizer_peer_kernel(const __grid_c
     base = end4;
   }
   for (int64_t i = base + threadIdx.x; i < end; i += kThreads) {
+    float t[kMaxPeers];
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < pa.world) t[r] = ld_peer1(pa.flat[buf][r] + goff + i);
     float g = 0.f;
-    for (int r = 0; r < pa.world; ++r) g += ld_peer1(pa.flat[buf][r] + goff + i);
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < pa.world) g += t[r];
     float pv = p[i], m = KIND != 0 ? s1[i] : 0.f, v = KIND == 1 ? s2[i] : 0.f;
     update<KIND>(pv, g, m, v, a, bc1, bc2);
     p[i] = pv;
@@ -246,12 +259,19 @@ __global__ void dp_signal_kernel(const SignalArgs sa, const int* ctrl) {
 // One block: thread r waits (bounded) until rank r has signalled this step, then the block marks the step ready - or,
 // when a wait ran out, records a code in the status word and marks the step failed, so that the optimizer kernel that
 // follows leaves parameters and state untouched in ALL of its blocks.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
 __global__ void dp_wait_kernel(const int* flags, int world, int rank, int* ctrl, uint32_t spin_limit, int* status) {
   __shared__ int bad;
   if (threadIdx.x == 0) bad = 0;
   __syncthreads();
   const int step = ctrl[kCtrlStep];
   const int r = threadIdx.x;
+  const unsigned long long t0 = global_timer_ns();
   if (r < world && r != rank) {
     const volatile int* f = flags + r;
     uint32_t spins = 0;
@@ -265,6 +285,8 @@ __global__ void dp_wait_kernel(const int* flags, int world, int rank, int* ctrl,
   }
   __syncthreads();
   if (threadIdx.x == 0) {
+    // how long this rank waited for its slowest peer, accumulated in units of 64 ns (a diagnostic: read with rt_memcpy_d2h)
+    ctrl[kCtrlWaited] += (int)((global_timer_ns() - t0) >> 6);
     __threadfence_system();
     if (bad) {
       volatile int* s = status;
@@ -288,7 +310,12 @@ struct PackArgs {
 };
 
 // flat1 / ctrl may be null; with them the destination alternates with the step number (buffer = step & 1).
-__global__ void __launch_bounds__(kThreads) pack_kernel(const __grid_constant__ PackArgs a, float* flat0, float* flat1, const int* ctrl) {
+// SIGNAL: the block that finishes last (a ticket) also writes the step number into this rank's slot of every peer's flag
+// array, which saves the separate signalling launch.  Every block makes its part of the buffer visible system-wide before it
+// draws its ticket, so the buffer is complete in this GPU's memory when a peer sees the flag.
+template <bool SIGNAL>
+__global__ void __launch_bounds__(kThreads) pack_kernel(const __grid_constant__ PackArgs a, float* flat0, float* flat1, const int* ctrl,
+                                                         const SignalArgs sa, unsigned* ticket) {
   float* __restrict__ flat = (ctrl && (ctrl[kCtrlStep] & 1)) ? flat1 : flat0;
   int ti = 0;
   while (ti + 1 < a.count && (int)blockIdx.x >= a.block_start[ti + 1]) ++ti;
@@ -313,6 +340,22 @@ __global__ void __launch_bounds__(kThreads) pack_kernel(const __grid_constant__ 
     float v = s[i];
     if (a.clip) v = fminf(fmaxf(v, a.clip_lo), a.clip_hi);
     d[i] = v;
+  }
+  if (SIGNAL) {
+    __shared__ int is_last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      is_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+      if (is_last) *ticket = 0;
+    }
+    __syncthreads();
+    const int r = threadIdx.x;
+    if (is_last && r < sa.world && r != sa.rank) {
+      const int step = ctrl[kCtrlStep];
+      __threadfence_system();
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(sa.flags[r] + sa.rank), "r"(step) : "memory");
+    }
   }
 }
 
@@ -403,7 +446,7 @@ rt_status rt_adam_step(rt_ctx* ctx, float* param, const float* grad, float* m, f
 }
 
 static rt_status pack_flat_impl(rt_ctx* ctx, int n_tensors, const float* const* srcs, const int64_t* sizes, float* flat0, float* flat1,
-                                const int* ctrl, int clip, float clip_lo, float clip_hi) {
+                                const int* ctrl, int clip, float clip_lo, float clip_hi, const SignalArgs* signal = nullptr) {
   if (n_tensors <= 0) return RT_OK;
   RT_CHECK_PTR(ctx, srcs);
   RT_CHECK_PTR(ctx, sizes);
@@ -431,7 +474,12 @@ static rt_status pack_flat_impl(rt_ctx* ctx, int n_tensors, const float* const* 
     if (a.count == 0) continue;
     a.block_start[a.count] = blocks;
     a.clip = clip; a.clip_lo = clip_lo; a.clip_hi = clip_hi;
-    pack_kernel<<<blocks, kThreads, 0, ctx->stream>>>(a, flat0, flat1, ctrl);
+    if (signal) {
+      unsigned* ticket = ctx->reduce_counters + 2 * kReduceCounterSlots + (ctx->on_side ? kAuxCounterSlots : 0) + kAuxCounterSlots - 1;
+      pack_kernel<true><<<blocks, kThreads, 0, ctx->stream>>>(a, flat0, flat1, ctrl, *signal, ticket);
+    } else {
+      pack_kernel<false><<<blocks, kThreads, 0, ctx->stream>>>(a, flat0, flat1, ctrl, SignalArgs{}, nullptr);
+    }
     RT_LAUNCHED(ctx);
   }
   return RT_OK;
@@ -449,6 +497,29 @@ rt_status rt_pack_flat_alternating(rt_ctx* ctx, int n_tensors, const float* cons
   RT_CHECK_PTR(ctx, flat1);
   RT_CHECK_PTR(ctx, step_state);
   return pack_flat_impl(ctx, n_tensors, srcs, sizes, flat0, flat1, step_state, clip, clip_lo, clip_hi);
+}
+
+rt_status rt_pack_flat_signal(rt_ctx* ctx, int n_tensors, const float* const* srcs, const int64_t* sizes, float* flat0, float* flat1,
+                              const int* step_state, int clip, float clip_lo, float clip_hi, int* const* peer_flags, int rank,
+                              int world) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, flat1);
+  RT_CHECK_PTR(ctx, step_state);
+  RT_CHECK_PTR(ctx, peer_flags);
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_pack_flat_signal: rank %d of %d (at most %d peers)", rank, world, kMaxPeers);
+  int live = 0;
+  for (int i = 0; i < n_tensors; ++i) live += sizes && sizes[i] > 0;
+  if (n_tensors > kMaxTensors || live == 0 || !ctx->reduce_counters) {  // several pack launches, or nothing to pack: signal separately
+    rt_status st = pack_flat_impl(ctx, n_tensors, srcs, sizes, flat0, flat1, step_state, clip, clip_lo, clip_hi);
+    return st != RT_OK ? st : rt_dp_signal_peers(ctx, peer_flags, rank, world, step_state);
+  }
+  SignalArgs sa;
+  for (int r = 0; r < kMaxPeers; ++r) sa.flags[r] = r < world ? peer_flags[r] : nullptr;
+  for (int r = 0; r < world; ++r)
+    if (r != rank && !sa.flags[r]) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_pack_flat_signal: no flag array for rank %d", r);
+  sa.world = world; sa.rank = rank;
+  return pack_flat_impl(ctx, n_tensors, srcs, sizes, flat0, flat1, step_state, clip, clip_lo, clip_hi, &sa);
 }
 
 rt_status rt_dp_step_begin(rt_ctx* ctx, int* step_state) {

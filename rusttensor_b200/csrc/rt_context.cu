@@ -536,6 +536,19 @@ rt_status rt_timer_stop(rt_ctx* ctx, float* ms) {
   return rt_take_status(ctx, nullptr);
 }
 
+__global__ void stamp_kernel(unsigned long long* dst) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  *dst = t;
+}
+rt_status rt_stamp(rt_ctx* ctx, unsigned long long* dst) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, dst);
+  stamp_kernel<<<1, 1, 0, ctx->stream>>>(dst);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
 // ---- NCCL, resolved at run time so that the library loads on machines without it ---
 // RT_B200_NCCL_LIBRARY names the shared object to load instead of libnccl.so.2 (the failure-handling tests load a
 // scripted stand-in through it).
@@ -647,9 +660,7 @@ rt_status rt_dp_init_deadline(rt_ctx* ctx, int rank, int world, const uint8_t id
   NcclId nid;
   memcpy(&nid, id, sizeof(nid));
   RT_CUDA(ctx, cudaSetDevice(ctx->device));
-  const char* blocking_env = getenv("RT_B200_NCCL_BLOCKING");
-  bool nonblocking = timeout_ms > 0 && !(blocking_env && blocking_env[0] == '1') && n.CommInitRankConfig && n.CommGetAsyncError &&
-                     n.CommAbort;
+  bool nonblocking = timeout_ms > 0 && n.CommInitRankConfig && n.CommGetAsyncError && n.CommAbort;
 #ifndef RT_HAVE_NCCL_HEADER
   nonblocking = false;  // the configuration structure comes from NCCL's own header
 #endif
@@ -682,9 +693,17 @@ rt_status rt_dp_init_deadline(rt_ctx* ctx, int rank, int world, const uint8_t id
 }
 
 rt_status rt_dp_init(rt_ctx* ctx, int rank, int world, const uint8_t id[RT_DP_ID_BYTES]) {
-  int64_t timeout_ms = 120000;
-  const char* env = getenv("RT_B200_DP_TIMEOUT_MS");
-  if (env && env[0]) timeout_ms = atoll(env);
+  // Blocking communicator by default: on a non-blocking one every ncclAllReduce answers "in progress" and has to be polled,
+  // which measured 0.13 ms of host time per step on eight B200s (end-to-end step 0.46 ms against 0.33 ms).  Callers that
+  // want the join bounded use rt_dp_init_deadline or set RT_B200_NCCL_NONBLOCKING=1 (deadline RT_B200_DP_TIMEOUT_MS,
+  // default 120000); the asynchronous-error watchdog (rt_dp_async_error, rt_dp_wait_event) works on either kind.
+  int64_t timeout_ms = 0;
+  const char* nb = getenv("RT_B200_NCCL_NONBLOCKING");
+  if (nb && nb[0] == '1') {
+    timeout_ms = 120000;
+    const char* env = getenv("RT_B200_DP_TIMEOUT_MS");
+    if (env && env[0]) timeout_ms = atoll(env);
+  }
   return rt_dp_init_deadline(ctx, rank, world, id, timeout_ms);
 }
 

@@ -78,6 +78,20 @@ class DataParallelTrainer:
         return k.value
 
     @property
+    def peer_wait_ns(self):
+        """Time this rank has spent waiting for its peers' gradients in the exchange over peer memory (synchronises)."""
+        n = C.c_int64(0)
+        self._call("dp_peer_wait_ns", C.c_int64(self.handle), C.byref(n))
+        return n.value
+
+    def trace(self):
+        """RT_B200_DP_TRACE=1: GPU time stamps (ns) of the last step: [start, forward done, backward done, packed + signalled,
+        peers complete, -, optimizer done]; zeros where a stamp does not exist in this mode."""
+        out = (C.c_int64 * 8)()
+        self._call("dp_trace", C.c_int64(self.handle), out, C.c_int(8))
+        return list(out)
+
+    @property
     def flat_len(self):
         """Floats in the flat gradient buffer (every tensor's start padded to 16 bytes): equal on all ranks of a job."""
         n = C.c_int64(0)
@@ -158,12 +172,13 @@ class DataParallelTrainer:
         discarded and a new one used with the NCCL exchange).  All collectives run on every rank whatever fails."""
         import torch
 
+        device = "cuda" if dist.get_backend() == "nccl" else "cpu"
         ok, blob = 1, bytes(192)
         try:
             blob = self.fused_export()
         except Exception as e:  # noqa: BLE001
             ok, self.peer_error = 0, str(e)
-        mine = torch.tensor(list(blob) + [ok], dtype=torch.uint8, device="cuda")
+        mine = torch.tensor(list(blob) + [ok], dtype=torch.uint8, device=device)
         parts = [torch.zeros_like(mine) for _ in range(self.world)]
         dist.all_gather(parts, mine)
         rows = [bytes(p.cpu().tolist()) for p in parts]
@@ -173,7 +188,7 @@ class DataParallelTrainer:
                 self.fused_connect(b"".join(r[:192] for r in rows))
             except Exception as e:  # noqa: BLE001
                 ok, self.peer_error = 0, str(e)
-        flag = torch.tensor([ok], dtype=torch.int32, device="cuda")
+        flag = torch.tensor([ok], dtype=torch.int32, device=device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         return bool(flag.item())
 
