@@ -131,7 +131,7 @@ rt_status rt_timer_start(rt_ctx* ctx);
 rt_status rt_timer_stop(rt_ctx* ctx, float* elapsed_ms); /* synchronises */
 /* A one-thread kernel that stores the GPU's nanosecond timer (%globaltimer) into *dst (device memory) when it runs: a
  * time stamp between two kernels of a stream, usable inside a captured graph, where events cannot be read back. */
-rt_status rt_stamp(rt_ctx* ctx, unsigned long long* dst);
+rt_status rt_stamp(rt_ctx* ctx, uint64_t* dst);
 
 /* ---- unary elementwise: y = f(x) and dx = g * f'(x), f' recomputed from the INPUT x ---------- */
 enum {

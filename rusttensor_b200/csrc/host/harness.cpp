@@ -70,7 +70,7 @@ struct DpTrainer {
   void stamp(int i) {
     if (!tracing) return;
     if (!trace.buf) trace = B200Backend::zeros(rt::Shape{32});
-    B200Backend::check(rt_stamp(B200Backend::ctx(), reinterpret_cast<unsigned long long*>(trace.ptr()) + i));
+    B200Backend::check(rt_stamp(B200Backend::ctx(), reinterpret_cast<uint64_t*>(trace.ptr()) + i));
   }
   bool update_in_stream() const { return tr->w.optimizer != 0 && (world == 1 || fused); }
   // pipelined steps: double-buffered uploads, two loss slots with completion events

@@ -541,10 +541,10 @@ __global__ void stamp_kernel(unsigned long long* dst) {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   *dst = t;
 }
-rt_status rt_stamp(rt_ctx* ctx, unsigned long long* dst) {
+rt_status rt_stamp(rt_ctx* ctx, uint64_t* dst) {
   RT_CHECK_CTX(ctx);
   RT_CHECK_PTR(ctx, dst);
-  stamp_kernel<<<1, 1, 0, ctx->stream>>>(dst);
+  stamp_kernel<<<1, 1, 0, ctx->stream>>>(reinterpret_cast<unsigned long long*>(dst));
   RT_LAUNCHED(ctx);
   return RT_OK;
 }
