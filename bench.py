@@ -462,6 +462,9 @@ def main():
     ap.add_argument("--conv-kernels", default=None, metavar="N,CIN,HW,COUT",
                     help="run rt_conv2d_backward (3x3, stride 1, padding 1; dx, dw and db) a few times on this shape and exit: the small, "
                          "self-contained command the ncu captures of the convolution-gradient kernels are taken on")
+    ap.add_argument("--steps-only", type=int, default=0, metavar="N",
+                    help="run N captured training steps of --workload (with --fused-forward: its fused variant) and exit: the small command "
+                         "the per-step kernel listing is captured on")
     ap.add_argument("--mma-rate", action="store_true",
                     help="print the issue-rate table of tcgen05.mma.kind::tf32 (cycles per MMA by shape and A-operand source)")
     args = ap.parse_args()
@@ -492,6 +495,22 @@ def main():
                           C.c_int(3), C.c_int(3), C.c_int(1), C.c_int(1), C.c_int(1), C.c_int(1), dx.ptr, dw.ptr, db.ptr)
             capi.sync()
             print(json.dumps({"conv_kernels": args.conv_kernels, "calls": 3, "checksum_dw": float(np.abs(dw.numpy()).sum())}))
+        return
+    if args.steps_only:
+        # a few captured training steps and nothing else: the command the per-step kernel listing (ncu launch list with
+        # --cache-control none) is taken on; the last `nodes` launches of the capture are one whole step in order
+        if rank == 0:
+            config, dims, per_gpu, desc = WORKLOADS[args.workload]
+            tr = rt.DataParallelTrainer(config + (100 if args.fused_forward else 0), dims, device=local_rank)
+            params, inputs = workload_data(config, dims, seed=0)
+            for t, p in zip(tr.params, params):
+                t.update_from_host(p)
+            for _ in range(2):
+                tr.step(inputs)
+            tr.last_loss()
+            for _ in range(args.steps_only):
+                tr.step(None)
+            print(json.dumps({"steps_only": args.steps_only, "workload": desc, "loss": tr.last_loss(), "kernels_per_step": tr.graph_nodes()}))
         return
     if args.mma_rate:
         if rank == 0:

@@ -23,6 +23,20 @@ def test_library_exports_every_declared_symbol():
     assert not missing, missing
 
 
+def test_rust_binding_is_generated_from_the_current_header(tmp_path):
+    """include/b200_backend.rs is what include/gen_rust_shim.py makes of include/rt_b200.h today: a changed header without a
+    regenerated binding fails here."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("gen_rust_shim", os.path.join(ROOT, "include", "gen_rust_shim.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    fresh = gen.TEMPLATE.replace("@ENUMS@", gen.enum_consts()).replace("@FFI@", gen.ffi_block()).replace("@IMPL@", gen.impl_block())
+    assert fresh == open(os.path.join(ROOT, "include", "b200_backend.rs")).read()
+    names = [n for n, _, _ in gen.parse_header()]
+    assert len(names) == len(set(names)) >= 99
+
+
 def test_host_library_exports_engine_api():
     host = rusttensor_b200.load_host_library()
     for name in ("rth_init", "rth_op", "rth_backward", "rth_tensor_from_host", "rth_optim_step", "rth_trainer_run",
