@@ -725,7 +725,7 @@ def main():
                 tr2.step(None)
             ms2 = float(np.median(timed(lambda: tr2.step(None), args.steps, repeats=min(3, args.repeats))))
             fused_line = {"value": per_gpu * world * args.steps / (ms2 * 1e-3), "unit": "samples/s", "ms_per_step": ms2 / args.steps,
-                          "note": "same network from the fused forward ops (ops::fused_relu_max_pool2d, ops::fused_softmax_nll, ops::fused_lstm_cell_c/_h)"}
+                          "note": "same network from the fused forward ops (ops::fused_conv2d_relu_max_pool2d, ops::fused_relu_max_pool2d, ops::fused_softmax_nll, ops::fused_lstm_cell_c/_h)"}
             del tr2
         except Exception as e:  # noqa: BLE001  (the headline above does not depend on this extra measurement)
             fused_line = {"unavailable": str(e)}

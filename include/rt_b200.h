@@ -265,6 +265,11 @@ rt_status rt_relu_max_pool2d(rt_ctx* ctx, const float* x, int64_t n, int64_t c, 
                              int sh, int sw, int ph, int pw, float* y, float* idx);
 rt_status rt_relu_max_pool2d_backward(rt_ctx* ctx, const float* x, const float* g, const float* idx, int64_t n, int64_t c,
                                       int64_t h, int64_t w, int kh, int kw, int sh, int sw, int ph, int pw, float* dx);
+/* The same from the POOLED output, for a 2x2 window with stride 2 over an un-pooled tensor [n, c, h, w] with even h and w:
+ * dx routes g through idx where y > 0 (y = relu of the window's maximum, so y > 0 exactly when the input at the saved position
+ * was positive).  Bit-identical to rt_relu_max_pool2d_backward; the un-pooled tensor is not needed. */
+rt_status rt_relu_max_pool2x2_backward_from_output(rt_ctx* ctx, const float* y, const float* g, const float* idx, int64_t n, int64_t c,
+                                                   int64_t h, int64_t w, float* dx);
 
 /* ---- dense contractions ---------------------------------------------------------------------- */
 /* C[M,N] = op(A) * op(B) (+ C when accumulate != 0); row-major with leading dimensions.
@@ -279,6 +284,13 @@ rt_status rt_matmul_backward(rt_ctx* ctx, const float* a, const float* b, const 
 /* conv2d mod.rs:101: x[N,Cin,H,W], w[Cout,Cin,kh,kw], bias[Cout] or NULL -> y[N,Cout,Ho,Wo] */
 rt_status rt_conv2d(rt_ctx* ctx, const float* x, const float* w, const float* bias, int64_t n, int64_t cin,
                     int64_t h, int64_t wd, int64_t cout, int kh, int kw, int sh, int sw, int ph, int pw, float* y);
+/* Fused conv2d + bias + relu + max_pool2d(2x2, stride 2) (no counterpart in the reference, whose CNN example calls the three
+ * ops one after the other, examples/train_mnist_cnn_cpu.rs:216-233): y, idx [n, cout, Ho/2, Wo/2]; the convolution output (Ho x
+ * Wo, both even) is not kept.  Values and indices are bit-identical to rt_conv2d -> relu -> rt_max_pool2d.  Single-channel 3x3
+ * unit-stride layers run as one kernel; other shapes as the convolution into scratch memory followed by the fused relu + pool
+ * kernel.  Backward: rt_relu_max_pool2x2_backward_from_output, then rt_conv2d_backward. */
+rt_status rt_conv2d_relu_max_pool2x2(rt_ctx* ctx, const float* x, const float* w, const float* bias, int64_t n, int64_t cin, int64_t h,
+                                     int64_t wd, int64_t cout, int kh, int kw, int sh, int sw, int ph, int pw, float* y, float* idx);
 /* conv2d_backward mod.rs:111: any of dx, dw, db may be NULL.  dx is the mathematically correct
  * input gradient (the reference CPU code's col2im reuses column 0, src/ops/cpu_ops.rs:266). */
 rt_status rt_conv2d_backward(rt_ctx* ctx, const float* x, const float* w, const float* g, int64_t n, int64_t cin,

@@ -100,7 +100,7 @@ struct OpType {
     Sigmoid, Sqrt, Tanh, Softplus, Max, Min, Prod, LogSumExp, ArgMax, ArgMin, Powf, Square,
     Maximum, Minimum, Elu, Transpose, Sin, Cos, Tan, Conv2d, MaxPool2D, Conv2DTranspose, Slice,
     Concat, ExpandDims, Squeeze, Clip, DivScalar, MulScalar,
-    FusedReluMaxPool2D, FusedSoftmaxNll, FusedLstmCellC, FusedLstmCellH  // fused forward ops added beside the reference's (ops::fused_*)
+    FusedReluMaxPool2D, FusedSoftmaxNll, FusedLstmCellC, FusedLstmCellH, FusedConvReluMaxPool2D  // fused forward ops added beside the reference's (ops::fused_*)
   } kind;
   std::optional<size_t> axis;          // Mean/Sum/Max/Min/Prod/LogSumExp(Option), LogSoftmax/ArgMax/...
   float scalar = 0.f;                  // Elu(alpha), MulScalar, DivScalar
@@ -120,7 +120,7 @@ struct OpType {
       "Div", "Exp", "Ln", "Broadcast", "View", "Abs", "Sigmoid", "Sqrt", "Tanh", "Softplus", "Max",
       "Min", "Prod", "LogSumExp", "ArgMax", "ArgMin", "Powf", "Square", "Maximum", "Minimum", "Elu",
       "Transpose", "Sin", "Cos", "Tan", "Conv2d", "MaxPool2D", "Conv2DTranspose", "Slice", "Concat",
-      "ExpandDims", "Squeeze", "Clip", "DivScalar", "MulScalar", "FusedReluMaxPool2D", "FusedSoftmaxNll", "FusedLstmCellC", "FusedLstmCellH"};
+      "ExpandDims", "Squeeze", "Clip", "DivScalar", "MulScalar", "FusedReluMaxPool2D", "FusedSoftmaxNll", "FusedLstmCellC", "FusedLstmCellH", "FusedConvReluMaxPool2D"};
     return n[(int)kind];
   }
 };
@@ -833,6 +833,38 @@ Tensor<B> fused_relu_max_pool2d(const Tensor<B>& input, Pair kernel, Pair stride
       t.set_op(Op<B>(ot, {input, idx}, [](const Op<B>& op, const St<B>& g) {
         St<B> gi = B::relu_max_pool2d_backward(op, g);
         return Grads<B>{std::move(gi), B::unused_grad(B::shape(op.inputs[1].data()))};
+      }));
+    }
+    return t;
+  }
+}
+
+// max_pool2d(relu(conv2d(x, w, bias)), 2x2, stride 2): the head of a CNN block as the reference's example spells it with three
+// ops (examples/train_mnist_cnn_cpu.rs:216-233).  The convolution output is never kept: the backward pass gets the gradient of
+// the convolution output from the pooled values (y > 0 exactly where the winning input was positive) and the saved indices.
+template <class B>
+Tensor<B> fused_conv2d_relu_max_pool2d(const Tensor<B>& input, const Tensor<B>& weights, const Tensor<B>* bias, Pair stride,
+                                       Pair padding) {
+  if constexpr (!HasFusedForward<B>::value) {
+    return max_pool2d(relu(conv2d(input, weights, bias, stride, padding)), {2, 2}, {2, 2}, {0, 0});
+  } else {
+    auto r = B::conv2d_relu_max_pool2x2(input.data(), weights.data(), bias ? &bias->data() : nullptr, stride, padding);
+    bool rg = input.requires_grad() || weights.requires_grad() || (bias && bias->requires_grad());
+    Tensor<B> t(r.first, rg);  // shares the buffer with the saved copy below (buffers are immutable)
+    if (rg) {
+      OpType ot(OpType::FusedConvReluMaxPool2D);
+      ot.stride = stride;
+      ot.padding = padding;
+      ot.kernel_size = {2, 2};
+      Tensor<B> b = bias ? *bias : Tensor<B>(B::zeros(Shape{weights.shape()[0]}), false);
+      Tensor<B> y_saved(std::move(r.first), false), idx(std::move(r.second), false);
+      t.set_op(Op<B>(ot, {input, weights, b, y_saved, idx}, [](const Op<B>& op, const St<B>& g) {
+        auto gr = B::conv2d_relu_max_pool2x2_backward(op.inputs[0].data(), op.inputs[1].data(), op.inputs[3].data(), op.inputs[4].data(), g,
+                                                      op.op_type.stride, op.op_type.padding, op.inputs[0].requires_grad(),
+                                                      op.inputs[1].requires_grad(), op.inputs[2].requires_grad());
+        St<B> gb = std::get<2>(gr) ? std::move(*std::get<2>(gr)) : B::zeros(Shape{0});
+        return Grads<B>{std::move(std::get<0>(gr)), std::move(std::get<1>(gr)), std::move(gb), B::unused_grad(B::shape(op.inputs[3].data())),
+                        B::unused_grad(B::shape(op.inputs[4].data()))};
       }));
     }
     return t;

@@ -593,6 +593,29 @@ struct B200Backend {
                              (int)s.second, (int)p.first, (int)p.second, dx.ptr(), dw.ptr(), db.ptr()));
     return {std::move(dx), std::move(dw), std::optional<Storage>(std::move(db))};
   }
+  // max_pool2d(relu(conv2d(x, w) + bias), 2x2, stride 2) without keeping the convolution output: {pooled values, indices}
+  static std::pair<Storage, Storage> conv2d_relu_max_pool2x2(const Storage& x, const Storage& w, const Storage* bias, Pair s, Pair p) {
+    conv_shapes(x, w, "conv2d_relu_max_pool2x2");
+    if (x.shape[1] != w.shape[1]) throw Error::invalid_op("conv2d_relu_max_pool2x2: input channels != weight channels");
+    if (bias && bias->numel() != w.shape[0]) throw Error::invalid_op("conv2d_relu_max_pool2x2: bias shape mismatch");
+    size_t ho = (x.shape[2] + 2 * p.first - w.shape[2]) / s.first + 1, wo = (x.shape[3] + 2 * p.second - w.shape[3]) / s.second + 1;
+    if ((ho & 1) || (wo & 1)) throw Error::invalid_op("conv2d_relu_max_pool2x2: the convolution output must have even extents");
+    Storage y = alloc(Shape{x.shape[0], w.shape[0], ho / 2, wo / 2}), idx = alloc(Shape{x.shape[0], w.shape[0], ho / 2, wo / 2});
+    check(rt_conv2d_relu_max_pool2x2(ctx(), x.ptr(), w.ptr(), bias ? bias->ptr() : nullptr, (int64_t)x.shape[0], (int64_t)x.shape[1],
+                                     (int64_t)x.shape[2], (int64_t)x.shape[3], (int64_t)w.shape[0], (int)w.shape[2], (int)w.shape[3],
+                                     (int)s.first, (int)s.second, (int)p.first, (int)p.second, y.ptr(), idx.ptr()));
+    return {std::move(y), std::move(idx)};
+  }
+  // Its backward: the gradient of the convolution output from the pooled output and the indices, then conv2d_backward.
+  static std::tuple<Storage, Storage, std::optional<Storage>> conv2d_relu_max_pool2x2_backward(
+      const Storage& x, const Storage& w, const Storage& y, const Storage& idx, const Storage& g, Pair s, Pair p, bool need_x, bool need_w,
+      bool need_b) {
+    if (g.shape != y.shape) throw Error::shape_mismatch(y.shape, g.shape);
+    Storage dconv = alloc(Shape{y.shape[0], y.shape[1], y.shape[2] * 2, y.shape[3] * 2});
+    check(rt_relu_max_pool2x2_backward_from_output(ctx(), y.ptr(), g.ptr(), idx.ptr(), (int64_t)y.shape[0], (int64_t)y.shape[1],
+                                                   (int64_t)y.shape[2] * 2, (int64_t)y.shape[3] * 2, dconv.ptr()));
+    return conv2d_backward(x, w, dconv, s, p, need_x, need_w, need_b);
+  }
   static Storage conv2d_transpose(const Storage& x, const Storage& w, const Storage* bias, Pair s, Pair p) {
     if (x.shape.size() != 4) throw Error(ErrorKind::ShapeError, "Expected 4D input tensor for conv2d_transpose");
     if (w.shape.size() != 4) throw Error(ErrorKind::ShapeError, "Expected 4D weights tensor for conv2d_transpose");

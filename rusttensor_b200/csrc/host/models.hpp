@@ -170,10 +170,12 @@ Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
     }
     case C3_CNN: {
       size_t n = in.at(0).shape()[0];
-      Tensor<B> c1 = ops::conv2d(in[0], p[0], &p[1], {1, 1}, {1, 1});
-      Tensor<B> p1 = relu_pool(c1);
-      Tensor<B> c2 = ops::conv2d(p1, p[2], &p[3], {1, 1}, {1, 1});
-      Tensor<B> p2 = relu_pool(c2);
+      auto block = [&](const Tensor<B>& x, const Tensor<B>& wt, const Tensor<B>& b) {
+        if (w.fused_forward) return ops::fused_conv2d_relu_max_pool2d(x, wt, &b, {1, 1}, {1, 1});
+        return relu_pool(ops::conv2d(x, wt, &b, {1, 1}, {1, 1}));
+      };
+      Tensor<B> p1 = block(in[0], p[0], p[1]);
+      Tensor<B> p2 = block(p1, p[2], p[3]);
       Tensor<B> flat = p2.view({n, p[4].shape()[0]});
       Tensor<B> f1 = ops::relu(linear(flat, p[4], p[5], w.fused_forward));
       Tensor<B> logits = linear(f1, p[6], p[7], w.fused_forward);
@@ -181,8 +183,8 @@ Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
       return ops::softmax_cross_entropy(logits, in.at(1), 1, Reduction::Mean);
     }
     case C4_CONV_CONVT: {
-      Tensor<B> c = ops::conv2d(in.at(0), p[0], &p[1], {1, 1}, {1, 1});
-      Tensor<B> pl = relu_pool(c);
+      Tensor<B> pl = w.fused_forward ? ops::fused_conv2d_relu_max_pool2d(in.at(0), p[0], &p[1], {1, 1}, {1, 1})
+                                     : relu_pool(ops::conv2d(in.at(0), p[0], &p[1], {1, 1}, {1, 1}));
       Tensor<B> up = ops::conv2d_transpose(pl, p[2], &p[3], {2, 2}, {1, 1});
       return ops::mse_loss(up, in.at(1), Reduction::Mean);
     }

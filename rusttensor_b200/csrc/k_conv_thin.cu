@@ -3,7 +3,8 @@
 // FP32 kernels.  A thread owns one output pixel and keeps its taps in registers.
 //   forward:          y[b,n,p] = bias[n] + sum_t tap_t(b,p) * w[n,t]
 //   weight gradient:  dw[n,t]  = sum_{b,p} g[b,n,p] * tap_t(b,p)   (per-warp partial sums over a pixel
-//                     range, then a deterministic second pass)
+//                     range, then a deterministic second pass; single-channel 3x3 layers: whole images per block, with db)
+//   forward fused with bias + relu + 2x2 max pooling for single-channel 3x3 layers
 // tap_t(b,p) = x[b, c, yo*sh-ph+ky, xo*sw-pw+kx] for t = (c,ky,kx), zero outside the image.
 #include "rt_internal.cuh"
 #include "conv_geom.cuh"
@@ -320,6 +321,69 @@ __global__ void __launch_bounds__(kImgThreads) thin_dw_image_kernel(const ImageD
   }
 }
 
+// ---- conv2d (single channel, 3x3, unit stride) + bias + relu + 2x2/stride-2 max pooling in one pass ----------------------
+// A thread owns one pooled pixel and a group of 16 output channels: it reads the 4x4 input patch its 2x2 window of
+// convolution outputs touches once, and for every channel forms the four outputs with the SAME sequence of fused multiply-adds
+// as thin_conv_forward_kernel (bias first, then the taps in (ky, kx) order), applies relu and keeps the first maximum in window
+// order - so values and indices are bit-identical to conv2d -> relu -> max_pool2d, and the convolution output never exists.
+struct ThinPoolParams {
+  const float* x;  // [Nb, 1, H, W]
+  int Nb, H, W, N, Hp, Wp, ph, pw;  // Hp x Wp: the pooled extent (convolution output Ho = 2*Hp, Wo = 2*Wp)
+  int64_t pooled;                   // Nb * Hp * Wp
+  FastDiv d_HpWp, d_Wp;
+};
+constexpr int kPoolChannelGroup = 16;
+
+__global__ void __launch_bounds__(kThreads) thin_conv_relu_pool_kernel(const ThinPoolParams p, const float* __restrict__ w,
+                                                                        const float* __restrict__ bias, float* __restrict__ y,
+                                                                        float* __restrict__ idx) {
+  __shared__ float w_s[kPoolChannelGroup][9];
+  __shared__ float b_s[kPoolChannelGroup];
+  const int n0 = blockIdx.y * kPoolChannelGroup;
+  const int nn = min(kPoolChannelGroup, p.N - n0);
+  for (int i = threadIdx.x; i < nn * 9; i += kThreads) w_s[i / 9][i % 9] = __ldg(w + (n0 + i / 9) * 9 + i % 9);
+  for (int i = threadIdx.x; i < nn; i += kThreads) b_s[i] = bias ? __ldg(bias + n0 + i) : 0.f;
+  __syncthreads();
+  const int hpwp = p.Hp * p.Wp;
+  for (int64_t q = (int64_t)blockIdx.x * kThreads + threadIdx.x; q < p.pooled; q += (int64_t)gridDim.x * kThreads) {
+    uint32_t b, r, yp, xp;
+    p.d_HpWp.divmod((uint32_t)q, b, r);
+    p.d_Wp.divmod(r, yp, xp);
+    float patch[4][4];
+    const int y0 = 2 * (int)yp - p.ph, x0 = 2 * (int)xp - p.pw;
+    const float* img = p.x + (int64_t)b * p.H * p.W;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int iy = y0 + i, ix = x0 + j;
+        patch[i][j] = ((unsigned)iy < (unsigned)p.H && (unsigned)ix < (unsigned)p.W) ? __ldg(img + iy * p.W + ix) : 0.f;
+      }
+    float* yo = y + ((int64_t)b * p.N + n0) * hpwp + r;
+    float* io = idx + ((int64_t)b * p.N + n0) * hpwp + r;
+    for (int n = 0; n < nn; ++n) {
+      float v[4];
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        const int dy = d >> 1, dx = d & 1;
+        float acc = b_s[n];
+#pragma unroll
+        for (int ky = 0; ky < 3; ++ky)
+#pragma unroll
+          for (int kx = 0; kx < 3; ++kx) acc = fmaf(patch[dy + ky][dx + kx], w_s[n][ky * 3 + kx], acc);
+        v[d] = fmaxf(acc, 0.f);
+      }
+      float mv = -INFINITY;
+      int mi = 0;
+#pragma unroll
+      for (int d = 0; d < 4; ++d)
+        if (v[d] > mv) { mv = v[d]; mi = d; }
+      yo[(int64_t)n * hpwp] = mv;
+      io[(int64_t)n * hpwp] = (float)mi;
+    }
+  }
+}
+
 bool make_params(const ConvGeom& g, const float* x, ThinParams* p) {
   const int T = g.Cx * g.kh * g.kw;
   const int64_t pixels = (int64_t)g.Nb * g.Hy * g.Wy;
@@ -358,6 +422,26 @@ rt_status rt_conv_forward_thin_internal(rt_ctx* ctx, const float* x, const float
     case 12: thin_conv_forward_kernel<12><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
     default: thin_conv_forward_kernel<16><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
   }
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
+// y, idx = max_pool2d(relu(conv2d(x, w) + bias), 2x2, stride 2) for a single-channel 3x3 unit-stride convolution with an even
+// output extent; RT_ERR_UNIMPLEMENTED otherwise.
+rt_status rt_conv_relu_pool_thin_internal(rt_ctx* ctx, const float* x, const float* w, const float* bias, const ConvGeom& g, float* y,
+                                          float* idx) {
+  if (g.Cx != 1 || g.kh != 3 || g.kw != 3 || g.sh != 1 || g.sw != 1 || g.Hy < 2 || g.Wy < 2 || (g.Hy & 1) || (g.Wy & 1) || g.Cy < 1)
+    return RT_ERR_UNIMPLEMENTED;
+  ThinPoolParams p;
+  p.x = x; p.Nb = g.Nb; p.H = g.Hx; p.W = g.Wx; p.N = g.Cy; p.Hp = g.Hy / 2; p.Wp = g.Wy / 2; p.ph = g.ph; p.pw = g.pw;
+  p.pooled = (int64_t)g.Nb * p.Hp * p.Wp;
+  if (p.pooled < 1 || p.pooled >= (1ll << 31) || (int64_t)g.Nb * g.Cy * p.Hp * p.Wp >= (1ll << 40)) return RT_ERR_UNIMPLEMENTED;
+  p.d_HpWp.init(p.Hp * p.Wp);
+  p.d_Wp.init(p.Wp);
+  const int groups = (g.Cy + kPoolChannelGroup - 1) / kPoolChannelGroup;
+  if (groups > 65535) return RT_ERR_UNIMPLEMENTED;
+  const dim3 grid(rt_grid_for(ctx, p.pooled, kThreads, 16), groups);
+  thin_conv_relu_pool_kernel<<<grid, kThreads, 0, ctx->stream>>>(p, w, bias, y, idx);
   RT_LAUNCHED(ctx);
   return RT_OK;
 }

@@ -29,6 +29,8 @@ rt_status rt_conv_forward_thin_internal(rt_ctx* ctx, const float* x, const float
                                         float* y);
 rt_status rt_conv_weight_grad_thin_internal(rt_ctx* ctx, const float* x, const float* gy, const ConvGeom& g, float* dw, float* db,
                                             bool* db_done);
+rt_status rt_conv_relu_pool_thin_internal(rt_ctx* ctx, const float* x, const float* w, const float* bias, const ConvGeom& g, float* y,
+                                          float* idx);
 rt_status rt_conv_window_tc_internal(rt_ctx* ctx, const float* src, int Nb, int C, int H, int W, int ph, int pw, const float* w,
                                      int N, int kh, int kw, int sn, int sc, int sky, int skx, int off0, const float* bias,
                                      float* out);
@@ -623,6 +625,32 @@ rt_status rt_conv2d(rt_ctx* ctx, const float* x, const float* w, const float* bi
   if ((int64_t)n * cout * g.Hy * g.Wy == 0) return RT_OK;
   RT_CHECK_PTR(ctx, y);
   return conv_forward_like(ctx, x, w, bias, g, y);
+}
+
+rt_status rt_conv2d_relu_max_pool2x2(rt_ctx* ctx, const float* x, const float* w, const float* bias, int64_t n, int64_t cin, int64_t h,
+                                     int64_t wd, int64_t cout, int kh, int kw, int sh, int sw, int ph, int pw, float* y, float* idx) {
+  RT_CHECK_CTX(ctx);
+  rt_status st = check_conv_args(ctx, n, cin, h, wd, cout, kh, kw, sh, sw, ph, pw);
+  if (st != RT_OK) return st;
+  if (h + 2 * ph < kh || wd + 2 * pw < kw) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "conv2d_relu_max_pool2x2: kernel larger than padded input");
+  ConvGeom g = make_geom(n, cin, h, wd, cout, kh, kw, sh, sw, ph, pw);
+  if ((g.Hy & 1) || (g.Wy & 1))
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "conv2d_relu_max_pool2x2: the convolution output %d x %d must have even extents", g.Hy, g.Wy);
+  if ((int64_t)n * cout * g.Hy * g.Wy == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, y);
+  RT_CHECK_PTR(ctx, idx);
+  if (ctx->use_tensor_cores) {  // the fused first-layer kernel (exact FP32, like the unfused first-layer kernel it mirrors)
+    st = rt_conv_relu_pool_thin_internal(ctx, x, w, bias, g, y, idx);
+    if (st != RT_ERR_UNIMPLEMENTED) return st;
+  }
+  // every other shape: the convolution into scratch memory, then relu + pooling in one kernel; the scratch block goes back to
+  // the pool when this call returns
+  RtScratch conv_out(ctx);
+  st = conv_out.alloc(sizeof(float) * (size_t)n * cout * g.Hy * g.Wy);
+  if (st != RT_OK) return st;
+  st = conv_forward_like(ctx, x, w, bias, g, conv_out.as<float>());
+  if (st != RT_OK) return st;
+  return rt_relu_max_pool2d(ctx, conv_out.as<float>(), n, cout, g.Hy, g.Wy, 2, 2, 2, 2, 0, 0, y, idx);
 }
 
 rt_status rt_conv2d_backward(rt_ctx* ctx, const float* x, const float* w, const float* gr, int64_t n, int64_t cin,

@@ -128,6 +128,46 @@ __global__ void __launch_bounds__(kThreads) pool_bwd_2x2_pair(const float* __res
   }
 }
 
+// Backward of max_pool2d(relu(.)) for 2x2 / stride 2 from the POOLED output: the gradient of window o goes to its saved
+// position when y[o] > 0 (y = relu of the window's maximum, so y > 0 exactly when the input at that position was positive)
+// and nowhere otherwise.  Two windows per thread like pool_bwd_2x2_pair; the un-pooled tensor is not read.
+__global__ void __launch_bounds__(kThreads) pool_bwd_2x2_from_output(const float* __restrict__ y, const float* __restrict__ g,
+                                                                      const float* __restrict__ idx, float* __restrict__ dx,
+                                                                      int64_t total2, int w, int wo2) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < total2; o += stride) {
+    const int xo = (int)(o % wo2);
+    const int64_t row = o / wo2;
+    float2 gv = __ldcs(reinterpret_cast<const float2*>(g) + o);
+    const float2 iv = __ldcs(reinterpret_cast<const float2*>(idx) + o);
+    const float2 yv = __ldg(reinterpret_cast<const float2*>(y) + o);
+    gv.x = yv.x > 0.f ? gv.x : 0.f;
+    gv.y = yv.y > 0.f ? gv.y : 0.f;
+    const int m0 = (int)lrintf(iv.x), m1 = (int)lrintf(iv.y);
+    const float4 a = make_float4(m0 == 0 ? gv.x : 0.f, m0 == 1 ? gv.x : 0.f, m1 == 0 ? gv.y : 0.f, m1 == 1 ? gv.y : 0.f);
+    const float4 b = make_float4(m0 == 2 ? gv.x : 0.f, m0 == 3 ? gv.x : 0.f, m1 == 2 ? gv.y : 0.f, m1 == 3 ? gv.y : 0.f);
+    float4* p = reinterpret_cast<float4*>(dx + (row * 2) * w) + xo;
+    p[0] = a;
+    p[w >> 2] = b;
+  }
+}
+__global__ void __launch_bounds__(kThreads) pool_bwd_2x2_from_output_scalar(const float* __restrict__ y, const float* __restrict__ g,
+                                                                             const float* __restrict__ idx, float* __restrict__ dx,
+                                                                             int64_t total, int w, int wo) {
+  int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += stride) {
+    const int xo = (int)(o % wo);
+    const int64_t row = o / wo;
+    const float gv = __ldg(y + o) > 0.f ? __ldg(g + o) : 0.f;
+    const int mi = (int)lrintf(__ldg(idx + o));
+    float* p = dx + (row * 2) * w + 2 * xo;
+    p[0] = mi == 0 ? gv : 0.f;
+    p[1] = mi == 1 ? gv : 0.f;
+    p[w] = mi == 2 ? gv : 0.f;
+    p[w + 1] = mi == 3 ? gv : 0.f;
+  }
+}
+
 // Disjoint windows: every input element is the target of at most one window, plain read-modify-write into a zero-filled dx.
 __global__ void __launch_bounds__(kThreads) pool_bwd_general(const float* __restrict__ g, const float* __restrict__ idx,
                                                               float* __restrict__ dx, int64_t total, int h, int w, int ho,
@@ -279,6 +319,28 @@ static rt_status pool_backward(rt_ctx* ctx, const float* x, const float* g, cons
     RT_LAUNCHED(ctx);
   }
   return x ? rt_unary_backward(ctx, RT_RELU, x, dx, dx, in_total, 0.f, 0.f) : RT_OK;  // element-wise, safe in place
+}
+
+rt_status rt_relu_max_pool2x2_backward_from_output(rt_ctx* ctx, const float* y, const float* g, const float* idx, int64_t n, int64_t c,
+                                                   int64_t h, int64_t w, float* dx) {
+  RT_CHECK_CTX(ctx);
+  if (n < 0 || c < 0 || h < 0 || w < 0 || (h & 1) || (w & 1))
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "relu_max_pool2x2_backward_from_output: the un-pooled extent %lld x %lld must be even", (long long)h,
+            (long long)w);
+  const int64_t total = n * c * (h / 2) * (w / 2);
+  if (total == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, y);
+  RT_CHECK_PTR(ctx, g);
+  RT_CHECK_PTR(ctx, idx);
+  RT_CHECK_PTR(ctx, dx);
+  const bool pair = w % 4 == 0 && rt_aligned16(dx) && (reinterpret_cast<uintptr_t>(g) % 8 == 0) && (reinterpret_cast<uintptr_t>(idx) % 8 == 0) &&
+                    (reinterpret_cast<uintptr_t>(y) % 8 == 0);
+  if (pair)
+    pool_bwd_2x2_from_output<<<rt_grid_for(ctx, total / 2, kThreads, 64), kThreads, 0, ctx->stream>>>(y, g, idx, dx, total / 2, (int)w, (int)(w / 4));
+  else
+    pool_bwd_2x2_from_output_scalar<<<rt_grid_for(ctx, total, kThreads, 16), kThreads, 0, ctx->stream>>>(y, g, idx, dx, total, (int)w, (int)(w / 2));
+  RT_LAUNCHED(ctx);
+  return RT_OK;
 }
 
 rt_status rt_max_pool2d_backward(rt_ctx* ctx, const float* g, const float* idx, int64_t n, int64_t c, int64_t h, int64_t w,

@@ -255,6 +255,54 @@ def test_fused_relu_max_pool_is_bit_identical_to_the_two_ops(capi):
         assert np.array_equal(d1.numpy(), d0.numpy())
 
 
+@pytest.mark.parametrize("shape", [(4, 1, 28, 28, 32, 1), (3, 1, 12, 8, 20, 1), (2, 1, 10, 10, 5, 0), (2, 3, 8, 12, 6, 1), (2, 32, 14, 14, 64, 1)],
+                         ids=str)
+def test_fused_conv_relu_pool_is_bit_identical_to_the_three_ops(capi, shape):
+    """rt_conv2d_relu_max_pool2x2 against rt_conv2d -> relu -> rt_max_pool2d(2x2, stride 2): pooled values, indices and the
+    gradient of the convolution output (from the pooled output, without the un-pooled tensor) must be equal bit for bit - for the
+    single-channel 3x3 layers that run as one kernel (16 and 4 channels in the last group, no padding) and for the shapes that
+    run as convolution + fused pooling."""
+    n, cin, h, w, cout, pad = shape
+    r = rng(77)
+    i64, i32 = C.c_int64, C.c_int
+    x = r.standard_normal((n, cin, h, w)).astype(np.float32)
+    wt = (r.standard_normal((cout, cin, 3, 3)) / 3.0).astype(np.float32)
+    b = r.standard_normal(cout).astype(np.float32)
+    b[::3] = -5.0                                           # whole windows below zero: relu ties, first position wins
+    ho, wo = h + 2 * pad - 2, w + 2 * pad - 2
+    assert ho % 2 == 0 and wo % 2 == 0
+    dx_, dw_, db_ = capi.to_device(x), capi.to_device(wt), capi.to_device(b)
+    conv_args = (i64(n), i64(cin), i64(h), i64(w), i64(cout), i32(3), i32(3), i32(1), i32(1), i32(pad), i32(pad))
+    pool_args = (i64(n), i64(cout), i64(ho), i64(wo), i32(2), i32(2), i32(2), i32(2), i32(0), i32(0))
+    conv, rl = capi.empty((n, cout, ho, wo)), capi.empty((n, cout, ho, wo))
+    y0, i0 = capi.empty((n, cout, ho // 2, wo // 2)), capi.empty((n, cout, ho // 2, wo // 2))
+    capi.call("conv2d", dx_.ptr, dw_.ptr, db_.ptr, *conv_args, conv.ptr)
+    capi.call("unary", i32(UNARY["relu"]), conv.ptr, rl.ptr, i64(conv.size), C.c_float(0), C.c_float(0))
+    capi.call("max_pool2d", rl.ptr, *pool_args, y0.ptr, i0.ptr)
+    g = capi.to_device(r.standard_normal(y0.shape).astype(np.float32))
+    dp, d0 = capi.empty(conv.shape), capi.empty(conv.shape)
+    capi.call("max_pool2d_backward", g.ptr, i0.ptr, *pool_args, dp.ptr)
+    capi.call("unary_backward", i32(UNARY["relu"]), conv.ptr, dp.ptr, d0.ptr, i64(conv.size), C.c_float(0), C.c_float(0))
+    y1, i1, d1 = capi.empty(y0.shape), capi.empty(y0.shape), capi.empty(conv.shape)
+    capi.call("conv2d_relu_max_pool2x2", dx_.ptr, dw_.ptr, db_.ptr, *conv_args, y1.ptr, i1.ptr)
+    capi.call("relu_max_pool2x2_backward_from_output", y1.ptr, g.ptr, i1.ptr, i64(n), i64(cout), i64(ho), i64(wo), d1.ptr)
+    assert np.array_equal(y1.numpy(), y0.numpy())
+    assert np.array_equal(i1.numpy(), i0.numpy())
+    assert np.array_equal(d1.numpy(), d0.numpy())
+    assert (y0.numpy() == 0).any() and (y0.numpy() > 0).any()
+
+
+def test_fused_conv_relu_pool_rejects_odd_outputs(capi):
+    from rusttensor_b200.capi import RtError
+
+    x, wt = capi.to_device(np.zeros((1, 1, 7, 7), np.float32)), capi.to_device(np.zeros((2, 1, 3, 3), np.float32))
+    y, idx = capi.empty((1, 2, 3, 3)), capi.empty((1, 2, 3, 3))
+    with pytest.raises(RtError) as ei:
+        capi.call("conv2d_relu_max_pool2x2", x.ptr, wt.ptr, None, C.c_int64(1), C.c_int64(1), C.c_int64(7), C.c_int64(7), C.c_int64(2), C.c_int(3),
+                  C.c_int(3), C.c_int(1), C.c_int(1), C.c_int(1), C.c_int(1), y.ptr, idx.ptr)
+    assert ei.value.code == 4
+
+
 def test_max_pool_backward_with_overlapping_windows_is_reproducible(capi):
     """stride < kernel: several windows can route their gradient to one input element.  The sum is formed in the order
     of the reference's sequential scatter (ascending output index), so it equals a float32 replay of that loop bit for
