@@ -195,6 +195,9 @@ rt_status rt_slice(rt_ctx* ctx, const float* x, const int64_t* x_shape, int ndim
  * (src/data.rs:125-209), done on the device instead of through a host copy of the whole data set. */
 rt_status rt_gather_rows(rt_ctx* ctx, const float* src, int64_t rows, int64_t row_len, const int32_t* idx, int64_t n_idx, float* out);
 
+/* out[c] += sum over r of x[r, c] for a row-major x[rows, cols]: the gradient of a bias that already holds a gradient (a bias
+ * used at every timestep of a recurrent layer), accumulated in place in one launch.  One thread per column: meant for few rows. */
+rt_status rt_sum_rows_accumulate(rt_ctx* ctx, const float* x, int64_t rows, int64_t cols, float* out);
 /* ---- reductions over one axis of a tensor viewed as [outer, len, inner] ----------------------- */
 enum {
   RT_RED_SUM = 0,       /* sum_along_axis mod.rs:291, sum_all mod.rs:293 */
@@ -281,6 +284,10 @@ rt_status rt_gemm(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, int64_t n, i
 /* da[M,K] = g * b^T, db[K,N] = a^T * g   (matmul_backward mod.rs:324); NULL skips one. */
 rt_status rt_matmul_backward(rt_ctx* ctx, const float* a, const float* b, const float* g, int64_t m, int64_t k,
                              int64_t n, float* da, float* db);
+/* The same with db_sum[K,N] += a^T * g: for a weight that already holds a gradient (used at every timestep of a recurrent
+ * layer), the product accumulates into it instead of a product followed by an addition (what add_grad does, src/tensor.rs:1099). */
+rt_status rt_matmul_backward_accumulate(rt_ctx* ctx, const float* a, const float* b, const float* g, int64_t m, int64_t k,
+                                        int64_t n, float* da, float* db_sum);
 /* conv2d mod.rs:101: x[N,Cin,H,W], w[Cout,Cin,kh,kw], bias[Cout] or NULL -> y[N,Cout,Ho,Wo] */
 rt_status rt_conv2d(rt_ctx* ctx, const float* x, const float* w, const float* bias, int64_t n, int64_t cin,
                     int64_t h, int64_t wd, int64_t cout, int kh, int kw, int sh, int sw, int ph, int pw, float* y);

@@ -155,6 +155,13 @@ struct TensorData {
   std::shared_ptr<Op<B>> op;
 };
 
+// A backend may add a product's weight gradient to the gradient the weight already holds (a weight used at every timestep
+// of a recurrent layer) inside the product itself, instead of returning it for a separate addition.
+template <class B, class = void>
+struct HasAccumulatingMatmul : std::false_type {};
+template <class B>
+struct HasAccumulatingMatmul<B, std::void_t<decltype(&B::matmul_backward_accumulate)>> : std::true_type {};
+
 template <class B>
 class Tensor {
  public:
@@ -182,6 +189,7 @@ class Tensor {
   bool requires_grad() const { return inner->requires_grad; }
   size_t id() const { return inner->id; }
   const std::optional<Storage>& grad() const { return inner->grad; }
+  Storage& grad_mut() const { return *inner->grad; }  // only valid while grad() holds a value
   std::vector<float> to_vec() const { return B::copy_to_host(inner->data); }
   std::vector<float> grad_vec() const {
     if (!inner->grad) throw Error(ErrorKind::NoGradientError, "tensor has no gradient");
@@ -278,8 +286,13 @@ class Tensor {
         throw Error::invalid_op(std::string("Backward function for op ") + op->op_type.name() +
                                 " returned " + std::to_string(grads.size()) + " gradients, expected " +
                                 std::to_string(op->inputs.size()));
-      for (size_t i = 0; i < grads.size(); ++i)
-        if (op->inputs[i].requires_grad()) op->inputs[i].add_grad(std::move(grads[i]));
+      for (size_t i = 0; i < grads.size(); ++i) {
+        if (!op->inputs[i].requires_grad()) continue;
+        if constexpr (HasAccumulatingMatmul<B>::value) {
+          if (B::is_accumulated(grads[i])) continue;  // the closure has added its gradient to the existing one itself
+        }
+        op->inputs[i].add_grad(std::move(grads[i]));
+      }
     }
   }
 
@@ -386,6 +399,13 @@ Tensor<B> matmul(const Tensor<B>& a, const Tensor<B>& b) {
   Tensor<B> t(std::move(out), rg);
   if (rg) {
     t.set_op(Op<B>(OpType(OpType::Matmul), {a, b}, [](const Op<B>& op, const St<B>& g) {
+      if constexpr (HasAccumulatingMatmul<B>::value) {
+        const Tensor<B>& wb = op.inputs[1];
+        if (wb.requires_grad() && wb.grad() && B::accumulates_well(wb.data())) {
+          St<B> da = B::matmul_backward_accumulate(op, g, wb.grad_mut());
+          return Grads<B>{std::move(da), B::unused_grad(B::shape(wb.data()))};
+        }
+      }
       auto p = B::matmul_closure_backward(op, g);
       return Grads<B>{std::move(p.first), std::move(p.second)};
     }));
@@ -866,6 +886,28 @@ Tensor<B> fused_conv2d_relu_max_pool2d(const Tensor<B>& input, const Tensor<B>& 
         return Grads<B>{std::move(std::get<0>(gr)), std::move(std::get<1>(gr)), std::move(gb), B::unused_grad(B::shape(op.inputs[3].data())),
                         B::unused_grad(B::shape(op.inputs[4].data()))};
       }));
+    }
+    return t;
+  }
+}
+
+// concat({slice(x, rows r0..r1, all columns), h}, axis 1) for a 2-D x that needs no gradient: what a recurrent model does at every
+// timestep with its time-major input (examples/lstm_char_rnn_cpu.rs).  The row slice is never materialised.
+template <class B>
+Tensor<B> fused_rows_concat(const Tensor<B>& x, size_t r0, size_t r1, const Tensor<B>& h) {
+  if constexpr (!HasFusedForward<B>::value) {
+    return concat<B>({slice(x, {{r0, r1}, {0, x.shape().at(1)}}), h}, 1);
+  } else {
+    if (x.requires_grad()) return concat<B>({slice(x, {{r0, r1}, {0, x.shape().at(1)}}), h}, 1);
+    St<B> out = B::concat_rows_with(x.data(), r0, r1, h.data());
+    bool rg = h.requires_grad();
+    Tensor<B> t(std::move(out), rg);
+    if (rg) {
+      OpType ot(OpType::Concat);  // the backward of a concatenation whose first input takes no gradient
+      ot.axis = 1;
+      Tensor<B> left(B::unused_grad(Shape{r1 - r0, x.shape()[1]}), false);
+      ot.input_shapes = {left.shape(), h.shape()};
+      t.set_op(Op<B>(ot, {left, h}, [](const Op<B>& op, const St<B>& g) { return B::concat_backward(op, g); }));
     }
     return t;
   }

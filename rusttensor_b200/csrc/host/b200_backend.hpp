@@ -254,7 +254,16 @@ struct B200Backend {
     // full-shape a + broadcast b (a bias): da is the upstream gradient itself, db its sum over the stretched axes
     if (o.inputs.size() == 2 && o.inputs[0].data().shape == g.shape && g.numel() > 0 && stretches_onto(o.inputs[1].data().shape, g.shape)) {
       const Shape& bs = o.inputs[1].data().shape;
-      return {g, o.inputs[1].requires_grad() ? unbroadcast(g, bs) : unused_grad(bs)};
+      const auto& bias = o.inputs[1];
+      if (bias.requires_grad() && bias.grad() && g.shape.size() == 2 && bs.size() == 1 && bs[0] == g.shape[1] && g.shape[0] <= 1024 &&
+          bias.grad()->shape == bs) {
+        // the bias already holds a gradient (it is used at every timestep): add this one's column sums to it in place
+        Storage& acc = bias.grad_mut();
+        make_unique(acc);
+        check(rt_sum_rows_accumulate(ctx(), g.ptr(), (int64_t)g.shape[0], (int64_t)g.shape[1], acc.ptr()));
+        return {g, unused_grad(bs)};
+      }
+      return {g, bias.requires_grad() ? unbroadcast(g, bs) : unused_grad(bs)};
     }
     return binary_bwd(RT_ADD, o, g, "add");
   }
@@ -392,6 +401,22 @@ struct B200Backend {
       check(rt_slice_assign(ctx(), y.ptr(), od.data(), (int)od.size(), starts.data(), x->ptr(), xd.data()));
       starts[axis] += (int64_t)x->shape[axis];
     }
+    return y;
+  }
+  // concat({x[r0:r1, :], h}, axis 1) for 2-D x and h without materialising the row slice: rows r0..r1 of a row-major matrix are
+  // one contiguous block, which goes straight into the left columns of the result.
+  static Storage concat_rows_with(const Storage& x, size_t r0, size_t r1, const Storage& h) {
+    if (x.shape.size() != 2 || h.shape.size() != 2 || r0 > r1 || r1 > x.shape[0] || h.shape[0] != r1 - r0)
+      throw Error(ErrorKind::ShapeError, "concat_rows_with: incompatible shapes");
+    Shape os{r1 - r0, x.shape[1] + h.shape[1]};
+    Storage y = alloc(os);
+    auto od = dims(os);
+    std::vector<int64_t> starts{0, 0};
+    Shape xs{r1 - r0, x.shape[1]};
+    auto xd = dims(xs), hd = dims(h.shape);
+    if (shape_numel(xs) > 0) check(rt_slice_assign(ctx(), y.ptr(), od.data(), 2, starts.data(), x.ptr() + r0 * x.shape[1], xd.data()));
+    starts[1] = (int64_t)x.shape[1];
+    if (h.numel() > 0) check(rt_slice_assign(ctx(), y.ptr(), od.data(), 2, starts.data(), h.ptr(), hd.data()));
     return y;
   }
   static std::vector<Storage> concat_backward(const OpB& o, const Storage& g) {
@@ -562,6 +587,22 @@ struct B200Backend {
     return {std::move(da), std::move(db)};
   }
   static std::pair<Storage, Storage> matmul_closure_backward(const OpB& o, const Storage& g) { return matmul_backward(o, g); }
+  // matmul backward when the second operand already holds a gradient: returns dA and adds A^T g to `acc` in place (the
+  // product kernel accumulates into its output; one launch instead of a product and an addition)
+  static Storage matmul_backward_accumulate(const OpB& o, const Storage& g, Storage& acc) {
+    const Storage& a = o.inputs[0].data();
+    const Storage& b = o.inputs[1].data();
+    int64_t m = (int64_t)a.shape[0], k = (int64_t)a.shape[1], n = (int64_t)b.shape[1];
+    if (g.shape != Shape{a.shape[0], b.shape[1]}) throw Error::incompatible("matmul", g.shape, b.shape);
+    if (acc.shape != b.shape) throw Error::shape_mismatch(b.shape, acc.shape);
+    Storage da = o.inputs[0].requires_grad() ? alloc(a.shape) : Storage{nullptr, a.shape};
+    make_unique(acc);  // nobody else may see the sum appear in a buffer they share
+    check(rt_matmul_backward_accumulate(ctx(), a.ptr(), b.ptr(), g.ptr(), m, k, n, da.ptr(), acc.ptr()));
+    return da;
+  }
+  static bool is_accumulated(const Storage& s) { return !s.buf; }
+  // the accumulating epilogue of the product works on 128-bit pieces of a row; other widths keep product + addition
+  static bool accumulates_well(const Storage& b) { return b.shape.size() == 2 && b.shape[1] % 4 == 0; }
 
   static void conv_shapes(const Storage& x, const Storage& w, const char* name) {
     if (x.shape.size() != 4 || w.shape.size() != 4) throw Error::invalid_op(std::string(name) + " expects 4D input and weights");

@@ -192,25 +192,35 @@ Tensor<B> forward_loss(const Workload<B>& w, const std::vector<Tensor<B>>& in) {
       size_t V = d[0], H = d[1], T = d[2], Bn = d[3];
       Tensor<B> h = Tensor<B>::zeros({Bn, H}, false), c = Tensor<B>::zeros({Bn, H}, false);
       Tensor<B> total;
+      std::vector<Tensor<B>> hs;  // fused variant: the hidden states of all timesteps, for ONE output projection
       for (size_t t = 0; t < T; ++t) {
-        Tensor<B> x_t = ops::slice(in.at(0), {{t * Bn, (t + 1) * Bn}, {0, V}});
-        Tensor<B> y_t = ops::slice(in.at(1), {{t * Bn, (t + 1) * Bn}, {0, V}});
-        Tensor<B> xh = ops::concat<B>({x_t, h}, 1);
+        Tensor<B> xh = w.fused_forward ? ops::fused_rows_concat(in.at(0), t * Bn, (t + 1) * Bn, h)
+                                       : ops::concat<B>({ops::slice(in.at(0), {{t * Bn, (t + 1) * Bn}, {0, V}}), h}, 1);
         Tensor<B> gates = linear(xh, p[0], p[1], w.fused_forward);
         if (w.fused_forward) {
           c = ops::fused_lstm_cell_c(gates, c);
           h = ops::fused_lstm_cell_h(gates, c);
-        } else {
-          Tensor<B> ig = ops::sigmoid(ops::slice(gates, {{0, Bn}, {0, H}}));
-          Tensor<B> fg = ops::sigmoid(ops::slice(gates, {{0, Bn}, {H, 2 * H}}));
-          Tensor<B> gg = ops::tanh(ops::slice(gates, {{0, Bn}, {2 * H, 3 * H}}));
-          Tensor<B> og = ops::sigmoid(ops::slice(gates, {{0, Bn}, {3 * H, 4 * H}}));
-          c = ops::add(ops::mul(fg, c), ops::mul(ig, gg));
-          h = ops::mul(og, ops::tanh(c));
+          hs.push_back(h);
+          continue;
         }
-        Tensor<B> logits = linear(h, p[2], p[3], w.fused_forward);
-        Tensor<B> l = w.fused_forward ? ops::fused_softmax_nll(logits, y_t) : ops::softmax_cross_entropy(logits, y_t, 1, Reduction::Mean);
+        Tensor<B> y_t = ops::slice(in.at(1), {{t * Bn, (t + 1) * Bn}, {0, V}});
+        Tensor<B> ig = ops::sigmoid(ops::slice(gates, {{0, Bn}, {0, H}}));
+        Tensor<B> fg = ops::sigmoid(ops::slice(gates, {{0, Bn}, {H, 2 * H}}));
+        Tensor<B> gg = ops::tanh(ops::slice(gates, {{0, Bn}, {2 * H, 3 * H}}));
+        Tensor<B> og = ops::sigmoid(ops::slice(gates, {{0, Bn}, {3 * H, 4 * H}}));
+        c = ops::add(ops::mul(fg, c), ops::mul(ig, gg));
+        h = ops::mul(og, ops::tanh(c));
+        Tensor<B> logits = linear(h, p[2], p[3], false);
+        Tensor<B> l = ops::softmax_cross_entropy(logits, y_t, 1, Reduction::Mean);
         total = t == 0 ? l : ops::add(total, l);
+      }
+      if (w.fused_forward) {
+        // The example projects and scores every timestep on its own (examples/lstm_char_rnn_cpu.rs:405-435) and adds the T mean
+        // losses.  The targets are already time-major [T*B, V], so one [T*B, H] x [H, V] product and one loss over all rows
+        // give the same sum: sum_t mean_b l(t, b) = T * mean over all T*B rows.
+        Tensor<B> all_h = ops::concat<B>(hs, 0);
+        Tensor<B> logits = linear(all_h, p[2], p[3], true);
+        total = ops::mul_scalar(ops::fused_softmax_nll(logits, in.at(1)), (float)T);
       }
       return total;
     }

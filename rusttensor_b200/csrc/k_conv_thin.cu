@@ -162,13 +162,15 @@ struct ImageDwParams {
   float* db;       // [N] or null
   unsigned* tickets;  // [1 + groups], zero between launches
   int Nb, H, W, N, Ho, Wo, ph, pw, Hp, Wp;
-  FastDiv d_Wo, d_Wp;
+  FastDiv d_Wo, d_Wp, d_Wq;  // d_Wq: Wo / 4 (pixel quads per output row)
 };
 constexpr int kGroupBlocks = 8;
 
 constexpr int kImgThreads = 512;
 
-template <int KH, int KW>
+// QUAD (Wo a multiple of 4, KW odd): a lane takes four horizontally adjacent pixels at a time - one 128-bit load of g per channel
+// and the KH x (KW + 3) patch of the image as 64-bit shared-memory loads - which halves the instructions per multiply-add.
+template <int KH, int KW, bool QUAD>
 __global__ void __launch_bounds__(kImgThreads) thin_dw_image_kernel(const ImageDwParams p) {
   constexpr int T = KH * KW;
   extern __shared__ __align__(16) float tile[];  // Hp x Wp: the image with its halo
@@ -203,6 +205,47 @@ __global__ void __launch_bounds__(kImgThreads) thin_dw_image_kernel(const ImageD
         pre[u] = (nb < p.Nb && i < tile_n) ? fetch(nb, i) : 0.f;
       }
       const float* gb = p.g + ((int64_t)b * p.N + n0) * howo;
+      if constexpr (QUAD) {
+        // the gradients of the next pixel quads are in flight while the current ones are accumulated
+        const int nquads = howo >> 2;
+        float4 gv[4], gn[4];
+        auto load_q = [&](int qd, float4 (&dst)[4]) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[i] = (qd < nquads && n0 + i < p.N) ? __ldg(reinterpret_cast<const float4*>(gb + (int64_t)i * howo) + qd)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        };
+        load_q(phase * 32 + lane, gv);
+        for (int base = phase * 32; base < nquads; base += 64) {
+          const int qd = base + lane;
+          load_q(qd + 64, gn);
+          uint32_t yo, xq;
+          p.d_Wq.divmod(qd < nquads ? (uint32_t)qd : 0u, yo, xq);
+          const float2* tp = reinterpret_cast<const float2*>(tile + (int)yo * p.Wp + 4 * (int)xq);  // Wp and 4*xq are even
+          float pt[KH][KW + 3];
+#pragma unroll
+          for (int ky = 0; ky < KH; ++ky)
+#pragma unroll
+            for (int j = 0; j < (KW + 3) / 2; ++j) {
+              const float2 t2 = tp[(ky * p.Wp >> 1) + j];
+              pt[ky][2 * j] = t2.x;
+              pt[ky][2 * j + 1] = t2.y;
+            }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float gq[4] = {gv[i].x, gv[i].y, gv[i].z, gv[i].w};
+#pragma unroll
+            for (int d = 0; d < 4; ++d)
+#pragma unroll
+              for (int ky = 0; ky < KH; ++ky)
+#pragma unroll
+                for (int kx = 0; kx < KW; ++kx) acc[i][ky * KW + kx] = fmaf(gq[d], pt[ky][d + kx], acc[i][ky * KW + kx]);
+            acc[i][T] += (gq[0] + gq[1]) + (gq[2] + gq[3]);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) gv[i] = gn[i];
+        }
+      } else {
       // the gradients of the next block of pixels are in flight while the current one is accumulated
       float gv[4][4], gn[4][4];
       auto load_g = [&](int q0, float (&dst)[4][4]) {
@@ -237,6 +280,7 @@ __global__ void __launch_bounds__(kImgThreads) thin_dw_image_kernel(const ImageD
         for (int u = 0; u < 4; ++u)
 #pragma unroll
           for (int i = 0; i < 4; ++i) gv[u][i] = gn[u][i];
+      }
       }
       __syncthreads();  // every warp is done with this image
       if (nb < p.Nb) {
@@ -469,7 +513,9 @@ static rt_status weight_grad_image(rt_ctx* ctx, const float* x, const float* gy,
   p.Nb = g.Nb; p.H = g.Hx; p.W = g.Wx; p.N = g.Cy; p.Ho = g.Hy; p.Wo = g.Wy; p.ph = g.ph; p.pw = g.pw;
   p.d_Wo.init(g.Wy);
   p.d_Wp.init(p.Wp);
-  thin_dw_image_kernel<3, 3><<<grid, kImgThreads, smem, ctx->stream>>>(p);
+  p.d_Wq.init(g.Wy / 4 > 0 ? g.Wy / 4 : 1);
+  if (g.Wy % 4 == 0 && rt_aligned16(gy)) thin_dw_image_kernel<3, 3, true><<<grid, kImgThreads, smem, ctx->stream>>>(p);
+  else thin_dw_image_kernel<3, 3, false><<<grid, kImgThreads, smem, ctx->stream>>>(p);
   RT_LAUNCHED(ctx);
   return RT_OK;
 }

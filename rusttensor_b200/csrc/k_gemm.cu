@@ -600,19 +600,29 @@ rt_status rt_gemm(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, int64_t n, i
   return gemm_plain(ctx, MatA<true>{a, lda}, MatB<true>{b, ldb}, c, ldc, m, n, k, acc, true);
 }
 
-rt_status rt_matmul_backward(rt_ctx* ctx, const float* a, const float* b, const float* g, int64_t m, int64_t k, int64_t n,
-                             float* da, float* db) {
+static rt_status matmul_backward_impl(rt_ctx* ctx, const float* a, const float* b, const float* g, int64_t m, int64_t k, int64_t n,
+                                      float* da, float* db, int accumulate_db) {
   RT_CHECK_CTX(ctx);
-  // da[M,K] = g[M,N] * b[K,N]^T ; db[K,N] = a[M,K]^T * g[M,N]: independent, so db goes to the side stream
+  // da[M,K] = g[M,N] * b[K,N]^T ; db[K,N] (+)= a[M,K]^T * g[M,N]: independent, so db goes to the side stream
   RtFork fork(ctx, da && db);
   rt_status st = RT_OK, st2 = RT_OK;
-  if (db) st2 = rt_gemm(ctx, 1, 0, k, n, m, a, k, g, n, db, n, 0);
+  if (db) st2 = rt_gemm(ctx, 1, 0, k, n, m, a, k, g, n, db, n, accumulate_db);
   rt_status e1 = fork.end();
   if (da) st = rt_gemm(ctx, 0, 1, m, k, n, g, n, b, n, da, k, 0);
   rt_status e2 = fork.join();
   if (st != RT_OK) return st;
   if (st2 != RT_OK) return st2;
   return e1 != RT_OK ? e1 : e2;
+}
+
+rt_status rt_matmul_backward(rt_ctx* ctx, const float* a, const float* b, const float* g, int64_t m, int64_t k, int64_t n,
+                             float* da, float* db) {
+  return matmul_backward_impl(ctx, a, b, g, m, k, n, da, db, 0);
+}
+
+rt_status rt_matmul_backward_accumulate(rt_ctx* ctx, const float* a, const float* b, const float* g, int64_t m, int64_t k, int64_t n,
+                                        float* da, float* db_sum) {
+  return matmul_backward_impl(ctx, a, b, g, m, k, n, da, db_sum, 1);
 }
 
 rt_status rt_conv2d(rt_ctx* ctx, const float* x, const float* w, const float* bias, int64_t n, int64_t cin, int64_t h,

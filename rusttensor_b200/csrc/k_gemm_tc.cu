@@ -407,6 +407,14 @@ struct PlainOut {  // c[z * split_stride + m * ld + n]
     if (vec4 && !accumulate) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(q + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else if (vec4) {  // accumulate: all eight 128-bit loads of the old values are issued before the first add
+      float4 old[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) old[j] = *reinterpret_cast<const float4*>(q + 4 * j);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(q + 4 * j) =
+            make_float4(old[j].x + v[4 * j], old[j].y + v[4 * j + 1], old[j].z + v[4 * j + 2], old[j].w + v[4 * j + 3]);
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)

@@ -738,12 +738,39 @@ __global__ void __launch_bounds__(kThreads) reduce_bwd_final_kernel(const float*
 
 }  // namespace
 
+// out[c] += sum over the rows of x[rows, cols]: a thread per column (rows are few: the bias gradient of one timestep of a
+// recurrent layer, added to the gradient the bias already holds).
+__global__ void __launch_bounds__(kThreads) col_sum_accumulate_kernel(const float* __restrict__ x, int64_t rows, int64_t cols,
+                                                                       float* __restrict__ out) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  int64_t r = 0;
+  for (; r + 3 < rows; r += 4) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] += __ldg(x + (r + u) * cols + c);
+  }
+  for (; r < rows; ++r) acc[0] += __ldg(x + r * cols + c);
+  out[c] += (acc[0] + acc[1]) + (acc[2] + acc[3]);
+}
+
 rt_status rt_sum_axis_internal(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out,
                                float scale) {
   return reduce_float<RT_RED_SUM>(ctx, x, outer, len, inner, out, scale);
 }
 
 extern "C" {
+
+rt_status rt_sum_rows_accumulate(rt_ctx* ctx, const float* x, int64_t rows, int64_t cols, float* out) {
+  RT_CHECK_CTX(ctx);
+  if (rows < 0 || cols < 0) RT_FAIL(ctx, RT_ERR_INVALID_INDEX, "rt_sum_rows_accumulate: negative extent");
+  if (rows * cols == 0) return RT_OK;
+  RT_CHECK_PTR(ctx, x);
+  RT_CHECK_PTR(ctx, out);
+  col_sum_accumulate_kernel<<<(unsigned)((cols + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(x, rows, cols, out);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
 
 rt_status rt_reduce(rt_ctx* ctx, int kind, const float* x, int64_t outer, int64_t len, int64_t inner, float* out) {
   RT_CHECK_CTX(ctx);

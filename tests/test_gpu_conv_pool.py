@@ -20,6 +20,7 @@ CONV = [
     # single-channel 3x3 inputs (the whole-image weight/bias gradient kernel): more images than SMs, more than 32 output
     # channels (two channel groups), a channel count that is no multiple of four, no padding, one image
     (301, 1, 12, 10, 5, 3, (1, 1), (1, 1)), (5, 1, 9, 11, 70, 3, (1, 1), (0, 0)), (1, 1, 28, 28, 33, 3, (1, 1), (1, 1)),
+    (6, 1, 10, 16, 7, 3, (1, 1), (1, 1)), (3, 1, 10, 14, 9, 3, (1, 1), (0, 0)),  # output rows of 16 and 12 pixels: four pixels per lane
 ]
 
 
