@@ -209,6 +209,9 @@ rt_status rt_memcpy_h2d(rt_ctx* ctx, void* dst, const void* src, size_t bytes) {
   if (bytes == 0) return RT_OK;
   RT_CHECK_PTR(ctx, dst);
   RT_CHECK_PTR(ctx, src);
+  if (ctx->capturing)  // the synchronisation below would end the capture with an error of its own
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION,
+            "rt_memcpy_h2d synchronises the stream and cannot be recorded in a graph: stage host data before rt_graph_begin");
   RT_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
   // The source may be pageable and freed by the caller right after the call.
   RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -220,6 +223,10 @@ rt_status rt_memcpy_d2h(rt_ctx* ctx, void* dst, const void* src, size_t bytes) {
   if (bytes == 0) return RT_OK;
   RT_CHECK_PTR(ctx, dst);
   RT_CHECK_PTR(ctx, src);
+  if (ctx->capturing)
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION,
+            "rt_memcpy_d2h synchronises the stream and cannot be recorded in a graph (an op that reads a device value on the host, "
+            "such as sqrt's negative-input check, is not capturable)");
   RT_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
   RT_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
   return rt_take_status(ctx, nullptr);
@@ -299,6 +306,7 @@ rt_status rt_upload_create(rt_ctx* ctx, size_t bytes, rt_upload** out) {
   RT_CHECK_CTX(ctx);
   RT_CHECK_PTR(ctx, out);
   *out = nullptr;
+  RT_CUDA(ctx, cudaSetDevice(ctx->device));  // the calling thread's current device may be another one
   rt_upload* up = new rt_upload();
   up->bytes = bytes ? bytes : 1;
   cudaError_t e = cudaStreamCreateWithFlags(&up->copy_stream, cudaStreamNonBlocking);
@@ -350,6 +358,7 @@ rt_status rt_side_stream_begin(rt_ctx* ctx) {
   if (ctx->on_side) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_side_stream_begin: a side section is already open");
   if (ctx->side_pending) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_side_stream_begin: join the previous side section first");
   if (!ctx->side_stream) {
+    RT_CUDA(ctx, cudaSetDevice(ctx->device));
     RT_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
     RT_CUDA(ctx, cudaEventCreateWithFlags(&ctx->fork_ev, cudaEventDisableTiming));
     RT_CUDA(ctx, cudaEventCreateWithFlags(&ctx->join_ev, cudaEventDisableTiming));
@@ -413,6 +422,7 @@ struct rt_event {
 rt_status rt_event_create(rt_ctx* ctx, rt_event** out) {
   RT_CHECK_CTX(ctx);
   RT_CHECK_PTR(ctx, out);
+  RT_CUDA(ctx, cudaSetDevice(ctx->device));
   rt_event* e = new rt_event();
   cudaError_t err = cudaEventCreateWithFlags(&e->ev, cudaEventDisableTiming);
   if (err != cudaSuccess) {
