@@ -196,7 +196,7 @@ rt_status rt_slice(rt_ctx* ctx, const float* x, const int64_t* x_shape, int ndim
 rt_status rt_gather_rows(rt_ctx* ctx, const float* src, int64_t rows, int64_t row_len, const int32_t* idx, int64_t n_idx, float* out);
 
 /* out[c] += sum over r of x[r, c] for a row-major x[rows, cols]: the gradient of a bias that already holds a gradient (a bias
- * used at every timestep of a recurrent layer), accumulated in place in one launch.  One thread per column: meant for few rows. */
+ * used at every timestep of a recurrent layer), accumulated in place in one launch.  Eight row lanes per column: meant for few rows. */
 rt_status rt_sum_rows_accumulate(rt_ctx* ctx, const float* x, int64_t rows, int64_t cols, float* out);
 /* ---- reductions over one axis of a tensor viewed as [outer, len, inner] ----------------------- */
 enum {

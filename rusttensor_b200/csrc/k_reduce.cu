@@ -738,20 +738,33 @@ __global__ void __launch_bounds__(kThreads) reduce_bwd_final_kernel(const float*
 
 }  // namespace
 
-// out[c] += sum over the rows of x[rows, cols]: a thread per column (rows are few: the bias gradient of one timestep of a
-// recurrent layer, added to the gradient the bias already holds).
+// out[c] += sum over the rows of x[rows, cols] (rows are few: the bias gradient of one timestep of a recurrent layer, added
+// to the gradient the bias already holds).  Block = 32 columns x 8 row lanes: every lane's loads are independent, the eight
+// partial sums of a column are added in lane order through shared memory.
 __global__ void __launch_bounds__(kThreads) col_sum_accumulate_kernel(const float* __restrict__ x, int64_t rows, int64_t cols,
                                                                        float* __restrict__ out) {
-  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  int64_t r = 0;
-  for (; r + 3 < rows; r += 4) {
+  __shared__ float part[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t c = (int64_t)blockIdx.x * 32 + tx;
+  float acc = 0.f;
+  if (c < cols) {
+    int64_t r = ty;
+    for (; r + 24 < rows; r += 32) {
+      float v[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) acc[u] += __ldg(x + (r + u) * cols + c);
+      for (int u = 0; u < 4; ++u) v[u] = __ldg(x + (r + 8 * u) * cols + c);
+      acc += (v[0] + v[1]) + (v[2] + v[3]);
+    }
+    for (; r < rows; r += 8) acc += __ldg(x + r * cols + c);
   }
-  for (; r < rows; ++r) acc[0] += __ldg(x + r * cols + c);
-  out[c] += (acc[0] + acc[1]) + (acc[2] + acc[3]);
+  part[ty][tx] = acc;
+  __syncthreads();
+  if (ty == 0 && c < cols) {
+    float s = part[0][tx];
+#pragma unroll
+    for (int y = 1; y < 8; ++y) s += part[y][tx];
+    out[c] += s;
+  }
 }
 
 rt_status rt_sum_axis_internal(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out,
@@ -767,7 +780,7 @@ rt_status rt_sum_rows_accumulate(rt_ctx* ctx, const float* x, int64_t rows, int6
   if (rows * cols == 0) return RT_OK;
   RT_CHECK_PTR(ctx, x);
   RT_CHECK_PTR(ctx, out);
-  col_sum_accumulate_kernel<<<(unsigned)((cols + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(x, rows, cols, out);
+  col_sum_accumulate_kernel<<<(unsigned)((cols + 31) / 32), kThreads, 0, ctx->stream>>>(x, rows, cols, out);
   RT_LAUNCHED(ctx);
   return RT_OK;
 }

@@ -303,6 +303,57 @@ def test_fused_conv_relu_pool_rejects_odd_outputs(capi):
     assert ei.value.code == 4
 
 
+def test_gradient_accumulation_inside_the_producing_kernels(capi):
+    """rt_matmul_backward_accumulate adds a^T g to a gradient that already exists (and still returns dA), rt_sum_rows_accumulate
+    adds the column sums of g to an existing bias gradient: what add_grad does with a separate addition for a weight used at
+    every timestep.  Widths that are and are not multiples of four (the epilogue's 128-bit path and its scalar path)."""
+    r = rng(81)
+    i64 = C.c_int64
+    for (m, k, n) in ((64, 577, 2048), (64, 512, 65), (33, 70, 36), (128, 256, 128)):
+        a = r.standard_normal((m, k)).astype(np.float32)
+        b = r.standard_normal((k, n)).astype(np.float32)
+        g = r.standard_normal((m, n)).astype(np.float32)
+        old = r.standard_normal((k, n)).astype(np.float32)
+        da, acc = capi.empty((m, k)), capi.to_device(old)
+        a_d, b_d, g_d = capi.to_device(a), capi.to_device(b), capi.to_device(g)  # kept alive: a released block is handed out again
+        capi.call("matmul_backward_accumulate", a_d.ptr, b_d.ptr, g_d.ptr, i64(m), i64(k), i64(n), da.ptr, acc.ptr)
+        assert_close(da.numpy(), (g.astype(np.float64) @ b.astype(np.float64).T), 1e-4, f"dA {m}x{k}x{n}")
+        assert_close(acc.numpy(), old.astype(np.float64) + a.astype(np.float64).T @ g.astype(np.float64), 1e-4, f"accumulated dB {m}x{k}x{n}")
+        # without dA (the first operand takes no gradient)
+        acc2 = capi.to_device(old)
+        capi.call("matmul_backward_accumulate", a_d.ptr, b_d.ptr, g_d.ptr, i64(m), i64(k), i64(n), None, acc2.ptr)
+        assert np.array_equal(acc2.numpy(), acc.numpy())
+    for (rows, cols) in ((64, 2048), (1, 5), (7, 300), (0, 9)):
+        g = r.standard_normal((rows, cols)).astype(np.float32)
+        old = r.standard_normal(cols).astype(np.float32)
+        acc = capi.to_device(old)
+        g_d = capi.to_device(g) if rows else None
+        capi.call("sum_rows_accumulate", g_d.ptr if rows else None, i64(rows), i64(cols), acc.ptr)
+        assert_close(acc.numpy(), old.astype(np.float64) + g.astype(np.float64).sum(axis=0), 1e-5, f"bias accumulation {rows}x{cols}")
+
+
+def test_blocking_copies_are_refused_during_capture(capi):
+    """A copy that synchronises the stream cannot be recorded in a graph; it is refused with a clear error instead of breaking
+    the capture, which can still be ended and replayed."""
+    a = capi.to_device(np.arange(8, dtype=np.float32))
+    host = np.zeros(8, np.float32)
+    graph = C.c_void_p()
+    capi.call("graph_begin")
+    try:
+        with pytest.raises(RtError) as ei:
+            capi.check(capi.lib.rt_memcpy_d2h(capi.ctx, host.ctypes.data_as(C.c_void_p), a.ptr, C.c_size_t(32)))
+        assert ei.value.code == 4 and "graph" in str(ei.value)
+        with pytest.raises(RtError):
+            capi.check(capi.lib.rt_memcpy_h2d(capi.ctx, a.ptr, host.ctypes.data_as(C.c_void_p), C.c_size_t(32)))
+        capi.call("unary", C.c_int(UNARY["exp"]), a.ptr, a.ptr, C.c_int64(8), C.c_float(0), C.c_float(0))
+    finally:
+        capi.call("graph_end", C.byref(graph))
+    capi.call("graph_launch", graph)
+    capi.sync()
+    assert_close(a.numpy(), np.exp(np.arange(8, dtype=np.float32)), 1e-6, "captured kernel replayed")
+    capi.call("graph_destroy", graph)
+
+
 def test_max_pool_backward_with_overlapping_windows_is_reproducible(capi):
     """stride < kernel: several windows can route their gradient to one input element.  The sum is formed in the order
     of the reference's sequential scatter (ascending output index), so it equals a float32 replay of that loop bit for
