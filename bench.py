@@ -735,6 +735,9 @@ def main():
     elif "peer memory" in exchange:
         step_text = ("one CUDA-graph launch per step: forward, backward, pack of the gradients, signal to / bounded wait for the peers, "
                      "optimizer kernel that reads every rank's gradients over NVLink (no all-reduce call)")
+    elif os.environ.get("RT_B200_DP_NCCL_GRAPH") == "1":
+        step_text = ("one CUDA-graph launch per step: forward, backward, pack of the gradients, NCCL all-reduce and the fused optimizer step "
+                     "(step count read on the device) all recorded in the graph")
     else:
         step_text = f"CUDA-graph replay of forward+backward, {exchange}, one fused optimizer launch"
     dp_check = data_parallel_check(rt, dist, config, dims, rank, world, local_rank, nccl_id, trainer_config, tr) if world > 1 and not uncoupled else None

@@ -72,7 +72,10 @@ struct DpTrainer {
     if (!trace.buf) trace = B200Backend::zeros(rt::Shape{32});
     B200Backend::check(rt_stamp(B200Backend::ctx(), reinterpret_cast<uint64_t*>(trace.ptr()) + i));
   }
-  bool update_in_stream() const { return tr->w.optimizer != 0 && (world == 1 || fused); }
+  // RT_B200_DP_NCCL_GRAPH=1: the NCCL all-reduce and the optimizer are recorded in the step's graph too (pack -> all-reduce ->
+  // optimizer with the step count on the device), one launch per step like the single-GPU and the peer-memory steps.
+  bool nccl_in_graph = std::getenv("RT_B200_DP_NCCL_GRAPH") && std::getenv("RT_B200_DP_NCCL_GRAPH")[0] == '1';
+  bool update_in_stream() const { return tr->w.optimizer != 0 && (world == 1 || fused || (nccl_in_graph && !overlap_exchange)); }
   // pipelined steps: double-buffered uploads, two loss slots with completion events
   std::vector<rt_upload*> uploads;
   float* pipe_loss[2] = {nullptr, nullptr};
@@ -171,7 +174,7 @@ struct DpTrainer {
     for (auto& x : inputs) x.zero_grad();
     Tensor loss = rt::models::forward_loss(w, inputs);
     early_lo = early_hi = 0;
-    if (world == 1 || fused) {
+    if (update_in_stream() || world == 1 || fused) {
       stamp(1);
       loss.backward();
       stamp(2);
@@ -323,6 +326,14 @@ struct DpTrainer {
     auto& w = tr->w;
     rt_ctx* c = B200Backend::ctx();
     const int kind = w.optimizer == 1 ? 1 : 2;
+    if (!fused && world > 1) {  // NCCL inside the step: pack (with the clip), all-reduce, optimizer on the summed buffer
+      pack_and_reduce(0, (int)w.params.size(), true, true);
+      UpdatePointers u = update_pointers(flat.ptr());
+      B200Backend::check(rt_optimizer_step_multi_device_t(c, kind, (int)u.ps.size(), u.ps.data(), u.gs.data(), u.s1.data(), u.s2.data(),
+                                                          sizes.data(), w.lr, w.beta1, w.beta2, w.eps, w.momentum, ctrl_ptr(),
+                                                          1.0f / (float)world, 0, w.clip_lo, w.clip_hi));
+      return;
+    }
     if (!fused) {
       UpdatePointers u = update_pointers(nullptr);
       B200Backend::check(rt_optimizer_step_multi_device_t(c, kind, (int)u.ps.size(), u.ps.data(), u.gs.data(), u.s1.data(), u.s2.data(),
