@@ -765,6 +765,227 @@ tc_gemm_kernel(const LA la, const LB lb, const EPI epi, int K, int k_per_split, 
   }
 }
 
+// ---- plain products with the A operand in tensor memory (TS form) -----------------------------------------------------
+// tc_gemm_kernel stages the hi / lo images of BOTH operands in shared memory and is bound by its bandwidth: per K-block of 32 the
+// producers write 64 KB and the twelve MMAs read 96 KB through a 128 B/cycle path (1 250 cycles against 780 cycles of tensor
+// work; measured 2 350 cycles per K-block).  Here the A tile never touches shared memory: every producer thread owns one row of
+// the tile (= one lane of tensor memory), loads 16 of its 32 k-values, splits them and writes hi and lo straight into tensor
+// memory with tcgen05.st; the MMAs read A from there (an MMA with A in tensor memory costs N/2 cycles for every N) and only
+// the 64-column B tile crosses shared memory (16 KB written, 24 KB read per K-block).  Used for products whose grid is small
+// enough to be latency-bound (the fully connected and recurrent layers); large products keep the 128 x 128 tile, whose wider B
+// tile halves the traffic from L2.
+struct PlainA {  // element(row, k) = trans ? p[k * ld + row] : p[row * ld + k]
+  const float* p;
+  int64_t ld;
+  int rows;
+  bool trans, vec;
+};
+constexpr int kTsBN = 64, kTsStages = 3, kTsAccs = 4;
+constexpr uint32_t kTsAccCols = kTsAccs * kTsBN;        // 256 accumulator columns
+constexpr uint32_t kTsAStageCols = 2 * BK;              // hi k 0..31, lo k 0..31
+struct TsSmem {
+  static constexpr uint32_t b_bytes = tile_bytes(kTsBN);
+  static constexpr uint32_t stage_bytes = 2 * b_bytes;  // B hi, B lo
+  static constexpr uint32_t bar_offset = kTsStages * stage_bytes;
+  static constexpr uint32_t total = bar_offset + (2 * kTsStages + 1) * 8 + 16;
+};
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
+      "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// One 3xTF32 K-step with A in tensor memory: lo*hi and hi*lo into the cross accumulator, hi*hi into the main one.
+__device__ __forceinline__ void umma_tf32_step_ts_elect(uint32_t d_cross, uint32_t d_main, uint32_t a_hi_t, uint32_t a_lo_t, uint32_t b_hi_lo32,
+                                                        uint32_t b_lo_lo32, uint32_t b_hi32, uint32_t idesc, uint32_t acc_cross,
+                                                        uint32_t acc_main) {
+  asm volatile(
+      "{\n\t.reg .pred pc, pm, pt, pe;\n\t"
+      ".reg .b64 dbh, dbl;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "setp.ne.b32 pc, %8, 0;\n\t"
+      "setp.ne.b32 pm, %9, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "mov.b64 dbh, {%4, %6};\n\t"
+      "mov.b64 dbl, {%5, %6};\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::tf32 [%0], [%3], dbh, %7, pc;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::tf32 [%0], [%2], dbl, %7, pt;\n\t"
+      "@pe tcgen05.mma.cta_group::1.kind::tf32 [%1], [%2], dbh, %7, pm;\n\t}" ::"r"(d_cross), "r"(d_main), "r"(a_hi_t), "r"(a_lo_t),
+      "r"(b_hi_lo32), "r"(b_lo_lo32), "r"(b_hi32), "r"(idesc), "r"(acc_cross), "r"(acc_main)
+      : "memory");
+}
+
+template <class LB, class EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_gemm_ts_kernel(const PlainA la, const LB lb, const EPI epi, int K, int k_per_split, int* status) {
+  extern __shared__ __align__(128) char smem[];
+  using SL = TsSmem;
+  constexpr int BN = kTsBN, STAGES = kTsStages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int kbeg = blockIdx.z * k_per_split;
+  const int kend = min(K, kbeg + k_per_split);
+  const int nkb = (kend - kbeg + BK - 1) / BK;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bars = smem_base + SL::bar_offset;  // full[s], empty[s], acc
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + SL::bar_offset + (2 * STAGES + 1) * 8);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bars + 8 * s, kProducerWarps);
+      mbar_init(bars + 8 * (STAGES + s), 1);
+    }
+    mbar_init(bars + 8 * (2 * STAGES), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kProducerWarps) tmem_alloc(smem_u32(tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_a = tmem_base + kTsAccCols;  // A stages behind the accumulators
+
+  bool ok = true;
+  if (warp < kProducerWarps) {
+    // ---------------- producers: every thread one row of A (16 k-values) and its share of the B tile ----------------
+    const int quad = warp & 3, khalf = warp >> 2;
+    const int row = m0 + quad * 32 + lane;
+    const bool row_ok = row < la.rows;
+    const float* arow = la.trans ? la.p + row : la.p + (int64_t)row * la.ld;
+    Producer<BN, LB> pb;
+    pb.init(lb, n0, warp, lane);
+    struct ABuf { float v[16]; };
+    auto fetch_a = [&](int k0, ABuf& b) {
+      const int kk = k0 + khalf * 16;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) b.v[i] = 0.f;
+      if (!row_ok || kk >= kend) return;
+      if (!la.trans) {
+        if (la.vec && kk + 15 < kend) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(arow + kk) + j);
+            b.v[4 * j] = t.x; b.v[4 * j + 1] = t.y; b.v[4 * j + 2] = t.z; b.v[4 * j + 3] = t.w;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            if (kk + i < kend) b.v[i] = __ldg(arow + kk + i);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (kk + i < kend) b.v[i] = __ldg(arow + (int64_t)(kk + i) * la.ld);  // consecutive lanes read consecutive rows
+      }
+    };
+    ABuf a0, a1;
+    typename Producer<BN, LB>::Buf b0, b1;
+    auto stage_out = [&](int it, const ABuf& ba, const typename Producer<BN, LB>::Buf& bb) -> bool {
+      const int s = it % STAGES;
+      if (it >= STAGES && !mbar_wait(bars + 8 * (STAGES + s), ((it / STAGES) - 1) & 1, status, 1)) return false;
+      char* st = smem + s * SL::stage_bytes;
+      pb.commit(bb, st, st + SL::b_bytes);
+      uint32_t hi[16], lo[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t h = __float_as_uint(ba.v[i]) & 0xFFFFE000u;
+        hi[i] = h;
+        lo[i] = __float_as_uint(ba.v[i] - __uint_as_float(h));
+      }
+      const uint32_t ta = tmem_a + ((uint32_t)(quad * 32) << 16) + (uint32_t)s * kTsAStageCols + (uint32_t)khalf * 16;
+      tmem_st16(ta, hi);
+      tmem_st16(ta + BK, lo);
+      tmem_wait_st();
+      fence_async_smem();  // the B stores -> async proxy
+      tc_fence_before();   // the tensor-memory stores are ordered before the arrive
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8 * s);
+      return true;
+    };
+    if (nkb > 0) {
+      fetch_a(kbeg, a0);
+      pb.fetch(lb, kbeg, kend, b0);
+    }
+    for (int it = 0; it < nkb && ok; it += 2) {
+      if (it + 1 < nkb) {
+        fetch_a(kbeg + (it + 1) * BK, a1);
+        pb.fetch(lb, kbeg + (it + 1) * BK, kend, b1);
+      }
+      ok = stage_out(it, a0, b0);
+      if (ok && it + 1 < nkb) {
+        if (it + 2 < nkb) {
+          fetch_a(kbeg + (it + 2) * BK, a0);
+          pb.fetch(lb, kbeg + (it + 2) * BK, kend, b0);
+        }
+        ok = stage_out(it + 1, a1, b1);
+      }
+    }
+    // ---------------- epilogue ----------------
+    if (ok && nkb > 0) ok = mbar_wait(bars + 8 * (2 * STAGES), 0, status, 2);
+    tc_fence_after();
+    if (ok) {
+      const int m = m0 + quad * 32 + lane;
+      const int c = khalf;  // two chunks of 32 columns: warps 0-3 the first, warps 4-7 the second
+      float v[32];
+      if (nkb > 0) {
+        const uint32_t t0 = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
+        tmem_ld32(t0, v);  // cross terms
+#pragma unroll
+        for (int a = 1; a < kTsAccs; ++a) {
+          float u[32];
+          tmem_ld32(t0 + (uint32_t)(a * BN), u);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] += u[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+      }
+      epi.store32(m, n0 + c * 32, v, blockIdx.z);
+    }
+  } else {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t idesc = make_idesc(BN);
+    const uint32_t hi32 = desc_hi32(SBO);
+    uint32_t rot = 0;
+    for (int it = 0; it < nkb && ok; ++it) {
+      const int s = it % STAGES;
+      ok = __all_sync(0xffffffffu, mbar_wait(bars + 8 * s, (it / STAGES) & 1, status, 3));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t b_hi = desc_lo32(smem_base + s * SL::stage_bytes, LBO), b_lo = b_hi + (SL::b_bytes >> 4);
+      const uint32_t a_hi = tmem_a + (uint32_t)s * kTsAStageCols, a_lo = a_hi + BK;
+#pragma unroll
+      for (int j = 0; j < BK / 8; ++j) {
+        const uint32_t ko = (uint32_t)j * ((2 * LBO) >> 4);
+        const int t = it * (BK / 8) + j;
+        umma_tf32_step_ts_elect(tmem_base, tmem_base + (1 + rot) * BN, a_hi + 8 * j, a_lo + 8 * j, b_hi + ko, b_lo + ko, hi32, idesc,
+                                t != 0 ? 1u : 0u, t >= 3 ? 1u : 0u);
+        rot = rot == 2 ? 0 : rot + 1;
+      }
+      umma_commit_elect(bars + 8 * (STAGES + s));  // frees the B stage and the A slot when these MMAs have read them
+    }
+    if (ok && nkb > 0) umma_commit_elect(bars + 8 * (2 * STAGES));
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kProducerWarps) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <class LB, class EPI>
+rt_status launch_ts(rt_ctx* ctx, const PlainA& la, const LB& lb, const EPI& epi, int M, int N, int K, int splits, int kps) {
+  auto kern = tc_gemm_ts_kernel<LB, EPI>;
+  RT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TsSmem::total));
+  dim3 grid((N + kTsBN - 1) / kTsBN, (M + BM - 1) / BM, splits);
+  kern<<<grid, kThreads, TsSmem::total, ctx->stream>>>(la, lb, epi, K, kps, ctx->device_status);
+  RT_LAUNCHED(ctx);
+  return RT_OK;
+}
+
 template <int BN, int STAGES, class LA, class LB, class EPI>
 rt_status launch(rt_ctx* ctx, const LA& la, const LB& lb, const EPI& epi, int M, int N, int K, int splits, int kps) {
   using SL = SmemLayout<BN, STAGES>;
@@ -827,6 +1048,51 @@ rt_status gemm_plain(rt_ctx* ctx, const LA& la, const LB& lb, float* c, int64_t 
 
 inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// The tensor-memory variant for products whose grid of 128 x 64 tiles fits one wave (one CTA per SM: the kernel takes all of
+// tensor memory): they are bound by latency and by the staging of the operands, not by the traffic from L2.  Measured on the
+// fully connected layer of the CNN (256 x 3136 x 128): 14.2 -> 11.2, 13.7 -> 9.4, 11.9 -> 10.2 us for forward, dX, dW; a K-block
+// costs 0.16 us instead of 1.1.  RT_B200_GEMM_TS=0 turns it off, =2 uses it for every plain product.
+inline bool use_ts_tile(rt_ctx* ctx, int64_t M, int64_t N) {
+  static const int mode = [] {
+    const char* e = getenv("RT_B200_GEMM_TS");
+    return e && e[0] ? atoi(e) : 1;
+  }();
+  if (mode == 0) return false;
+  if (mode >= 2) return true;
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + kTsBN - 1) / kTsBN);
+  return tiles <= (int64_t)ctx->sm_count;
+}
+template <class LB>
+rt_status gemm_plain_ts(rt_ctx* ctx, const PlainA& la, const LB& lb, float* c, int64_t ldc, int64_t M, int64_t N, int64_t K,
+                        bool accumulate) {
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + kTsBN - 1) / kTsBN);
+  int splits = 1, kps = (int)((K + BK - 1) / BK * BK);
+  if (!accumulate && ldc == N) {  // one CTA per SM (the kernel takes all of tensor memory); at least 4 K-blocks per split
+    int64_t want = ((int64_t)ctx->sm_count + tiles - 1) / tiles;
+    int64_t max_s = K / (4 * BK);
+    if (max_s < 1) max_s = 1;
+    int64_t sp = want < max_s ? want : max_s;
+    if (sp < 1) sp = 1;
+    if (sp > 512) sp = 512;
+    int64_t per = (K + sp - 1) / sp;
+    per = (per + BK - 1) / BK * BK;
+    sp = (K + per - 1) / per;
+    splits = (int)(sp < 1 ? 1 : sp);
+    kps = (int)per;
+  }
+  if (splits == 1) {
+    PlainOut epi{c, ldc, 0, (int)M, (int)N, accumulate};
+    return launch_ts(ctx, la, lb, epi, (int)M, (int)N, (int)K, 1, kps);
+  }
+  RtScratch ws(ctx);
+  rt_status st = ws.alloc(sizeof(float) * (size_t)splits * M * N);
+  if (st != RT_OK) return st;
+  PlainOut epi{ws.as<float>(), N, M * N, (int)M, (int)N, false};
+  st = launch_ts(ctx, la, lb, epi, (int)M, (int)N, (int)K, splits, kps);
+  if (st != RT_OK) return st;
+  return rt_sum_axis_internal(ctx, ws.as<float>(), 1, splits, M * N, c, 1.f);
+}
+
 inline PixelTapRows pixel_rows(const float* src, int C, int H, int W, int rows_h, int rows_w, int kh, int kw, int sh, int sw,
                                int ph, int pw, int rows) {
   PixelTapRows l;
@@ -859,6 +1125,11 @@ rt_status rt_gemm_tc_internal(rt_ctx* ctx, int trans_a, int trans_b, int64_t m, 
   if (m <= 0 || n <= 0 || k <= 0) return RT_ERR_UNIMPLEMENTED;
   if (m >= (1ll << 31) || n >= (1ll << 31) || k >= (1ll << 31)) return RT_ERR_UNIMPLEMENTED;
   bool acc = accumulate != 0;
+  if (use_ts_tile(ctx, m, n)) {
+    const PlainA pa{a, lda, (int)m, trans_a != 0, al16(a) && lda % 4 == 0};
+    if (!trans_b) return gemm_plain_ts(ctx, pa, MatMN{b, ldb, (int)n, al16(b) && ldb % 4 == 0}, c, ldc, m, n, k, acc);
+    return gemm_plain_ts(ctx, pa, MatK{b, ldb, (int)n, al16(b) && ldb % 4 == 0}, c, ldc, m, n, k, acc);
+  }
   // A(row=m, k): not transposed -> K-contiguous; transposed ([K,M] storage) -> M-contiguous
   // B(row=n, k): not transposed ([K,N] storage) -> N-contiguous; transposed ([N,K]) -> K-contiguous
   if (!trans_a && !trans_b)
