@@ -336,6 +336,39 @@ __global__ void __launch_bounds__(256) col_reduce_single(const float* __restrict
   }
 }
 
+// ---- inner > 1, few rows and a narrow output (a bias gradient, the sum of a few split-K partials of a small matrix) ----------
+// One launch of latency-bound size: what counts is that every load is in flight at once.  Block = 32 columns x 32 row lanes; a
+// lane takes rows ty, ty + 32, ... with eight independent loads per round; the 32 partial results of a column are combined in
+// lane order through shared memory.  grid: (column tiles, outer).
+template <int KIND>
+__global__ void __launch_bounds__(1024) col_reduce_short(const float* __restrict__ x, float* __restrict__ out, int64_t len, int64_t inner,
+                                                          float scale) {
+  __shared__ float part[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t c = (int64_t)blockIdx.x * 32 + tx, o = blockIdx.y;
+  float acc = Red<KIND>::init();
+  if (c < inner) {
+    const float* base = x + o * len * inner + c;
+    int64_t r = ty;
+    for (; r + 7 * 32 < len; r += 8 * 32) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldg(base + (r + 32 * u) * inner);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc = Red<KIND>::op(acc, v[u]);
+    }
+    for (; r < len; r += 32) acc = Red<KIND>::op(acc, __ldg(base + r * inner));
+  }
+  part[ty][tx] = acc;
+  __syncthreads();
+  if (ty == 0 && c < inner) {
+    float s = part[0][tx];
+#pragma unroll
+    for (int y = 1; y < 32; ++y) s = Red<KIND>::op(s, part[y][tx]);
+    out[o * inner + c] = s * scale;
+  }
+}
+
 template <int KIND>
 rt_status reduce_float(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, int64_t inner, float* out, float scale) {
   if (outer * inner == 0) return RT_OK;
@@ -420,6 +453,12 @@ rt_status reduce_float(rt_ctx* ctx, const float* x, int64_t outer, int64_t len, 
       rt_status st = reduce_float<KIND>(ctx, x + o0 * len * inner, oc, len, inner, out + o0 * inner, scale);
       if (st != RT_OK) return st;
     }
+    return RT_OK;
+  }
+  if (short_reduction && len >= 16 && outer * inner <= 4096 && outer <= 65535) {
+    // few rows, narrow output: one latency-bound launch with all loads in flight (6 us -> 2.5 us for a [256, 10] bias gradient)
+    col_reduce_short<KIND><<<dim3((unsigned)((inner + 31) / 32), (unsigned)outer), 1024, 0, ctx->stream>>>(x, out, len, inner, scale);
+    RT_LAUNCHED(ctx);
     return RT_OK;
   }
   if (vec && !short_reduction && ctx->reduce_counters) {
