@@ -594,7 +594,10 @@ def main():
     l0 = capi.launches()
     tr.step(inputs)
     tr.last_loss()
-    launches_per_replay = capi.launches() - l0 - 1  # kernels recorded in the graph (the optimizer launch is eager)
+    # kernels recorded in the graph; with the NCCL exchange the optimizer launch of that first step was eager (the all-reduce is
+    # NCCL's kernel, not counted)
+    eager_update = (world > 1 and not uncoupled and "peer memory" not in exchange and os.environ.get("RT_B200_DP_NCCL_GRAPH") != "1")
+    launches_per_replay = capi.launches() - l0 - (1 if eager_update else 0)
     for _ in range(args.warmup):
         tr.step(None)
     barrier()
