@@ -134,9 +134,20 @@ def cpu_all_cores(config, dims, per_gpu, steps):
                       f"(wall {wall:.1f} s incl. start-up); not reference behaviour (the reference runs one thread)"}
 
 
-def workload_config(desc, per_gpu, world, extra=None):
+# How the timed steps treat the L2 (part of `config`, identical in both arms so that the two lines describe one configuration)
+L2_POLICY = {
+    "c3": "no explicit flush: one step touches about 230 MB of device tensors (L2 is 126 MB) and steps run back to back",
+    "c4": "no explicit flush: one step touches about 2 GB of device tensors (L2 is 126 MB) and steps run back to back",
+    "c2": "no explicit flush: one pass touches about 1.5 GB of device tensors (L2 is 126 MB) and passes run back to back",
+    "c5": "no explicit flush: one step touches several hundred MB of device tensors (L2 is 126 MB) and steps run back to back",
+    "c1": "no explicit flush: the model and a batch fit the L2 (a launch-bound workload); steps run back to back",
+}
+
+
+def workload_config(desc, per_gpu, world, workload=None):
     cfg = {"workload": desc, "per_gpu_batch": per_gpu, "global_batch": per_gpu * world, "parallelism": f"dp{world}"}
-    cfg.update(extra or {})
+    if workload is not None:
+        cfg["l2"] = L2_POLICY[workload]
     return cfg
 
 
@@ -156,7 +167,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(desc, per_gpu, max(1, args.gpus)),
+        "config": workload_config(desc, per_gpu, max(1, args.gpus), args.workload),
         "note": "CPU path of the reference, single host thread (as the reference is built); one process whatever --gpus says",
         "cpu_baseline": cpu,
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -762,9 +773,8 @@ def main():
             "metric": "train_samples_per_s", "value": total * args.steps / (ms_resident * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_resident / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(desc, per_gpu, world, {
-                "l2": f"no explicit flush: device memory in use by one step is {in_use.value / 1e6:.0f} MB (L2 is 126 MB); steps run back to back",
-                "step": step_text}),
+            "config": workload_config(desc, per_gpu, world, args.workload),
+            "step_structure": step_text, "device_bytes_in_use": int(in_use.value),
             "e2e": {"value": total * args.steps / (ms_e2e * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(gpu_launches), "final_loss": loss, "clocks": clocks,
