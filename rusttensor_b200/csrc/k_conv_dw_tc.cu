@@ -16,7 +16,7 @@
 //   D (kh accumulators of N columns, fp32, tensor memory): D_ky[r, kx*CIT + ci] += A[r, :] . B_row(yo-ph+ky)[kx*CIT+ci, :].
 //     Both the hi and the lo image of B are multiplied into the same accumulator, so rows 0..63 hold g_hi * x and rows
 //     64..127 g_lo * x; the epilogue adds the two halves.
-// Rows of g and x reach shared memory through cp.async.bulk.tensor (TMA, 3-D maps over [HW, C, N], no multicast) issued by
+// Rows of g and x reach shared memory through cp.async.bulk.tensor (TMA, 3-D maps over [HW, C, N], every CTA fetching its own rows) issued by
 // one thread several stages ahead; eight converter warps turn them into MMA operands; one warp issues the MMAs.  The CTAs
 // of one (output-channel tile, input-channel tile) pair split the units among themselves; every CTA writes its partial
 // sums to a workspace and a second kernel adds the partials in a fixed order (bit-reproducible, no atomics).  Long
