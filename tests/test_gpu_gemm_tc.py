@@ -22,7 +22,9 @@ def gemm(capi, ta, tb, m, n, k, a, b, c0=None, accumulate=0, lda=None, ldb=None)
 
 
 SHAPES = [(128, 128, 32), (128, 128, 64), (256, 128, 3136), (256, 3136, 128), (3136, 128, 256), (64, 2048, 577), (577, 2048, 64),
-          (64, 577, 2048), (130, 70, 33), (257, 129, 65), (1000, 24, 200), (128, 32, 4096), (512, 512, 512), (33, 17, 2000)]
+          (64, 577, 2048), (130, 70, 33), (257, 129, 65), (1000, 24, 200), (128, 32, 4096), (512, 512, 512), (33, 17, 2000),
+          # more 128x64 tiles than the GPU has multiprocessors: the shared-memory-operand kernel takes these
+          (1024, 1536, 160), (2100, 1030, 72)]
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES, ids=str)
