@@ -210,7 +210,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_x, const Params p, int* status) {
   extern __shared__ __align__(128) char smem[];
   constexpr int KSTEPS = P / 8;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // broadcast from lane 0 so that the compiler knows the value is the same in every lane (uniform role branches and registers)
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int combo = (int)blockIdx.x % p.n_combo, slot_id = (int)blockIdx.x / p.n_combo;
   const int cot = combo / p.n_cit, cit = combo - cot * p.n_cit;
   // this CTA's units, cut into SEG segments
@@ -246,7 +247,7 @@ conv_dw_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
   const uint32_t a_col0 = (uint32_t)(p.kh * p.N);  // the A slots follow the kh accumulators
 
   if (warp == kConvWarps) {

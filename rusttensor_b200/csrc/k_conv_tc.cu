@@ -83,7 +83,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
   extern __shared__ __align__(128) char smem[];
   constexpr uint32_t kTmemCols = BN == 32 ? 256 : 512;  // two accumulator sets of 3*BN columns, rounded to a power of two
   static_assert(2 * kAccCols * BN <= kTmemCols, "accumulator sets must fit the allocation");
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The warp index and the tensor-memory base are broadcast from lane 0: a value that comes out of a shuffle from a fixed lane is
+  // known to be the same in every lane, so the role branches are uniform and the MMA warp's descriptor arithmetic can stay in
+  // uniform registers, which is where tcgen05.mma takes its operands from.
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int taps = p.kh * p.kw;
   const uint32_t plane = (uint32_t)p.win * 16;               // bytes of one channel-quad plane
   const uint32_t a_half = (uint32_t)CGQ * plane;           // hi (or lo) part of a window stage
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
   const int my_tiles = p.tiles > (int)blockIdx.x ? (p.tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
   bool ok = true;

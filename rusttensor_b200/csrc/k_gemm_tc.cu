@@ -644,7 +644,8 @@ tc_gemm_kernel(const LA la, const LB lb, const EPI epi, int K, int k_per_split, 
   constexpr int kAccs = 4;
   constexpr uint32_t kTmemCols = kAccs * BN;
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM allocation must be a power of two <= 512");
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // broadcast from lane 0 so that the compiler knows the value is the same in every lane (uniform role branches and registers)
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int kbeg = blockIdx.z * k_per_split;
   const int kend = min(K, kbeg + k_per_split);
@@ -666,7 +667,7 @@ tc_gemm_kernel(const LA la, const LB lb, const EPI epi, int K, int k_per_split, 
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
 
   bool ok = true;
   if (warp < kProducerWarps) {
@@ -823,7 +824,8 @@ tc_gemm_ts_kernel(const PlainA la, const LB lb, const EPI epi, int K, int k_per_
   extern __shared__ __align__(128) char smem[];
   using SL = TsSmem;
   constexpr int BN = kTsBN, STAGES = kTsStages;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // broadcast from lane 0 so that the compiler knows the value is the same in every lane (uniform role branches and registers)
+  const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int kbeg = blockIdx.z * k_per_split;
   const int kend = min(K, kbeg + k_per_split);
@@ -843,7 +845,7 @@ tc_gemm_ts_kernel(const PlainA la, const LB lb, const EPI epi, int K, int k_per_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
   const uint32_t tmem_a = tmem_base + kTsAccCols;  // A stages behind the accumulators
 
   bool ok = true;
