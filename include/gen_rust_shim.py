@@ -24,7 +24,8 @@ C2RUST = {
     "int32_t": "i32", "const int32_t*": "*const i32", "int64_t": "i64", "int64_t*": "*mut i64", "const int64_t*": "*const i64",
     "uint32_t": "u32", "uint64_t": "u64", "uint64_t*": "*mut u64", "size_t": "usize", "float": "f32", "float*": "*mut f32", "const float*": "*const f32",
     "double*": "*mut f64", "float* const*": "*const *mut f32", "const float* const*": "*const *const f32",
-    "void*": "*mut c_void", "void**": "*mut *mut c_void", "const void*": "*const c_void",
+    "void*": "*mut c_void", "void**": "*mut *mut c_void", "const void*": "*const c_void", "void* const*": "*const *mut c_void",
+    "rt_upload* const*": "*const *mut RtUpload",
     "const uint8_t*": "*const u8", "uint8_t*": "*mut u8", "rt_status": "RtStatus", "const char*": "*const c_char", "void": "()",
 }
 

@@ -85,6 +85,15 @@ rt_status rt_upload_create(rt_ctx* ctx, size_t bytes, rt_upload** out);
 rt_status rt_upload_destroy(rt_ctx* ctx, rt_upload* up);
 rt_status rt_upload_host_buffer(rt_ctx* ctx, rt_upload* up, void** pinned);
 rt_status rt_upload_submit(rt_ctx* ctx, rt_upload* up, void* dst);
+/* The same for up to 8 uploads at once (all inputs of a step): their host -> staging copies run on their copy streams as above,
+ * and ONE kernel on the context's stream copies every staging buffer to its destination, instead of one device-to-device
+ * memcpy per input.  ups[i] must be distinct. */
+rt_status rt_upload_submit_all(rt_ctx* ctx, rt_upload* const* ups, void* const* dsts, int n);
+/* Writes n <= 4096 floats at src (device) to pinned host memory from rt_host_alloc with a one-block kernel on the context's
+ * stream: the read-back of a loss (Backend::copy_to_host, mod.rs:248, without its synchronisation) costs a kernel launch
+ * instead of a copy-engine round trip.  The values are visible to the host once an event recorded after this call has
+ * completed.  Any other kind of destination is refused. */
+rt_status rt_publish_to_host(rt_ctx* ctx, float* pinned_dst, const float* src, int64_t n);
 /* A side stream for work that may overlap what follows on the context's stream (new; used to all-reduce the
  * gradients that are ready while the rest of the backward pass runs).  Between begin and end every rt_* call of this
  * context is enqueued on the side stream, which first waits for everything queued before `begin`; `join` makes the

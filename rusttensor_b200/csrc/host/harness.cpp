@@ -537,14 +537,19 @@ struct DpTrainer {
     pipe_setup();
     if (!graph) capture();
     rt_ctx* c = B200Backend::ctx();
-    for (size_t i = 0; i < inputs.size(); ++i) {
-      B200Backend::make_unique(inputs[i].data_mut());
-      B200Backend::check(rt_upload_submit(c, uploads[i], inputs[i].data().ptr()));
+    // all inputs in one staging -> tensor kernel (one call per 8 inputs), the loss by a store to pinned memory: no copy-engine
+    // round trip sits between two replays of the step
+    std::vector<void*> dsts;
+    for (auto& x : inputs) {
+      B200Backend::make_unique(x.data_mut());
+      dsts.push_back(x.data().ptr());
     }
+    for (size_t i = 0; i < inputs.size(); i += 8)
+      B200Backend::check(rt_upload_submit_all(c, uploads.data() + i, dsts.data() + i, (int)std::min<size_t>(8, inputs.size() - i)));
     replay();
     exchange_and_update();
     const int k = (int)(pipe_steps & 1);
-    B200Backend::check(rt_memcpy_d2h_async(c, pipe_loss[k], captured_loss.data().ptr(), sizeof(float)));
+    B200Backend::check(rt_publish_to_host(c, pipe_loss[k], captured_loss.data().ptr(), 1));
     B200Backend::check(rt_event_record(c, pipe_done[k]));
     const bool have_prev = pipe_steps > 0;
     if (have_prev) {
@@ -599,7 +604,7 @@ struct DpTrainer {
     }
     replay();
     exchange_and_update();
-    B200Backend::check(rt_memcpy_d2h_async(c, pipe_loss[k], captured_loss.data().ptr(), sizeof(float)));
+    B200Backend::check(rt_publish_to_host(c, pipe_loss[k], captured_loss.data().ptr(), 1));
     B200Backend::check(rt_event_record(c, pipe_done[k]));
     const bool have_prev = pipe_steps > 0;
     if (have_prev) {

@@ -2,6 +2,7 @@
 // gradient all-reduce of librt_b200.so.
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdlib>
 #include <cstring>
@@ -349,6 +350,98 @@ rt_status rt_upload_submit(rt_ctx* ctx, rt_upload* up, void* dst) {
   RT_CUDA(ctx, cudaEventRecord(up->consumed[k], ctx->stream));
   up->used[k] = true;
   up->next = k ^ 1;
+  return RT_OK;
+}
+
+// ---- several uploads in one go, and a result written straight to pinned host memory ---------------
+// A training step that takes its inputs from the host needs, per step, one staging -> tensor copy per input and the
+// read-back of the loss.  As stream memcpys these are three copy-engine round trips between two graph launches; as
+// two small kernels they run back to back with the step's own kernels.
+constexpr int kMaxUploadsPerSubmit = 8;
+struct MultiCopyParams {
+  const char* src[kMaxUploadsPerSubmit];
+  char* dst[kMaxUploadsPerSubmit];
+  unsigned long long bytes[kMaxUploadsPerSubmit];
+};
+// blockIdx.y = which copy; 16-byte units when both ends are 16-byte aligned, single bytes for the rest
+__global__ void multi_copy_kernel(const MultiCopyParams p) {
+  const int seg = blockIdx.y;
+  const char* __restrict__ src = p.src[seg];
+  char* __restrict__ dst = p.dst[seg];
+  const size_t bytes = p.bytes[seg];
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (size_t)gridDim.x * blockDim.x;
+  size_t done = 0;
+  if (((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+    const size_t n16 = bytes >> 4;
+    const float4* s4 = reinterpret_cast<const float4*>(src);
+    float4* d4 = reinterpret_cast<float4*>(dst);
+    for (size_t i = tid; i < n16; i += nthreads) d4[i] = __ldcs(s4 + i);
+    done = n16 << 4;
+  }
+  for (size_t i = done + tid; i < bytes; i += nthreads) dst[i] = src[i];
+}
+
+rt_status rt_upload_submit_all(rt_ctx* ctx, rt_upload* const* ups, void* const* dsts, int n) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, ups);
+  RT_CHECK_PTR(ctx, dsts);
+  if (n < 1 || n > kMaxUploadsPerSubmit)
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_upload_submit_all: 1 to %d uploads per call, got %d", kMaxUploadsPerSubmit, n);
+  if (ctx->capturing) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_upload_submit_all during graph capture");
+  for (int i = 0; i < n; ++i) {
+    RT_CHECK_PTR(ctx, ups[i]);
+    RT_CHECK_PTR(ctx, dsts[i]);
+    for (int j = 0; j < i; ++j)
+      if (ups[j] == ups[i]) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_upload_submit_all: upload %d is listed twice", i);
+  }
+  MultiCopyParams p{};
+  size_t most = 0;
+  for (int i = 0; i < n; ++i) {
+    rt_upload* up = ups[i];
+    const int k = up->next;
+    // the staging buffer may still be read by the staging -> dst copy of two submits ago
+    if (up->used[k]) RT_CUDA(ctx, cudaStreamWaitEvent(up->copy_stream, up->consumed[k], 0));
+    RT_CUDA(ctx, cudaMemcpyAsync(up->staging[k], up->pinned[k], up->bytes, cudaMemcpyHostToDevice, up->copy_stream));
+    RT_CUDA(ctx, cudaEventRecord(up->copied[k], up->copy_stream));
+    RT_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, up->copied[k], 0));
+    p.src[i] = static_cast<const char*>(up->staging[k]);
+    p.dst[i] = static_cast<char*>(dsts[i]);
+    p.bytes[i] = up->bytes;
+    most = up->bytes > most ? up->bytes : most;
+  }
+  const size_t units = (most + 15) / 16;
+  const unsigned blocks = (unsigned)std::min<size_t>((units + 255) / 256, (size_t)ctx->sm_count * 4);
+  multi_copy_kernel<<<dim3(blocks ? blocks : 1, (unsigned)n), 256, 0, ctx->stream>>>(p);
+  RT_LAUNCHED(ctx);
+  for (int i = 0; i < n; ++i) {
+    rt_upload* up = ups[i];
+    const int k = up->next;
+    RT_CUDA(ctx, cudaEventRecord(up->consumed[k], ctx->stream));
+    up->used[k] = true;
+    up->next = k ^ 1;
+  }
+  return RT_OK;
+}
+
+__global__ void publish_kernel(const float* __restrict__ src, float* __restrict__ host_dst, int n) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) host_dst[i] = src[i];
+  __threadfence_system();
+}
+
+rt_status rt_publish_to_host(rt_ctx* ctx, float* pinned_dst, const float* src, int64_t n) {
+  RT_CHECK_CTX(ctx);
+  RT_CHECK_PTR(ctx, pinned_dst);
+  RT_CHECK_PTR(ctx, src);
+  if (n < 1 || n > 4096) RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_publish_to_host: 1 to 4096 values, got %lld", (long long)n);
+  // The kernel stores through the host pointer, so it must be pinned memory the device can reach (rt_host_alloc).
+  cudaPointerAttributes attr{};
+  cudaError_t e = cudaPointerGetAttributes(&attr, pinned_dst);
+  if (e != cudaSuccess || attr.type != cudaMemoryTypeHost || attr.devicePointer == nullptr) {
+    if (e != cudaSuccess) cudaGetLastError();
+    RT_FAIL(ctx, RT_ERR_INVALID_OPERATION, "rt_publish_to_host: the destination is not pinned host memory (use rt_host_alloc)");
+  }
+  publish_kernel<<<1, n < 256 ? 32 : 256, 0, ctx->stream>>>(src, static_cast<float*>(attr.devicePointer), (int)n);
+  RT_LAUNCHED(ctx);
   return RT_OK;
 }
 

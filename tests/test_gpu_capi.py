@@ -205,6 +205,58 @@ def test_upload_pipeline_and_events(capi):
     capi.call("upload_destroy", up)
 
 
+def test_upload_submit_all_and_publish_to_host(capi):
+    """rt_upload_submit_all: several uploads, one staging -> destination kernel (sizes that are and are not multiples of 16
+    bytes, a destination that is not 16-byte aligned); rt_publish_to_host: values land in pinned memory once an event recorded
+    after the call has completed, and a destination that is not pinned host memory is refused."""
+    sizes = [1 << 16, 2560, 7, 1]
+    ups = []
+    for n in sizes:
+        up = C.c_void_p()
+        capi.call("upload_create", C.c_size_t(4 * n), C.byref(up))
+        ups.append(up)
+    big = capi.empty((sizes[0] + 1,))
+    dsts = [capi.empty((n,)) for n in sizes[1:]]
+    ptrs = [C.c_void_p(big.ptr.value + 4)] + [d.ptr for d in dsts]  # the first destination starts 4 bytes into its buffer
+    ev = C.c_void_p()
+    capi.call("event_create", C.byref(ev))
+    up_arr = (C.c_void_p * len(ups))(*[u.value for u in ups])
+    dst_arr = (C.c_void_p * len(ups))(*[q.value for q in ptrs])
+    total = capi.to_device(np.zeros(1, np.float32))
+    out = C.c_void_p()
+    capi.call("host_alloc", C.c_size_t(4), C.byref(out))
+    host_out = np.ctypeslib.as_array(C.cast(out, C.POINTER(C.c_float)), shape=(1,))
+    for step in range(3):
+        want = []
+        for up, n in zip(ups, sizes):
+            p = C.c_void_p()
+            capi.call("upload_host_buffer", up, C.byref(p))
+            host = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n,))
+            host[...] = np.arange(n, dtype=np.float32) * (step + 1) + n
+            want.append(host.copy())
+        capi.call("upload_submit_all", up_arr, dst_arr, C.c_int(len(ups)))
+        capi.call("reduce", C.c_int(REDUCE["sum"]), dsts[0].ptr, C.c_int64(1), C.c_int64(sizes[1]), C.c_int64(1), total.ptr)
+        capi.call("publish_to_host", out, total.ptr, C.c_int64(1))
+        capi.call("event_record", ev)
+        capi.call("event_synchronize", ev)
+        assert_close(host_out.copy(), np.array([want[1].astype(np.float64).sum()]), 1e-5, "published sum")
+        got = [big.numpy()[1:]] + [d.numpy() for d in dsts]
+        for g, w in zip(got, want):
+            assert np.array_equal(g, w)
+    twice = (C.c_void_p * 2)(ups[0].value, ups[0].value)
+    pageable = np.zeros(4, np.float32)
+    for name, args in (("upload_submit_all", (up_arr, dst_arr, C.c_int(0))), ("upload_submit_all", (twice, dst_arr, C.c_int(2))),
+                       ("publish_to_host", (pageable.ctypes.data_as(C.c_void_p), total.ptr, C.c_int64(1))),
+                       ("publish_to_host", (total.ptr, total.ptr, C.c_int64(1)))):
+        with pytest.raises(RtError) as ei:
+            capi.call(name, *args)
+        assert ei.value.code == 4
+    capi.call("host_free", out)
+    capi.call("event_destroy", ev)
+    for up in ups:
+        capi.call("upload_destroy", up)
+
+
 def test_side_stream_sections(capi):
     """Work issued between rt_side_stream_begin and _end runs after what was queued before and is waited for by _join;
     nesting, joining inside a section and allocating inside a section are refused."""
