@@ -59,6 +59,9 @@ struct Params {
 // 8-row groups NQ*128 bytes apart.  value(n, c, t) = w[n*sn + c*sc + ky*sky + kx*skx + off0].
 __global__ void pack_weights_kernel(const float* __restrict__ w, float* __restrict__ img, int N, int C, int BN, int NQ,
                                     int kh, int kw, int sn, int sc, int sky, int skx, int off0) {
+  // The convolution kernel is launched as a programmatic dependent of this one: it may start its prologue (barriers, tensor
+  // memory, the first window loads) right away and waits for this grid only before it fetches the packed weights.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int Cp = NQ * 4;
   const int per_tap = BN * Cp;
   const int total = kh * kw * per_tap;
@@ -254,6 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_window_kernel(const Params p
     // resident weights: bulk copies of the packed image, in pieces of at most 32 KiB
     {
       const uint32_t bytes = 2 * b_half;
+      asm volatile("griddepcontrol.wait;" ::: "memory");  // the packing kernel has finished and its image is visible
       if (lane == 0) {
         mbar_expect_tx(bars + 8 * 8, bytes);
         for (uint32_t o = 0; o < bytes; o += 32768u) {
@@ -362,7 +366,17 @@ rt_status rt_conv_window_tc_internal(rt_ctx* ctx, const float* src, int Nb, int 
   const int grid = p.tiles < ctx->sm_count ? p.tiles : ctx->sm_count;
   auto launch = [&](auto kern) -> rt_status {
     RT_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-    kern<<<grid, kThreads, smem_bytes, ctx->stream>>>(p, ctx->device_status);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    RT_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, p, ctx->device_status));
     return RT_OK;
   };
   rt_status ls;
