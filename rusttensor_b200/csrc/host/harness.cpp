@@ -85,8 +85,8 @@ struct DpTrainer {
   // travel; the rows are gathered on the device straight into the step's input tensors
   std::vector<Storage> dataset;          // one [rows, sample elements] tensor per input
   int64_t dataset_rows = 0;
-  int32_t* idx_pinned[2] = {nullptr, nullptr};
-  Storage idx_dev[2];
+  rt_upload* idx_upload = nullptr;  // row numbers of the next batch: pinned buffers, copy stream and staging like any input
+  Storage idx_dev;
   // RT_B200_DP_OVERLAP=1 sends the early gradient slice while the backward pass is still running.  Off by default:
   // with this model (1.7 MB of gradients) on two B200s the extra NCCL launch and graph launch cost more than the
   // overlap hides (0.371 ms per step against 0.362 ms).
@@ -101,8 +101,7 @@ struct DpTrainer {
       if (pipe_loss[i]) rt_host_free(c, pipe_loss[i]);
       if (pipe_done[i]) rt_event_destroy(c, pipe_done[i]);
     }
-    for (int i = 0; i < 2; ++i)
-      if (idx_pinned[i]) rt_host_free(c, idx_pinned[i]);
+    if (idx_upload) rt_upload_destroy(c, idx_upload);
     if (graph) rt_graph_destroy(c, graph);
     if (graph_b) rt_graph_destroy(c, graph_b);
     for (float* p : pinned_in) rt_host_free(c, p);
@@ -572,14 +571,8 @@ struct DpTrainer {
     }
     dataset_rows = rows;
     const size_t batch = inputs[0].shape()[0];
-    for (int i = 0; i < 2; ++i) {
-      if (!idx_pinned[i]) {
-        void* hp = nullptr;
-        B200Backend::check(rt_host_alloc(B200Backend::ctx(), sizeof(int32_t) * batch, &hp));
-        idx_pinned[i] = (int32_t*)hp;
-      }
-      idx_dev[i] = B200Backend::zeros(rt::Shape{batch});
-    }
+    if (!idx_upload) B200Backend::check(rt_upload_create(B200Backend::ctx(), sizeof(int32_t) * batch, &idx_upload));
+    idx_dev = B200Backend::zeros(rt::Shape{batch});
   }
   // Like step_pipelined, but the inputs are rows `indices` of the attached data set: 4 bytes per sample go to the device.
   bool step_dataset(const int64_t* indices, int64_t n, float* prev_loss) {
@@ -590,16 +583,18 @@ struct DpTrainer {
     if (!graph) capture();
     rt_ctx* c = B200Backend::ctx();
     const int k = (int)(pipe_steps & 1);
-    if (pipe_steps >= 2) B200Backend::check(rt_event_synchronize(c, pipe_done[k]));  // the copy that last read this index buffer is done
-    for (int64_t i = 0; i < n; ++i) {
+    for (int64_t i = 0; i < n; ++i)
       if (indices[i] < 0 || indices[i] >= dataset_rows) throw Error(ErrorKind::InvalidIndex, "step_dataset: row outside the data set");
-      idx_pinned[k][i] = (int32_t)indices[i];
-    }
-    B200Backend::check(rt_memcpy_h2d_async(c, idx_dev[k].ptr(), idx_pinned[k], sizeof(int32_t) * (size_t)n));
+    // the row numbers travel like an input of step_pipelined: host -> staging on the copy stream, staging -> idx_dev by a kernel
+    void* hp = nullptr;
+    B200Backend::check(rt_upload_host_buffer(c, idx_upload, &hp));
+    for (int64_t i = 0; i < n; ++i) static_cast<int32_t*>(hp)[i] = (int32_t)indices[i];
+    void* idx_dst = idx_dev.ptr();
+    B200Backend::check(rt_upload_submit_all(c, &idx_upload, &idx_dst, 1));
     for (size_t i = 0; i < inputs.size(); ++i) {
       B200Backend::make_unique(inputs[i].data_mut());
       const int64_t per = (int64_t)(inputs[i].size() / (size_t)batch);
-      B200Backend::check(rt_gather_rows(c, dataset[i].ptr(), dataset_rows, per, reinterpret_cast<const int32_t*>(idx_dev[k].ptr()), n,
+      B200Backend::check(rt_gather_rows(c, dataset[i].ptr(), dataset_rows, per, reinterpret_cast<const int32_t*>(idx_dev.ptr()), n,
                                         inputs[i].data().ptr()));
     }
     replay();
