@@ -38,38 +38,56 @@ __device__ __forceinline__ void load_taps(const ThinParams& p, uint32_t b, uint3
   }
 }
 
+// Thread = output pixel: its taps sit in registers, the weights in shared memory transposed to [tap][channel] so that one
+// 128-bit broadcast load brings a tap's weights for four channels.  Four channels are computed at a time - four independent
+// chains of fused multiply-adds, each in the order bias, then the taps (ky, kx) ascending - and stored as four coalesced rows.
 template <int TP>
 __global__ void __launch_bounds__(kThreads) thin_conv_forward_kernel(const ThinParams p, const float* __restrict__ w,
                                                                       const float* __restrict__ bias, float* __restrict__ y) {
-  extern __shared__ __align__(16) float sm[];  // w_s[N][TP], bias_s[N]
-  float* w_s = sm;
-  float* bias_s = sm + p.N * TP;
-  for (int i = threadIdx.x; i < p.N * TP; i += kThreads) {
-    const int n = i / TP, t = i - n * TP;
-    w_s[i] = t < p.T ? __ldg(w + n * p.T + t) : 0.f;
-  }
-  for (int i = threadIdx.x; i < p.N; i += kThreads) bias_s[i] = bias ? __ldg(bias + i) : 0.f;
-  __syncthreads();
-  const int howo = p.Ho * p.Wo;
-  for (int64_t px = (int64_t)blockIdx.x * kThreads + threadIdx.x; px < p.pixels; px += (int64_t)gridDim.x * kThreads) {
-    uint32_t b, r, yo, xo;
+  extern __shared__ __align__(16) float sm[];  // w_t[TP][NP], bias_s[NP]; NP = N rounded up to a multiple of four
+  const int NP = (p.N + 3) & ~3;
+  float* w_t = sm;
+  float* bias_s = sm + TP * NP;
+  // the taps of the first pixel are requested before the weights are staged, so that the two latencies overlap
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  int64_t px = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  uint32_t b = 0, r = 0, yo, xo;
+  float tap[TP];
+  if (px < p.pixels) {
     p.d_HoWo.divmod((uint32_t)px, b, r);
     p.d_Wo.divmod(r, yo, xo);
-    float tap[TP];
     load_taps<TP>(p, b, yo, xo, tap);
+  }
+  for (int i = threadIdx.x; i < TP * NP; i += kThreads) {
+    const int t = i / NP, n = i - t * NP;
+    w_t[i] = (t < p.T && n < p.N) ? __ldg(w + n * p.T + t) : 0.f;
+  }
+  for (int i = threadIdx.x; i < NP; i += kThreads) bias_s[i] = (bias && i < p.N) ? __ldg(bias + i) : 0.f;
+  __syncthreads();
+  const int howo = p.Ho * p.Wo;
+  while (px < p.pixels) {
     float* out = y + (int64_t)b * p.N * howo + r;
-    for (int n = 0; n < p.N; ++n) {
-      float acc = bias_s[n];
-      const float4* wr = reinterpret_cast<const float4*>(w_s + n * TP);
+    for (int n = 0; n < p.N; n += 4) {
+      float4 acc = *reinterpret_cast<const float4*>(bias_s + n);
 #pragma unroll
-      for (int t4 = 0; t4 < TP / 4; ++t4) {
-        const float4 wv = wr[t4];
-        acc = fmaf(tap[t4 * 4 + 0], wv.x, acc);
-        acc = fmaf(tap[t4 * 4 + 1], wv.y, acc);
-        acc = fmaf(tap[t4 * 4 + 2], wv.z, acc);
-        acc = fmaf(tap[t4 * 4 + 3], wv.w, acc);
+      for (int t = 0; t < TP; ++t) {
+        const float4 wv = *reinterpret_cast<const float4*>(w_t + t * NP + n);
+        acc.x = fmaf(tap[t], wv.x, acc.x);
+        acc.y = fmaf(tap[t], wv.y, acc.y);
+        acc.z = fmaf(tap[t], wv.z, acc.z);
+        acc.w = fmaf(tap[t], wv.w, acc.w);
       }
-      out[(int64_t)n * howo] = acc;
+      float* o = out + (int64_t)n * howo;
+      o[0] = acc.x;
+      if (n + 1 < p.N) o[howo] = acc.y;
+      if (n + 2 < p.N) o[2 * (int64_t)howo] = acc.z;
+      if (n + 3 < p.N) o[3 * (int64_t)howo] = acc.w;
+    }
+    px += stride;
+    if (px < p.pixels) {
+      p.d_HoWo.divmod((uint32_t)px, b, r);
+      p.d_Wo.divmod(r, yo, xo);
+      load_taps<TP>(p, b, yo, xo, tap);
     }
   }
 }
@@ -457,10 +475,12 @@ rt_status rt_conv_forward_thin_internal(rt_ctx* ctx, const float* x, const float
                                         float* y) {
   ThinParams p;
   if (g.Cy < 1 || g.Cy > 512 || !make_params(g, x, &p)) return RT_ERR_UNIMPLEMENTED;
-  const int TP = (p.T + 3) / 4 * 4;
-  const size_t smem = sizeof(float) * (size_t)(g.Cy * TP + g.Cy);
+  const int TP = p.T == 9 ? 9 : (p.T + 3) / 4 * 4;  // a 3x3 single-channel layer gets its exact tap count
+  const int NP = (g.Cy + 3) & ~3;
+  const size_t smem = sizeof(float) * (size_t)(NP * TP + NP);
   const int grid = rt_grid_for(ctx, p.pixels, kThreads, 16);
   switch (TP) {
+    case 9: thin_conv_forward_kernel<9><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
     case 4: thin_conv_forward_kernel<4><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
     case 8: thin_conv_forward_kernel<8><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
     case 12: thin_conv_forward_kernel<12><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
