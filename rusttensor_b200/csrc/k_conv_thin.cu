@@ -41,11 +41,14 @@ __device__ __forceinline__ void load_taps(const ThinParams& p, uint32_t b, uint3
 // Thread = output pixel: its taps sit in registers, the weights in shared memory transposed to [tap][channel] so that one
 // 128-bit broadcast load brings a tap's weights for four channels.  Four channels are computed at a time - four independent
 // chains of fused multiply-adds, each in the order bias, then the taps (ky, kx) ascending - and stored as four coalesced rows.
-template <int TP>
+// NQC > 0: the layer has exactly 4 * NQC output channels, a compile-time constant, so that the channel loop unrolls into
+// straight-line code with immediate shared-memory offsets and no tests (the kernel is bound by instruction issue: the
+// run-time loop spent 1 100 instructions per warp on 288 fused multiply-adds per lane).  NQC == 0: any channel count.
+template <int TP, int NQC>
 __global__ void __launch_bounds__(kThreads) thin_conv_forward_kernel(const ThinParams p, const float* __restrict__ w,
                                                                       const float* __restrict__ bias, float* __restrict__ y) {
   extern __shared__ __align__(16) float sm[];  // w_t[TP][NP], bias_s[NP]; NP = N rounded up to a multiple of four
-  const int NP = (p.N + 3) & ~3;
+  const int NP = NQC > 0 ? 4 * NQC : (p.N + 3) & ~3;
   float* w_t = sm;
   float* bias_s = sm + TP * NP;
   // the taps of the first pixel are requested before the weights are staged, so that the two latencies overlap
@@ -67,21 +70,41 @@ __global__ void __launch_bounds__(kThreads) thin_conv_forward_kernel(const ThinP
   const int howo = p.Ho * p.Wo;
   while (px < p.pixels) {
     float* out = y + (int64_t)b * p.N * howo + r;
-    for (int n = 0; n < p.N; n += 4) {
-      float4 acc = *reinterpret_cast<const float4*>(bias_s + n);
+    if (NQC > 0) {
 #pragma unroll
-      for (int t = 0; t < TP; ++t) {
-        const float4 wv = *reinterpret_cast<const float4*>(w_t + t * NP + n);
-        acc.x = fmaf(tap[t], wv.x, acc.x);
-        acc.y = fmaf(tap[t], wv.y, acc.y);
-        acc.z = fmaf(tap[t], wv.z, acc.z);
-        acc.w = fmaf(tap[t], wv.w, acc.w);
+      for (int q = 0; q < NQC; ++q) {
+        float4 acc = *reinterpret_cast<const float4*>(bias_s + 4 * q);
+#pragma unroll
+        for (int t = 0; t < TP; ++t) {
+          const float4 wv = *reinterpret_cast<const float4*>(w_t + t * (4 * NQC) + 4 * q);
+          acc.x = fmaf(tap[t], wv.x, acc.x);
+          acc.y = fmaf(tap[t], wv.y, acc.y);
+          acc.z = fmaf(tap[t], wv.z, acc.z);
+          acc.w = fmaf(tap[t], wv.w, acc.w);
+        }
+        out[0] = acc.x;
+        out[howo] = acc.y;
+        out[2 * howo] = acc.z;
+        out[3 * howo] = acc.w;
+        out += 4 * howo;
       }
-      float* o = out + (int64_t)n * howo;
-      o[0] = acc.x;
-      if (n + 1 < p.N) o[howo] = acc.y;
-      if (n + 2 < p.N) o[2 * (int64_t)howo] = acc.z;
-      if (n + 3 < p.N) o[3 * (int64_t)howo] = acc.w;
+    } else {
+      for (int n = 0; n < p.N; n += 4) {
+        float4 acc = *reinterpret_cast<const float4*>(bias_s + n);
+#pragma unroll
+        for (int t = 0; t < TP; ++t) {
+          const float4 wv = *reinterpret_cast<const float4*>(w_t + t * NP + n);
+          acc.x = fmaf(tap[t], wv.x, acc.x);
+          acc.y = fmaf(tap[t], wv.y, acc.y);
+          acc.z = fmaf(tap[t], wv.z, acc.z);
+          acc.w = fmaf(tap[t], wv.w, acc.w);
+        }
+        float* o = out + (int64_t)n * howo;
+        o[0] = acc.x;
+        if (n + 1 < p.N) o[howo] = acc.y;
+        if (n + 2 < p.N) o[2 * (int64_t)howo] = acc.z;
+        if (n + 3 < p.N) o[3 * (int64_t)howo] = acc.w;
+      }
     }
     px += stride;
     if (px < p.pixels) {
@@ -479,12 +502,18 @@ rt_status rt_conv_forward_thin_internal(rt_ctx* ctx, const float* x, const float
   const int NP = (g.Cy + 3) & ~3;
   const size_t smem = sizeof(float) * (size_t)(NP * TP + NP);
   const int grid = rt_grid_for(ctx, p.pixels, kThreads, 16);
+  if ((int64_t)g.Cy * p.Ho * p.Wo >= (1ll << 31)) return RT_ERR_UNIMPLEMENTED;  // channel offsets inside one image are 32-bit
   switch (TP) {
-    case 9: thin_conv_forward_kernel<9><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
-    case 4: thin_conv_forward_kernel<4><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
-    case 8: thin_conv_forward_kernel<8><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
-    case 12: thin_conv_forward_kernel<12><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
-    default: thin_conv_forward_kernel<16><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
+    case 9:
+      if (g.Cy == 16) thin_conv_forward_kernel<9, 4><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y);
+      else if (g.Cy == 32) thin_conv_forward_kernel<9, 8><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y);
+      else if (g.Cy == 64) thin_conv_forward_kernel<9, 16><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y);
+      else thin_conv_forward_kernel<9, 0><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y);
+      break;
+    case 4: thin_conv_forward_kernel<4, 0><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
+    case 8: thin_conv_forward_kernel<8, 0><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
+    case 12: thin_conv_forward_kernel<12, 0><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
+    default: thin_conv_forward_kernel<16, 0><<<grid, kThreads, smem, ctx->stream>>>(p, w, bias, y); break;
   }
   RT_LAUNCHED(ctx);
   return RT_OK;
