@@ -422,12 +422,17 @@ constexpr int kPoolChannelGroup = 16;
 __global__ void __launch_bounds__(kThreads) thin_conv_relu_pool_kernel(const ThinPoolParams p, const float* __restrict__ w,
                                                                         const float* __restrict__ bias, float* __restrict__ y,
                                                                         float* __restrict__ idx) {
-  __shared__ float w_s[kPoolChannelGroup][9];
-  __shared__ float b_s[kPoolChannelGroup];
+  // weights transposed to [tap][channel]: one 128-bit broadcast load brings a tap's weights for four channels; channels past the
+  // layer's last one hold zeros and are computed but not stored
+  __shared__ __align__(16) float w_t[9][kPoolChannelGroup];
+  __shared__ __align__(16) float b_s[kPoolChannelGroup];
   const int n0 = blockIdx.y * kPoolChannelGroup;
   const int nn = min(kPoolChannelGroup, p.N - n0);
-  for (int i = threadIdx.x; i < nn * 9; i += kThreads) w_s[i / 9][i % 9] = __ldg(w + (n0 + i / 9) * 9 + i % 9);
-  for (int i = threadIdx.x; i < nn; i += kThreads) b_s[i] = bias ? __ldg(bias + n0 + i) : 0.f;
+  for (int i = threadIdx.x; i < kPoolChannelGroup * 9; i += kThreads) {
+    const int n = i / 9, t = i - n * 9;
+    w_t[t][n] = n < nn ? __ldg(w + (n0 + n) * 9 + t) : 0.f;
+  }
+  for (int i = threadIdx.x; i < kPoolChannelGroup; i += kThreads) b_s[i] = (bias && i < nn) ? __ldg(bias + n0 + i) : 0.f;
   __syncthreads();
   const int hpwp = p.Hp * p.Wp;
   for (int64_t q = (int64_t)blockIdx.x * kThreads + threadIdx.x; q < p.pooled; q += (int64_t)gridDim.x * kThreads) {
@@ -446,25 +451,44 @@ __global__ void __launch_bounds__(kThreads) thin_conv_relu_pool_kernel(const Thi
       }
     float* yo = y + ((int64_t)b * p.N + n0) * hpwp + r;
     float* io = idx + ((int64_t)b * p.N + n0) * hpwp + r;
-    for (int n = 0; n < nn; ++n) {
-      float v[4];
 #pragma unroll
-      for (int d = 0; d < 4; ++d) {
-        const int dy = d >> 1, dx = d & 1;
-        float acc = b_s[n];
+    for (int c4 = 0; c4 < kPoolChannelGroup; c4 += 4) {
+      if (c4 < nn) {  // the same for every thread of the block
+        // acc[d][j]: output d of the 2x2 window (row-major) for channel c4 + j; per output the chain is bias, then the taps in
+        // (ky, kx) order - the order of thin_conv_forward_kernel
+        float acc[4][4];
+        const float4 bv = *reinterpret_cast<const float4*>(&b_s[c4]);
+#pragma unroll
+        for (int d = 0; d < 4; ++d) { acc[d][0] = bv.x; acc[d][1] = bv.y; acc[d][2] = bv.z; acc[d][3] = bv.w; }
 #pragma unroll
         for (int ky = 0; ky < 3; ++ky)
 #pragma unroll
-          for (int kx = 0; kx < 3; ++kx) acc = fmaf(patch[dy + ky][dx + kx], w_s[n][ky * 3 + kx], acc);
-        v[d] = fmaxf(acc, 0.f);
-      }
-      float mv = -INFINITY;
-      int mi = 0;
+          for (int kx = 0; kx < 3; ++kx) {
+            const float4 wv = *reinterpret_cast<const float4*>(&w_t[ky * 3 + kx][c4]);
 #pragma unroll
-      for (int d = 0; d < 4; ++d)
-        if (v[d] > mv) { mv = v[d]; mi = d; }
-      yo[(int64_t)n * hpwp] = mv;
-      io[(int64_t)n * hpwp] = (float)mi;
+            for (int d = 0; d < 4; ++d) {
+              const float a = patch[(d >> 1) + ky][(d & 1) + kx];
+              acc[d][0] = fmaf(a, wv.x, acc[d][0]);
+              acc[d][1] = fmaf(a, wv.y, acc[d][1]);
+              acc[d][2] = fmaf(a, wv.z, acc[d][2]);
+              acc[d][3] = fmaf(a, wv.w, acc[d][3]);
+            }
+          }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (c4 + j < nn) {
+            float mv = -INFINITY;
+            int mi = 0;
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+              const float v = fmaxf(acc[d][j], 0.f);
+              if (v > mv) { mv = v; mi = d; }
+            }
+            yo[(int64_t)(c4 + j) * hpwp] = mv;
+            io[(int64_t)(c4 + j) * hpwp] = (float)mi;
+          }
+        }
+      }
     }
   }
 }
